@@ -1,0 +1,194 @@
+/*
+ * ingot_qmm.h — C ABI of libingot_qmm.so: ingot's quantized-matmul hot path (MLX affine 4/8-bit g64 and MXFP4
+ * quantized linear layers; decode GEMV, prefill GEMM, MoE grouped form) as hand-written CUDA for NVIDIA B200 (sm_100a).
+ *
+ * The reference engine (Swift + Metal) has no FFI; this header is what a Swift module map (include/module.modulemap,
+ * module CIngotQMM) would import so that the bodies of the reference's four launcher entry points can call CUDA where
+ * they dispatched Metal kernels. Each declaration cites the reference interface it replaces (paths inside the
+ * reference project).
+ *
+ * Conventions, kept from the reference:
+ *   - weights stay in the MLX layout byte for byte (Sources/Ingot/Loader/Quant.swift:4-12): `w` uint32
+ *     [experts, n, k*bits/32] with value j of a row in bits [bits*j, bits*j+bits); `scales`/`biases` bf16
+ *     [experts, n, k/group] (affine, w = scale*q + bias) or `scales` uint8 e8m0 [experts, n, k/32] and no biases (mxfp4);
+ *   - every pointer is a device pointer owned by the caller; nothing is allocated, freed or synchronised in a call that
+ *     takes a stream: work is enqueued on `stream` (a cudaStream_t passed as void*) and the call returns;
+ *   - scratch memory is the caller's: ask for the size once (…_workspace_bytes), allocate it at layer construction
+ *     (the reference allocates its scratch at construction too, Layers/MoE.swift:220-241), pass it to every call;
+ *   - every function returns 0 or a negative iq_status; iq_last_error(ctx) gives the message. Shapes the reference's
+ *     launchers reject with a precondition (rows > 16 in qmv, M % 64 != 0 in qmm, …) come back as IQ_ERR_INVALID_ARG;
+ *   - a context serves one device; calls on one context from several threads must use different streams and may not
+ *     share workspaces.
+ * There is no CPU path: every entry point either enqueues CUDA kernels or fails.
+ */
+#ifndef INGOT_QMM_H
+#define INGOT_QMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct iq_ctx iq_ctx;
+typedef struct iq_moe iq_moe;
+
+typedef enum iq_status {
+    IQ_OK = 0,
+    IQ_ERR_INVALID_ARG = -1, /* a shape / pointer / flag the operator does not accept */
+    IQ_ERR_UNSUPPORTED = -2, /* a format or combination with no kernel (the reference's "load error") */
+    IQ_ERR_CUDA = -3,        /* a CUDA runtime call failed; see iq_last_error */
+    IQ_ERR_WORKSPACE = -4,   /* workspace missing or too small */
+    IQ_ERR_NO_KERNEL = -5,
+    IQ_ERR_TIMEOUT = -6, /* a bounded device-side wait gave up (status word written by the kernel) */
+    IQ_ERR_COMM = -7
+} iq_status;
+
+typedef enum iq_dtype { IQ_F32 = 0, IQ_F16 = 1, IQ_BF16 = 2 } iq_dtype;
+typedef enum iq_mode { IQ_MODE_AFFINE = 0, IQ_MODE_MXFP4 = 1 } iq_mode;
+typedef enum iq_act { IQ_ACT_SILU = 0, IQ_ACT_SWIGLU_OAI = 2 } iq_act; /* qmm.metal:17-31 ACT0 / ACT2 */
+typedef enum iq_router_kind { IQ_ROUTER_BF16 = 0, IQ_ROUTER_Q8 = 1 } iq_router_kind;
+
+enum { IQ_FLAG_ACCUMULATE = 1 }; /* y += result (VQMV.encode accumulate:, encodeQmmF32 accumulate:) */
+
+/* A quantized matrix on the device. Replaces DenseQ (Sources/Ingot/Layers/Linear.swift:17-33) and
+ * DeviceQuantizedLinear (Sources/Ingot/Loader/Quant.swift:205-231): three buffers plus N, K, bits, group size.
+ * `experts` > 1: stacked expert tensors, expert e at word offset e*n*(k*bits/32) and scale offset e*n*(k/group). */
+typedef struct iq_qlinear {
+    const void* w;
+    const void* scales;
+    const void* biases; /* NULL for mxfp4 */
+    int32_t n;          /* output features (rows of W) */
+    int32_t k;          /* input features */
+    int32_t bits;       /* 4 or 8 */
+    int32_t group;      /* 64 (affine) or 32 (mxfp4) */
+    int32_t mode;       /* iq_mode */
+    int32_t experts;    /* leading dimension, 1 for a plain layer */
+} iq_qlinear;
+
+/* ---- context -------------------------------------------------------------------------------------------------------
+ * Replaces MetalContext (Sources/Ingot/GPU.swift:6-29: one device, one queue, the pipeline cache). Creating a context
+ * selects the device, checks that it is sm_100 and configures the kernels' shared-memory limits. */
+int32_t iq_ctx_create(int32_t device, iq_ctx** out);
+void iq_ctx_destroy(iq_ctx* ctx);
+const char* iq_strerror(int32_t status);
+const char* iq_last_error(const iq_ctx* ctx);
+/* Synchronises the device and returns the status word that kernels with bounded waits write when a wait gives up
+ * (0 = none did; the word is cleared when read). The reference surfaces GPU errors at waitUntilCompleted
+ * (Sources/Ingot/GPU.swift:164-167); this is the equivalent place. Not for the enqueue path. */
+int32_t iq_ctx_status(iq_ctx* ctx, int32_t* device_status);
+/* ABI version of this header (bumped on incompatible changes). */
+int32_t iq_abi_version(void);
+
+/* ---- decode GEMV ---------------------------------------------------------------------------------------------------
+ * Y[rows, n] (+)= X[rows, k] * W^T, rows <= 16. Replaces VQMV.encode(enc, x:, xOffset:, xFloat:, m, y:, yOffset:, rows:,
+ * ldx:, ldy:, accumulate:, nPrefix:) (Sources/Ingot/Layers/Linear.swift:287-444) and the kernels behind it
+ * (Shaders/verify_nax.metal:105-209, Shaders/verify.metal:89-155).
+ * x: [rows, ldx] of x_dtype (the reference takes half or float; bf16 is added because the checkpoints' activations
+ * are bf16); y: [rows, ldy] of y_dtype (the reference writes float). n_prefix > 0 computes only the first n_prefix
+ * output features (a multiple of 16). Requires n % 16 == 0, k % 64 == 0, ldx % 8 == 0, 16-byte aligned x.
+ * The bits of row i do not depend on `rows` or on the other rows. */
+int32_t iq_qmv(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx, const iq_qlinear* m, void* y,
+               int32_t y_dtype, int64_t ldy, int32_t rows, uint32_t flags, int32_t n_prefix);
+
+/* ---- prefill GEMM --------------------------------------------------------------------------------------------------
+ * Y[rows, n] (+)= X[rows, k] * W^T on the tcgen05 tensor cores (weights dequantised to fp16 in shared memory, fp32
+ * accumulation in tensor memory). Replaces DenseQ.encodeQmmF32(ctx, enc, x:, xOffset:, y:, rows:, accumulate:, halfOut:)
+ * (Sources/Ingot/Layers/Linear.swift:688-713) and qmm_t_nax3* (Shaders/qmm_nax_v3.metal:107-256).
+ * Requires rows % 64 == 0 and n % 64 == 0 like the reference (Linear.swift:695), k % 64 == 0.
+ * x of dtype bf16/f32 is converted to fp16 into the workspace first; fp16 x is used in place. */
+int32_t iq_qmm_workspace_bytes(iq_ctx* ctx, const iq_qlinear* m, int32_t rows, int32_t x_dtype, size_t* bytes);
+int32_t iq_qmm(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx, const iq_qlinear* m, void* y,
+               int32_t y_dtype, int64_t ldy, int32_t rows, uint32_t flags, void* workspace, size_t workspace_bytes);
+
+/* ---- dense gated FFN ------------------------------------------------------------------------------------------------
+ * out[rows, d] (+)= down( act(gate x) * up x ) with gate|up concatenated by rows as one [2*d_ff, d] matrix (gate rows
+ * first). Replaces DenseMLP.encode / encodePrefill (Sources/Ingot/Layers/Dense.swift:56-96) and dswiglu*
+ * (Shaders/yy_model.metal:187-227). rows <= 16 takes the GEMV path, larger multiples of 64 the GEMM path. */
+int32_t iq_dense_ffn_workspace_bytes(iq_ctx* ctx, const iq_qlinear* gate_up, const iq_qlinear* down, int32_t rows,
+                                     int32_t x_dtype, size_t* bytes);
+int32_t iq_dense_ffn(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx, const iq_qlinear* gate_up,
+                     const iq_qlinear* down, int32_t act, float act_limit, void* out, int32_t out_dtype, int64_t ldo,
+                     int32_t rows, uint32_t flags, void* workspace, size_t workspace_bytes);
+
+/* ---- MoE layer -----------------------------------------------------------------------------------------------------
+ * Replaces MoELayer (Sources/Ingot/Layers/MoE.swift:54-429) and PrefillMoE (Sources/Ingot/Layers/MoEPrefill.swift:29-278):
+ * router -> top-k -> group by expert -> gate+up+activation -> down -> weighted combine. The description is the
+ * reference's load-time state: RouterSpec (Loader/ModelSpecParts.swift:64), the stacked expert tensors, the optional
+ * gpt-oss expert biases (MoEPrefill.swift:9-22). Accepted shapes are the reference's (MoE.swift:186-219,
+ * MoEPrefill.swift:129-142): experts % 32 == 0, experts <= 512, top_k <= 16, d_ff % 64 == 0, d_model % 64 == 0,
+ * d_model >= 128, experts affine 4-bit g64 or mxfp4, router bf16 or 8-bit g64; anything else is IQ_ERR_UNSUPPORTED. */
+typedef struct iq_moe_desc {
+    int32_t experts;        /* E: experts of the model (router width) */
+    int32_t top_k;
+    int32_t d_model;
+    int32_t d_ff;
+    int32_t act;            /* iq_act */
+    float act_limit;        /* swiglu_oai clamp (the config's swiglu_limit, 7) */
+    int32_t router_kind;    /* iq_router_kind */
+    float routed_scale;     /* multiplies the renormalised weights (routed_scaling_factor); 1 when absent */
+    const void* router_w;   /* bf16 [E, d_model], or uint32 8-bit codes [E, d_model/4] */
+    const void* router_scales;      /* 8-bit router only */
+    const void* router_biases;      /* 8-bit router only */
+    const float* router_logit_bias; /* fp32 [E] added to the logits (gpt-oss mlp.router.bias) or NULL */
+    const float* per_expert_scale;  /* fp32 [E] (Gemma 4 router.per_expert_scale) or NULL */
+    iq_qlinear gate;        /* [local experts, d_ff, d_model] */
+    iq_qlinear up;          /* [local experts, d_ff, d_model] */
+    iq_qlinear down;        /* [local experts, d_model, d_ff] */
+    const float* gate_bias; /* fp32 [local experts, d_ff] or NULL */
+    const float* up_bias;   /* fp32 [local experts, d_ff] or NULL */
+    const float* down_bias; /* fp32 [local experts, d_model] or NULL */
+    int32_t expert_lo;      /* first expert held here (expert parallel); 0 on one GPU */
+    int32_t expert_count;   /* experts held here; == experts on one GPU. The reference's analogue is the
+                               expert->slot table `smap` (MoE.swift:104) */
+} iq_moe_desc;
+
+/* Pieces of a forward call, for timing and for callers that run an exchange between them. The names are the
+ * reference's (MoELayer.Piece MoE.swift:328; PrefillMoE.Piece MoEPrefill.swift:55). */
+enum {
+    IQ_PIECE_ROUTER = 1,  /* logits = x * router^T */
+    IQ_PIECE_ROUTE = 2,   /* top-k indices and weights */
+    IQ_PIECE_GROUP = 4,   /* token -> expert permutation, tile list */
+    IQ_PIECE_GATEUP = 8,  /* h = act(gate x, up x) per expert */
+    IQ_PIECE_DOWN = 16,   /* yd = down h per expert */
+    IQ_PIECE_COMBINE = 32, /* out (+)= sum_k w * yd */
+    IQ_PIECE_ALL = 63
+};
+
+/* Device views into the workspace after a forward call (valid until the next call with the same workspace). */
+typedef struct iq_moe_views {
+    float* logits;      /* [T, ld], ld = experts rounded up to 64 (MoELayer.routerLD, MoE.swift:296) */
+    int32_t ld;
+    uint32_t* inds;     /* [T, top_k] expert ids, descending score, ties to the lower id */
+    float* wts;         /* [T, top_k] */
+    uint32_t* offsets;  /* [E + 1] first sorted position of each expert */
+    uint32_t* row_map;  /* [T*top_k] sorted position -> pair id (pair = token*top_k + rank) */
+    uint32_t* pos;      /* [T*top_k] pair id -> sorted position */
+    void* h;            /* fp16 [T*top_k, d_ff] activations at sorted positions */
+    float* yd;          /* fp32 [T*top_k, d_model] expert outputs at sorted positions */
+} iq_moe_views;
+
+int32_t iq_moe_create(iq_ctx* ctx, const iq_moe_desc* desc, iq_moe** out);
+void iq_moe_destroy(iq_moe* layer);
+/* Workspace for up to `max_tokens` tokens per call. */
+int32_t iq_moe_workspace_bytes(const iq_moe* layer, int32_t max_tokens, size_t* bytes);
+/* out[T, ldo] (+)= MoE(x[T, ldx]). Replaces MoELayer.encode(enc, x:, out:, rows:, accumulate:, only:)
+ * (MoE.swift:346-428) for any T and PrefillMoE.encode / encodeAll (MoEPrefill.swift:173-278). `pieces` is a mask of
+ * IQ_PIECE_*; a partial mask reuses what earlier pieces left in the workspace. */
+int32_t iq_moe_forward(iq_moe* layer, void* stream, const void* x, int32_t x_dtype, int64_t ldx, void* out,
+                       int32_t out_dtype, int64_t ldo, int32_t tokens, uint32_t flags, uint32_t pieces, void* workspace,
+                       size_t workspace_bytes);
+/* Routing only, on logits the caller supplies ([T, ld] fp32): writes inds [T, top_k] and wts [T, top_k].
+ * Replaces the route kernels as the reference's router cases drive them (Tests/IngotTests/KernelCaseRouter.swift:110-126). */
+int32_t iq_moe_route(iq_moe* layer, void* stream, const float* logits, int32_t ld, int32_t tokens, uint32_t* inds,
+                     float* wts);
+/* Routing set by the caller for the next forward calls (PrefillMoE.externalRouting, MoEPrefill.swift:80-86): device
+ * arrays inds [T, top_k], wts [T, top_k]; pass NULLs to go back to the layer's own router. */
+int32_t iq_moe_set_external_routing(iq_moe* layer, const uint32_t* inds, const float* wts);
+int32_t iq_moe_get_views(const iq_moe* layer, void* workspace, int32_t tokens, iq_moe_views* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INGOT_QMM_H */

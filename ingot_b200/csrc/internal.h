@@ -1,0 +1,67 @@
+// Internal declarations shared by the translation units of libingot_qmm.so.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ingot_qmm.h"
+#include "common.cuh"
+
+struct iq_ctx {
+    int device = 0;
+    int sms = 0;
+    int smem_optin = 0;
+    // cuTensorMapEncodeTiled, resolved through the runtime so that the library does not link libcuda directly
+    void* encode_tiled = nullptr;
+    int32_t* d_status = nullptr;  // device status word written by kernels whose bounded waits gave up
+    char last_error[256] = {0};
+};
+
+namespace iq {
+
+int32_t fail(iq_ctx* ctx, int32_t code, const char* fmt, ...);
+int32_t check_cuda(iq_ctx* ctx, cudaError_t e, const char* what);
+
+inline bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+inline size_t round_up_sz(size_t v, size_t m) { return (v + m - 1) / m * m; }
+inline int dtype_size(int32_t dt) { return dt == kF32 ? 4 : 2; }
+
+// format id from (bits, group, mode) or -1
+int32_t format_of(const iq_qlinear* m);
+
+struct Tile;
+// One launch of the gqmv family. mode: 0 plain, 1 gate/up, 2 down. `max_rows` bounds the rows of any tile (<= 16).
+// tiles == nullptr means a single tile of `rows` rows. grid_tiles = upper bound of the tile count for the launch.
+struct GqmvCall {
+    int mode = 0;
+    int32_t fmt = 0;
+    const uint32_t* w[2] = {nullptr, nullptr};
+    const void* s[2] = {nullptr, nullptr};
+    const void* b[2] = {nullptr, nullptr};
+    int64_t w_estride = 0, s_estride = 0;
+    int32_t N = 0, K = 0;
+    const void* x = nullptr;
+    int32_t x_dtype = 0;
+    int64_t ldx = 0;
+    const uint32_t* row_map = nullptr;
+    int32_t topk = 1;
+    const Tile* tiles = nullptr;
+    const uint32_t* ntiles = nullptr;
+    int32_t grid_tiles = 1;
+    int32_t rows = 1;
+    int32_t max_rows = 1;
+    void* y = nullptr;
+    int32_t y_dtype = 0;
+    int64_t ldy = 0;
+    int32_t accumulate = 0;
+    const float* ebias[2] = {nullptr, nullptr};
+    float limit = 0.f;
+};
+int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c);
+int32_t gqmv_init(iq_ctx* ctx);
+int32_t qmm_init(iq_ctx* ctx);
+int32_t moe_init(iq_ctx* ctx);
+
+}  // namespace iq

@@ -1,0 +1,397 @@
+// MoE layer and dense gated FFN entry points.
+#include <new>
+
+#include "internal.h"
+#include "moe_aux.cuh"
+
+struct iq_moe {
+    iq_ctx* ctx = nullptr;
+    iq_moe_desc d;
+    int32_t fmt = 0;
+    int32_t ld = 0;  // logits row stride
+    const uint32_t* ext_inds = nullptr;
+    const float* ext_wts = nullptr;
+};
+
+namespace iq {
+
+namespace {
+
+struct MoeWs {
+    float* logits;
+    uint32_t* inds;
+    float* wts;
+    uint32_t* counts;
+    uint32_t* offsets;
+    uint32_t* row_map;
+    uint32_t* pos;
+    uint32_t* ntiles;
+    Tile* tiles_a;
+    Tile* tiles_b;
+    __half* h;
+    float* yd;
+    size_t bytes;
+};
+
+// Height of the tiles of the GEMV-style expert kernels: 8 rows while experts see few rows, else 16.
+int decode_tile_rows(const iq_moe* l, int tokens) {
+    const int64_t pairs = (int64_t)tokens * l->d.top_k;
+    return pairs <= (int64_t)l->d.experts * 6 ? 8 : 16;
+}
+constexpr int kPrefillTileRows = 128;
+constexpr int kRouterSmemMax = 200 * 1024;
+
+MoeWs carve(const iq_moe* l, void* base, int tokens) {
+    const iq_moe_desc& d = l->d;
+    const size_t P = (size_t)tokens * d.top_k;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        void* p = base ? static_cast<char*>(base) + off : nullptr;
+        off += round_up_sz(bytes, 256);
+        return p;
+    };
+    MoeWs w;
+    w.logits = static_cast<float*>(take((size_t)tokens * l->ld * 4));
+    w.inds = static_cast<uint32_t*>(take(P * 4));
+    w.wts = static_cast<float*>(take(P * 4));
+    w.counts = static_cast<uint32_t*>(take((size_t)d.experts * 4));
+    w.offsets = static_cast<uint32_t*>(take((size_t)(d.experts + 1) * 4));
+    w.row_map = static_cast<uint32_t*>(take(P * 4));
+    w.pos = static_cast<uint32_t*>(take(P * 4));
+    w.ntiles = static_cast<uint32_t*>(take(16));
+    w.tiles_a = static_cast<Tile*>(take((d.experts + P / 8 + 1) * sizeof(Tile)));
+    w.tiles_b = static_cast<Tile*>(take((d.experts + P / kPrefillTileRows + 1) * sizeof(Tile)));
+    w.h = static_cast<__half*>(take(P * d.d_ff * 2));
+    w.yd = static_cast<float*>(take(P * d.d_model * 4));
+    w.bytes = off;
+    return w;
+}
+
+typedef void (*RouteKernel)(const RouteParams);
+RouteKernel route_kernel_for(int experts) {
+    switch ((experts + 31) / 32) {
+        case 1: return route_topk_kernel<1>;
+        case 2: return route_topk_kernel<2>;
+        case 3: return route_topk_kernel<3>;
+        case 4: return route_topk_kernel<4>;
+        case 5: case 6: return route_topk_kernel<6>;
+        case 7: case 8: return route_topk_kernel<8>;
+        case 9: case 10: case 11: case 12: return route_topk_kernel<12>;
+        default: return route_topk_kernel<16>;
+    }
+}
+
+int32_t launch_route(iq_moe* l, cudaStream_t st, const float* logits, int ld, int tokens, uint32_t* inds, float* wts) {
+    RouteParams rp;
+    rp.logits = logits;
+    rp.logit_bias = l->d.router_logit_bias;
+    rp.pes = l->d.per_expert_scale;
+    rp.inds = inds;
+    rp.wts = wts;
+    rp.T = tokens; rp.E = l->d.experts; rp.ld = ld; rp.topk = l->d.top_k;
+    rp.scale = l->d.routed_scale;
+    route_kernel_for(l->d.experts)<<<(tokens + 3) / 4, 128, 0, st>>>(rp);
+    return check_cuda(l->ctx, cudaGetLastError(), "route_topk launch");
+}
+
+}  // namespace
+
+int32_t moe_init(iq_ctx* ctx) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(router_logits_kernel<0>),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterSmemMax);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(router_logits_kernel<1>),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterSmemMax);
+    return check_cuda(ctx, e, "cudaFuncSetAttribute(router)");
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Elementwise gated activation of the dense FFN GEMM path: h[r, i] = half(act(gu[r, i], gu[r, d_ff + i]))
+// (dswiglu_hh of the reference, Shaders/yy_model.metal:187-227).
+__global__ void dswiglu_kernel(const float* __restrict__ gu, __half* __restrict__ h, int rows, int d_ff, int act,
+                               float limit) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * d_ff) return;
+    const size_t r = i / d_ff, c = i % d_ff;
+    const float g = gu[r * 2 * d_ff + c], u = gu[r * 2 * d_ff + d_ff + c];
+    h[i] = __float2half_rn(act == kActSwigluOai ? glu<kActSwigluOai>(g, u, limit) : glu<kActSilu>(g, u, 0.f));
+}
+
+}  // namespace iq
+
+using namespace iq;
+
+// ---------------------------------------------------------------------------------------------------------------------
+// dense FFN
+
+extern "C" int32_t iq_dense_ffn_workspace_bytes(iq_ctx* ctx, const iq_qlinear* gate_up, const iq_qlinear* down,
+                                                int32_t rows, int32_t x_dtype, size_t* bytes) {
+    if (ctx == nullptr || gate_up == nullptr || down == nullptr || bytes == nullptr) return kErrInvalidArg;
+    if (gate_up->n % 2 != 0 || gate_up->n / 2 != down->k || gate_up->k != down->n)
+        return fail(ctx, kErrInvalidArg, "dense_ffn: gate|up [%d, %d] and down [%d, %d] do not chain", gate_up->n,
+                    gate_up->k, down->n, down->k);
+    const size_t d_ff = down->k;
+    size_t total = round_up_sz((size_t)rows * d_ff * 2, 256);  // h fp16
+    if (rows > 16) {
+        size_t q = 0;
+        int32_t st = iq_qmm_workspace_bytes(ctx, gate_up, rows, x_dtype, &q);
+        if (st != kOk) return st;
+        total += round_up_sz((size_t)rows * 2 * d_ff * 4, 256) + round_up_sz(q, 256);  // gate|up fp32 + qmm scratch
+    }
+    *bytes = total;
+    return kOk;
+}
+
+extern "C" int32_t iq_dense_ffn(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx,
+                                const iq_qlinear* gate_up, const iq_qlinear* down, int32_t act, float act_limit, void* out,
+                                int32_t out_dtype, int64_t ldo, int32_t rows, uint32_t flags, void* workspace,
+                                size_t workspace_bytes) {
+    size_t need = 0;
+    int32_t st = iq_dense_ffn_workspace_bytes(ctx, gate_up, down, rows, x_dtype, &need);
+    if (st != kOk) return st;
+    if (workspace == nullptr || workspace_bytes < need)
+        return fail(ctx, kErrWorkspace, "dense_ffn: workspace %zu < %zu", workspace_bytes, need);
+    if (act != IQ_ACT_SILU && act != IQ_ACT_SWIGLU_OAI) return fail(ctx, kErrUnsupported, "dense_ffn: activation %d", act);
+    const int32_t fmt = format_of(gate_up);
+    if (fmt < 0 || format_of(down) < 0) return fail(ctx, kErrUnsupported, "dense_ffn: weight format");
+    cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+    const int d_ff = down->k;
+    __half* h = static_cast<__half*>(workspace);
+    if (rows <= 16) {
+        if (rows < 1) return fail(ctx, kErrInvalidArg, "dense_ffn: rows = %d", rows);
+        if (d_ff % 16 != 0 || gate_up->k % 64 != 0 || ldx % 8 != 0)
+            return fail(ctx, kErrInvalidArg, "dense_ffn: shapes (d_ff %% 16, d %% 64, ldx %% 8)");
+        // gate and up rows of the concatenated matrix feed one fused gate+up+activation launch
+        const size_t row_words = (size_t)gate_up->k / 32 * gate_up->bits;
+        const size_t row_groups = (size_t)gate_up->k / gate_up->group;
+        const size_t sbytes = fmt == kFmtMxfp4 ? 1 : 2;
+        GqmvCall c;
+        c.mode = kModeGateUp;
+        c.fmt = fmt;
+        c.w[0] = static_cast<const uint32_t*>(gate_up->w);
+        c.w[1] = c.w[0] + (size_t)d_ff * row_words;
+        c.s[0] = gate_up->scales;
+        c.s[1] = static_cast<const char*>(gate_up->scales) + (size_t)d_ff * row_groups * sbytes;
+        c.b[0] = gate_up->biases;
+        c.b[1] = gate_up->biases ? static_cast<const char*>(gate_up->biases) + (size_t)d_ff * row_groups * 2 : nullptr;
+        c.N = d_ff; c.K = gate_up->k;
+        c.x = x; c.x_dtype = x_dtype; c.ldx = ldx;
+        c.rows = rows; c.max_rows = rows;
+        c.y = h; c.y_dtype = kF16; c.ldy = d_ff;
+        c.limit = act == IQ_ACT_SWIGLU_OAI ? act_limit : 0.f;
+        st = launch_gqmv(ctx, cs, c);
+        if (st != kOk) return st;
+        return iq_qmv(ctx, stream, h, IQ_F16, d_ff, down, out, out_dtype, ldo, rows, flags, 0);
+    }
+    // GEMM path: gate|up GEMM -> activation -> down GEMM
+    char* p = static_cast<char*>(workspace) + round_up_sz((size_t)rows * d_ff * 2, 256);
+    float* gu = reinterpret_cast<float*>(p);
+    p += round_up_sz((size_t)rows * 2 * d_ff * 4, 256);
+    const size_t qbytes = workspace_bytes - (p - static_cast<char*>(workspace));
+    st = iq_qmm(ctx, stream, x, x_dtype, ldx, gate_up, gu, IQ_F32, 2 * d_ff, rows, 0, p, qbytes);
+    if (st != kOk) return st;
+    const size_t total = (size_t)rows * d_ff;
+    dswiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, cs>>>(gu, h, rows, d_ff, act, act_limit);
+    st = check_cuda(ctx, cudaGetLastError(), "dswiglu launch");
+    if (st != kOk) return st;
+    return iq_qmm(ctx, stream, h, IQ_F16, d_ff, down, out, out_dtype, ldo, rows, flags, p, qbytes);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// MoE
+
+extern "C" int32_t iq_moe_create(iq_ctx* ctx, const iq_moe_desc* d, iq_moe** out) {
+    if (ctx == nullptr || d == nullptr || out == nullptr) return kErrInvalidArg;
+    *out = nullptr;
+    // the reference's load guards (Layers/MoE.swift:186-219, Layers/MoEPrefill.swift:129-142)
+    if (d->experts <= 0 || d->experts % 32 != 0 || d->experts > 512)
+        return fail(ctx, kErrUnsupported, "moe: experts = %d (a multiple of 32, at most 512)", d->experts);
+    if (d->top_k < 1 || d->top_k > 16 || d->top_k > d->experts)
+        return fail(ctx, kErrUnsupported, "moe: top_k = %d (1..16)", d->top_k);
+    if (d->d_ff <= 0 || d->d_ff % 64 != 0) return fail(ctx, kErrUnsupported, "moe: d_ff = %d (a multiple of 64)", d->d_ff);
+    if (d->d_model < 128 || d->d_model % 64 != 0)
+        return fail(ctx, kErrUnsupported, "moe: d_model = %d (a multiple of 64, at least 128)", d->d_model);
+    if (d->act != IQ_ACT_SILU && d->act != IQ_ACT_SWIGLU_OAI) return fail(ctx, kErrUnsupported, "moe: activation %d", d->act);
+    if (d->router_kind != IQ_ROUTER_BF16 && d->router_kind != IQ_ROUTER_Q8)
+        return fail(ctx, kErrUnsupported, "moe: router kind %d (bf16 or 8-bit g64; a 4-bit router is not supported)",
+                    d->router_kind);
+    if (d->router_w == nullptr || (d->router_kind == IQ_ROUTER_Q8 && (!d->router_scales || !d->router_biases)))
+        return fail(ctx, kErrInvalidArg, "moe: router tensors missing");
+    const int32_t fg = format_of(&d->gate), fu = format_of(&d->up), fd = format_of(&d->down);
+    if (fg < 0 || fg != fu || fg != fd || fg == kFmtAffine8)
+        return fail(ctx, kErrUnsupported, "moe: experts must be all affine 4-bit g64 or all mxfp4");
+    if (d->gate.n != d->d_ff || d->gate.k != d->d_model || d->up.n != d->d_ff || d->up.k != d->d_model ||
+        d->down.n != d->d_model || d->down.k != d->d_ff)
+        return fail(ctx, kErrInvalidArg, "moe: expert tensor shapes do not match d_model/d_ff");
+    if (d->expert_lo < 0 || d->expert_count < 1 || d->expert_lo + d->expert_count > d->experts ||
+        d->gate.experts != d->expert_count || d->up.experts != d->expert_count || d->down.experts != d->expert_count)
+        return fail(ctx, kErrInvalidArg, "moe: expert range [%d, %d) vs %d stacked experts", d->expert_lo,
+                    d->expert_lo + d->expert_count, d->gate.experts);
+    if (!d->gate.w || !d->up.w || !d->down.w || !d->gate.scales || !d->up.scales || !d->down.scales)
+        return fail(ctx, kErrInvalidArg, "moe: expert tensors missing");
+    if (fg != kFmtMxfp4 && (!d->gate.biases || !d->up.biases || !d->down.biases))
+        return fail(ctx, kErrInvalidArg, "moe: affine experts without biases");
+    if ((d->gate_bias != nullptr) != (d->up_bias != nullptr))
+        return fail(ctx, kErrInvalidArg, "moe: gate and up expert biases go together");
+    iq_moe* l = new (std::nothrow) iq_moe();
+    if (l == nullptr) return kErrCuda;
+    l->ctx = ctx;
+    l->d = *d;
+    l->fmt = fg;
+    l->ld = round_up(d->experts, 64);
+    *out = l;
+    return kOk;
+}
+
+extern "C" void iq_moe_destroy(iq_moe* l) { delete l; }
+
+extern "C" int32_t iq_moe_workspace_bytes(const iq_moe* l, int32_t max_tokens, size_t* bytes) {
+    if (l == nullptr || bytes == nullptr || max_tokens < 1) return kErrInvalidArg;
+    *bytes = carve(l, nullptr, max_tokens).bytes;
+    return kOk;
+}
+
+extern "C" int32_t iq_moe_get_views(const iq_moe* l, void* workspace, int32_t tokens, iq_moe_views* v) {
+    if (l == nullptr || workspace == nullptr || v == nullptr || tokens < 1) return kErrInvalidArg;
+    MoeWs w = carve(l, workspace, tokens);
+    v->logits = w.logits; v->ld = l->ld;
+    v->inds = l->ext_inds ? const_cast<uint32_t*>(l->ext_inds) : w.inds;
+    v->wts = l->ext_wts ? const_cast<float*>(l->ext_wts) : w.wts;
+    v->offsets = w.offsets; v->row_map = w.row_map; v->pos = w.pos;
+    v->h = w.h; v->yd = w.yd;
+    return kOk;
+}
+
+extern "C" int32_t iq_moe_set_external_routing(iq_moe* l, const uint32_t* inds, const float* wts) {
+    if (l == nullptr || ((inds == nullptr) != (wts == nullptr))) return kErrInvalidArg;
+    l->ext_inds = inds;
+    l->ext_wts = wts;
+    return kOk;
+}
+
+extern "C" int32_t iq_moe_route(iq_moe* l, void* stream, const float* logits, int32_t ld, int32_t tokens, uint32_t* inds,
+                                float* wts) {
+    if (l == nullptr) return kErrInvalidArg;
+    if (logits == nullptr || inds == nullptr || wts == nullptr || tokens < 1 || ld < l->d.experts)
+        return fail(l->ctx, kErrInvalidArg, "moe_route: arguments");
+    return launch_route(l, reinterpret_cast<cudaStream_t>(stream), logits, ld, tokens, inds, wts);
+}
+
+extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_t x_dtype, int64_t ldx, void* out,
+                                  int32_t out_dtype, int64_t ldo, int32_t tokens, uint32_t flags, uint32_t pieces,
+                                  void* workspace, size_t workspace_bytes) {
+    if (l == nullptr) return kErrInvalidArg;
+    iq_ctx* ctx = l->ctx;
+    const iq_moe_desc& d = l->d;
+    if (tokens < 1) return fail(ctx, kErrInvalidArg, "moe: tokens = %d", tokens);
+    if (x_dtype < 0 || x_dtype > 2 || out_dtype < 0 || out_dtype > 2) return fail(ctx, kErrInvalidArg, "moe: dtype");
+    if ((pieces & (IQ_PIECE_ROUTER | IQ_PIECE_GATEUP)) &&
+        (x == nullptr || ldx < d.d_model || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0))
+        return fail(ctx, kErrInvalidArg, "moe: x must be 16-byte aligned with ldx >= d_model and ldx %% 8 == 0");
+    if ((pieces & IQ_PIECE_COMBINE) && (out == nullptr || ldo < d.d_model || ldo % 4 != 0))
+        return fail(ctx, kErrInvalidArg, "moe: out / ldo");
+    MoeWs w = carve(l, workspace, tokens);
+    if (workspace == nullptr || workspace_bytes < w.bytes)
+        return fail(ctx, kErrWorkspace, "moe: workspace %zu < %zu", workspace_bytes, w.bytes);
+    cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+    const int P = tokens * d.top_k;
+    const uint32_t* inds = l->ext_inds ? l->ext_inds : w.inds;
+    const float* wts = l->ext_wts ? l->ext_wts : w.wts;
+    int32_t st;
+
+    if ((pieces & IQ_PIECE_ROUTER) && l->ext_inds == nullptr) {
+        const int ee = d.experts < 256 ? d.experts : 256;
+        const size_t smem = (size_t)kRouterTT * d.d_model * 8 + (size_t)(256 / ee) * kRouterTT * ee * 8;
+        if (smem > (size_t)kRouterSmemMax) return fail(ctx, kErrUnsupported, "moe: d_model = %d is too wide for the router kernel", d.d_model);
+        const int grid = (tokens + kRouterTT - 1) / kRouterTT;
+        if (d.router_kind == IQ_ROUTER_BF16)
+            router_logits_kernel<0><<<grid, 256, smem, cs>>>(x, x_dtype, ldx, d.router_w, nullptr, nullptr, w.logits,
+                                                              tokens, d.experts, d.d_model, l->ld);
+        else
+            router_logits_kernel<1><<<grid, 256, smem, cs>>>(x, x_dtype, ldx, d.router_w, d.router_scales,
+                                                              d.router_biases, w.logits, tokens, d.experts, d.d_model,
+                                                              l->ld);
+        st = check_cuda(ctx, cudaGetLastError(), "router_logits launch");
+        if (st != kOk) return st;
+    }
+    if ((pieces & IQ_PIECE_ROUTE) && l->ext_inds == nullptr) {
+        st = launch_route(l, cs, w.logits, l->ld, tokens, w.inds, w.wts);
+        if (st != kOk) return st;
+    }
+    const int bm = decode_tile_rows(l, tokens);
+    if (pieces & IQ_PIECE_GROUP) {
+        GroupParams gp;
+        gp.inds = inds; gp.counts = w.counts; gp.offsets = w.offsets; gp.row_map = w.row_map; gp.pos = w.pos;
+        gp.tiles_a = w.tiles_a; gp.tiles_b = w.tiles_b; gp.ntiles = w.ntiles;
+        gp.P = P; gp.E = d.experts; gp.bm_a = bm; gp.bm_b = kPrefillTileRows;
+        gp.e_lo = d.expert_lo; gp.e_hi = d.expert_lo + d.expert_count;
+        moe_count_kernel<<<d.experts, 256, 0, cs>>>(gp);
+        moe_scatter_kernel<<<d.experts, 256, 0, cs>>>(gp);
+        st = check_cuda(ctx, cudaGetLastError(), "moe_group launch");
+        if (st != kOk) return st;
+    }
+    const int64_t max_tiles64 = (int64_t)d.expert_count + P / bm;
+    const int max_tiles = (int)(max_tiles64 < P ? max_tiles64 : P);
+    if (max_tiles > 65535) return fail(ctx, kErrInvalidArg, "moe: %d tokens give too many tiles for one launch", tokens);
+    // expert e's weights live at local slot e - expert_lo: fold the offset into the base pointers
+    const int64_t lo = d.expert_lo;
+    if (pieces & IQ_PIECE_GATEUP) {
+        GqmvCall c;
+        c.mode = kModeGateUp;
+        c.fmt = l->fmt;
+        c.w_estride = (int64_t)d.d_ff * (d.d_model / 8);
+        c.s_estride = (int64_t)d.d_ff * (d.d_model / d.gate.group);
+        const size_t sb = l->fmt == kFmtMxfp4 ? 1 : 2;
+        c.w[0] = static_cast<const uint32_t*>(d.gate.w) - lo * c.w_estride;
+        c.w[1] = static_cast<const uint32_t*>(d.up.w) - lo * c.w_estride;
+        c.s[0] = static_cast<const char*>(d.gate.scales) - lo * c.s_estride * (int64_t)sb;
+        c.s[1] = static_cast<const char*>(d.up.scales) - lo * c.s_estride * (int64_t)sb;
+        if (d.gate.biases) {
+            c.b[0] = static_cast<const char*>(d.gate.biases) - lo * c.s_estride * 2;
+            c.b[1] = static_cast<const char*>(d.up.biases) - lo * c.s_estride * 2;
+        }
+        c.N = d.d_ff; c.K = d.d_model;
+        c.x = x; c.x_dtype = x_dtype; c.ldx = ldx;
+        c.row_map = w.row_map; c.topk = d.top_k;
+        c.tiles = w.tiles_a; c.ntiles = w.ntiles; c.grid_tiles = max_tiles;
+        c.rows = 0; c.max_rows = bm;
+        c.y = w.h; c.y_dtype = kF16; c.ldy = d.d_ff;
+        if (d.gate_bias) {
+            c.ebias[0] = d.gate_bias - lo * d.d_ff;
+            c.ebias[1] = d.up_bias - lo * d.d_ff;
+        }
+        c.limit = d.act == IQ_ACT_SWIGLU_OAI ? d.act_limit : 0.f;
+        st = launch_gqmv(ctx, cs, c);
+        if (st != kOk) return st;
+    }
+    if (pieces & IQ_PIECE_DOWN) {
+        GqmvCall c;
+        c.mode = kModeDown;
+        c.fmt = l->fmt;
+        c.w_estride = (int64_t)d.d_model * (d.d_ff / 8);
+        c.s_estride = (int64_t)d.d_model * (d.d_ff / d.down.group);
+        const size_t sb = l->fmt == kFmtMxfp4 ? 1 : 2;
+        c.w[0] = static_cast<const uint32_t*>(d.down.w) - lo * c.w_estride;
+        c.s[0] = static_cast<const char*>(d.down.scales) - lo * c.s_estride * (int64_t)sb;
+        if (d.down.biases) c.b[0] = static_cast<const char*>(d.down.biases) - lo * c.s_estride * 2;
+        c.N = d.d_model; c.K = d.d_ff;
+        c.x = w.h; c.x_dtype = kF16; c.ldx = d.d_ff;
+        c.tiles = w.tiles_a; c.ntiles = w.ntiles; c.grid_tiles = max_tiles;
+        c.rows = 0; c.max_rows = bm;
+        c.y = w.yd; c.y_dtype = kF32; c.ldy = d.d_model;
+        if (d.down_bias) c.ebias[0] = d.down_bias - lo * d.d_model;
+        st = launch_gqmv(ctx, cs, c);
+        if (st != kOk) return st;
+    }
+    if (pieces & IQ_PIECE_COMBINE) {
+        CombineParams cp;
+        cp.yd = w.yd; cp.pos = w.pos; cp.wts = wts;
+        cp.out = out; cp.out_dtype = out_dtype; cp.ldo = ldo;
+        cp.T = tokens; cp.D = d.d_model; cp.topk = d.top_k;
+        cp.accumulate = (flags & IQ_FLAG_ACCUMULATE) ? 1 : 0;
+        moe_combine_kernel<<<tokens, 256, 0, cs>>>(cp);
+        st = check_cuda(ctx, cudaGetLastError(), "moe_combine launch");
+        if (st != kOk) return st;
+    }
+    return kOk;
+}

@@ -1,0 +1,352 @@
+// MoE routing, token->expert permutation and combine kernels.
+//
+// Replaces, on sm_100a, the reference's router/group/combine kernels:
+//   router logits   MoE.swift:359-361 (router qmv) and MoEPrefill.swift:176-186 (router qmm)
+//   route_topk      Shaders/verify.metal:181-260 (decode) and Shaders/qmm_nax_moe.metal:26-126 (prefill)
+//   count/scatter   Shaders/qmm_nax_moe.metal:139-217 (moe_group) and the union build of Shaders/verify.metal:282-318
+//   combine         Shaders/qmm_nax_moe.metal:371-396, Shaders/yy_model.metal:129-149
+#pragma once
+
+#include "common.cuh"
+#include "gqmv.cuh"
+
+namespace iq {
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Router logits with a float64 accumulator: logits[t, e] = fp32( sum_k x[t,k] * w[e,k] ).
+//
+// The inputs are bf16/fp16/fp32 values, so each product is exact in float64 and the sum does not depend on the order
+// at fp32 resolution. That is what makes the top-k indices reproducible bit for bit whatever the tiling, the batch
+// size or the number of GPUs. Columns E..ld-1 of the output are written as zero (the reference pads the router to a
+// multiple of 64 rows, MoE.swift:258-273).
+//
+// Block: TT tokens (x staged in shared memory as doubles), thread = (expert, k-slice).
+constexpr int kRouterTT = 4;
+
+template <int WFMT>  // 0: bf16 dense router; 1: 8-bit affine g64 router
+__global__ void __launch_bounds__(256) router_logits_kernel(const void* __restrict__ x, int32_t x_dtype, int64_t ldx,
+                                                            const void* __restrict__ wr, const void* __restrict__ ws,
+                                                            const void* __restrict__ wb, float* __restrict__ logits,
+                                                            int T, int E, int D, int ld) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    double* xs = reinterpret_cast<double*>(smem);                      // [TT][D]
+    double* part = xs + (size_t)kRouterTT * D;                         // [slices][TT][ee]
+    const int tid = threadIdx.x;
+    const int t0 = blockIdx.x * kRouterTT;
+    const int nt = min(kRouterTT, T - t0);
+    const int ee = min(E, 256);                 // experts handled per pass
+    const int slices = 256 / ee;                // k-slices per expert
+    for (int i = tid; i < kRouterTT * D / 8; i += 256) {
+        const int tt = i / (D / 8), ku = i % (D / 8);
+        float v[8];
+        if (tt < nt) load_x8(x, x_dtype, (size_t)(t0 + tt) * ldx + ku * 8, v);
+        else {
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; e++) xs[(size_t)tt * D + ku * 8 + e] = (double)v[e];
+    }
+    __syncthreads();
+    const int el = tid % ee, sl = tid / ee;
+    const int units = D / 8;                                  // 8-input units per row
+    const int upw = (units + slices - 1) / slices;            // units per slice
+    for (int e0 = 0; e0 < E; e0 += ee) {
+        const int e = e0 + el;
+        double acc[kRouterTT];
+#pragma unroll
+        for (int tt = 0; tt < kRouterTT; tt++) acc[tt] = 0.0;
+        if (e < E && sl < slices) {
+            for (int u = sl * upw; u < min(units, (sl + 1) * upw); u++) {
+                double w[8];
+                if (WFMT == 0) {
+                    const uint4 r = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(wr) +
+                                                                    (size_t)e * D + u * 8);
+                    const uint32_t q[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        w[2 * j] = (double)__uint_as_float(q[j] << 16);
+                        w[2 * j + 1] = (double)__uint_as_float(q[j] & 0xFFFF0000u);
+                    }
+                } else {
+                    const uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint32_t*>(wr) +
+                                                                    (size_t)e * (D / 4) + u * 2);
+                    const int gi = e * (D / 64) + u / 8;
+                    // the weight value is the fp32 s*q + b of the reference's CPU dequantisation
+                    const float sc = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(ws)[gi]);
+                    const float bi = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(wb)[gi]);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        w[j] = (double)__fadd_rn(__fmul_rn(sc, (float)((r.x >> (8 * j)) & 0xFFu)), bi);
+                        w[4 + j] = (double)__fadd_rn(__fmul_rn(sc, (float)((r.y >> (8 * j)) & 0xFFu)), bi);
+                    }
+                }
+#pragma unroll
+                for (int tt = 0; tt < kRouterTT; tt++) {
+                    const double2* xp = reinterpret_cast<const double2*>(xs + (size_t)tt * D + u * 8);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const double2 xv = xp[j];
+                        acc[tt] = fma(xv.x, w[2 * j], acc[tt]);
+                        acc[tt] = fma(xv.y, w[2 * j + 1], acc[tt]);
+                    }
+                }
+            }
+        }
+        if (slices > 1) {
+            __syncthreads();
+#pragma unroll
+            for (int tt = 0; tt < kRouterTT; tt++) part[((size_t)sl * kRouterTT + tt) * ee + el] = acc[tt];
+            __syncthreads();
+            if (sl == 0) {
+#pragma unroll
+                for (int tt = 0; tt < kRouterTT; tt++) {
+                    double s = 0.0;
+                    for (int k = 0; k < slices; k++) s += part[((size_t)k * kRouterTT + tt) * ee + el];
+                    acc[tt] = s;
+                }
+            }
+        }
+        if (sl == 0 && e < E) {
+#pragma unroll
+            for (int tt = 0; tt < kRouterTT; tt++)
+                if (tt < nt) logits[(size_t)(t0 + tt) * ld + e] = (float)acc[tt];
+        }
+    }
+    for (int i = tid; i < kRouterTT * (ld - E); i += 256) {
+        const int tt = i / (ld - E), c = E + i % (ld - E);
+        if (tt < nt) logits[(size_t)(t0 + tt) * ld + c] = 0.f;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Top-k routing of softmax-family routers. One warp per token. The rule (KernelCaseRouter.swift:57-80 of the
+// reference): add the router bias to the logits, NaN counts as -inf, pick the maximum k times with ties going to the
+// lower index (when everything left is -inf the lowest index not yet taken wins), weights exp(l_k - l_top1) / sum in
+// k order, then x routed scale and x the per-expert scale of the chosen expert.
+struct RouteParams {
+    const float* logits;       // [T, ld]
+    const float* logit_bias;   // [E] or null
+    const float* pes;          // per-expert scale [E] or null
+    uint32_t* inds;            // [T, topk]
+    float* wts;                // [T, topk]
+    int32_t T, E, ld, topk;
+    float scale;
+};
+
+template <int VPL>
+__global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (t >= p.T) return;
+    const float* lr = p.logits + (size_t)t * p.ld;
+    float v[VPL];
+    uint32_t taken = 0;
+#pragma unroll
+    for (int j = 0; j < VPL; j++) {
+        const int e = j * 32 + lane;
+        float f = e < p.E ? lr[e] : -INFINITY;
+        if (e < p.E && p.logit_bias != nullptr) f += p.logit_bias[e];
+        if (f != f) f = -INFINITY;
+        v[j] = f;
+        if (e >= p.E) taken |= 1u << j;
+    }
+    float myv = -INFINITY;
+    uint32_t myi = 0;
+    for (int k = 0; k < p.topk; k++) {
+        float bv = -INFINITY;
+        uint32_t bi = 0xFFFFFFFFu;
+#pragma unroll
+        for (int j = 0; j < VPL; j++) {
+            if (!((taken >> j) & 1u) && (bi == 0xFFFFFFFFu || v[j] > bv)) {
+                bv = v[j];
+                bi = j * 32 + lane;
+            }
+        }
+        // warp maximum over the lanes that still have a candidate, then the lowest index among the equal ones
+        float gv = bv;
+        uint32_t any = bi != 0xFFFFFFFFu;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, gv, o);
+            const uint32_t oa = __shfl_xor_sync(0xffffffffu, any, o);
+            if (oa && (!any || ov > gv)) gv = ov;
+            any |= oa;
+        }
+        uint32_t gi = (bi != 0xFFFFFFFFu && bv == gv) ? bi : 0xFFFFFFFFu;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) gi = min(gi, __shfl_xor_sync(0xffffffffu, gi, o));
+#pragma unroll
+        for (int j = 0; j < VPL; j++)
+            if ((uint32_t)(j * 32 + lane) == gi) taken |= 1u << j;
+        if (lane == k) { myv = gv; myi = gi; }
+    }
+    const float top1 = __shfl_sync(0xffffffffu, myv, 0);
+    const float ex = lane < p.topk ? expf(myv - top1) : 0.f;
+    float sum = 0.f;
+    for (int k = 0; k < p.topk; k++) sum += __shfl_sync(0xffffffffu, ex, k);
+    if (lane < p.topk) {
+        float w = ex / sum * p.scale;
+        if (p.pes != nullptr) w *= p.pes[myi];
+        p.inds[(size_t)t * p.topk + lane] = myi;
+        p.wts[(size_t)t * p.topk + lane] = w;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Token->expert permutation, deterministic: inside an expert the pairs keep ascending pair id.
+// count: one block per expert counts its pairs. scatter: one block per expert places them, writes the tile
+// descriptors for two tile heights and, in the last block, the totals.
+struct GroupParams {
+    const uint32_t* inds;   // [P] expert of each pair
+    uint32_t* counts;       // [E]
+    uint32_t* offsets;      // [E + 1]
+    uint32_t* row_map;      // [P] sorted position -> pair
+    uint32_t* pos;          // [P] pair -> sorted position
+    Tile* tiles_a;          // tile height bm_a
+    Tile* tiles_b;          // tile height bm_b
+    uint32_t* ntiles;       // [2]
+    int32_t P, E, bm_a, bm_b;
+    int32_t e_lo, e_hi;     // experts owned here (expert parallel); tiles are emitted only for these
+};
+
+__global__ void __launch_bounds__(256) moe_count_kernel(const GroupParams p) {
+    __shared__ uint32_t wsum[8];
+    const uint32_t e = blockIdx.x;
+    uint32_t c = 0;
+    for (int i = threadIdx.x; i < p.P; i += 256) c += p.inds[i] == e;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t s = 0;
+        for (int i = 0; i < 8; i++) s += wsum[i];
+        p.counts[e] = s;
+    }
+}
+
+__global__ void __launch_bounds__(256) moe_scatter_kernel(const GroupParams p) {
+    __shared__ uint32_t sh[3][8];
+    __shared__ uint32_t base[4];
+    const uint32_t e = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // exclusive prefixes over the experts before this one: pairs, tiles of height a, tiles of height b
+    uint32_t c0 = 0, ta = 0, tb = 0;
+    for (int i = tid; i < (int)e; i += 256) {
+        const uint32_t c = p.counts[i];
+        c0 += c;
+        if (i >= p.e_lo && i < p.e_hi) {
+            ta += (c + p.bm_a - 1) / p.bm_a;
+            tb += (c + p.bm_b - 1) / p.bm_b;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        c0 += __shfl_xor_sync(0xffffffffu, c0, o);
+        ta += __shfl_xor_sync(0xffffffffu, ta, o);
+        tb += __shfl_xor_sync(0xffffffffu, tb, o);
+    }
+    if (lane == 0) { sh[0][warp] = c0; sh[1][warp] = ta; sh[2][warp] = tb; }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t a = 0, b = 0, c = 0;
+        for (int i = 0; i < 8; i++) { a += sh[0][i]; b += sh[1][i]; c += sh[2][i]; }
+        base[0] = a; base[1] = b; base[2] = c;
+    }
+    __syncthreads();
+    const uint32_t off = base[0], tile_a0 = base[1], tile_b0 = base[2];
+    const uint32_t cnt = p.counts[e];
+    if (tid == 0) {
+        p.offsets[e] = off;
+        if ((int)e == p.E - 1) {
+            p.offsets[p.E] = off + cnt;
+            const bool own = (int)e >= p.e_lo && (int)e < p.e_hi;
+            p.ntiles[0] = tile_a0 + (own ? (cnt + p.bm_a - 1) / p.bm_a : 0);
+            p.ntiles[1] = tile_b0 + (own ? (cnt + p.bm_b - 1) / p.bm_b : 0);
+        }
+    }
+    if ((int)e >= p.e_lo && (int)e < p.e_hi) {
+        for (uint32_t j = tid; j * p.bm_a < cnt; j += 256)
+            p.tiles_a[tile_a0 + j] = Tile{e, off + j * p.bm_a, min((uint32_t)p.bm_a, cnt - j * p.bm_a), 0};
+        for (uint32_t j = tid; j * p.bm_b < cnt; j += 256)
+            p.tiles_b[tile_b0 + j] = Tile{e, off + j * p.bm_b, min((uint32_t)p.bm_b, cnt - j * p.bm_b), 0};
+    }
+    // ordered placement: walk the pairs 256 at a time, rank the matches with a block-wide prefix
+    uint32_t placed = 0;
+    for (int i0 = 0; i0 < p.P; i0 += 256) {
+        const int i = i0 + tid;
+        const bool hit = i < p.P && p.inds[i] == e;
+        const uint32_t bal = __ballot_sync(0xffffffffu, hit);
+        __syncthreads();  // sh[0] reuse
+        if (lane == 0) sh[0][warp] = __popc(bal);
+        __syncthreads();
+        uint32_t before = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const uint32_t c = sh[0][w];
+            if (w < warp) before += c;
+            total += c;
+        }
+        if (hit) {
+            const uint32_t r = off + placed + before + __popc(bal & ((1u << lane) - 1u));
+            p.row_map[r] = (uint32_t)i;
+            p.pos[i] = r;
+        }
+        placed += total;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Combine: out[t, :] (+)= sum_k wts[t, k] * Yd[pos[t*topk + k], :] in router rank order k = 0..topk-1, fp32
+// (Shaders/qmm_nax_moe.metal:371-396 of the reference). One block per token.
+struct CombineParams {
+    const float* yd;        // [P, D] expert outputs at sorted positions
+    const uint32_t* pos;    // [P]
+    const float* wts;       // [T, topk]
+    void* out;              // [T, ldo]
+    int32_t out_dtype;
+    int64_t ldo;
+    int32_t T, D, topk, accumulate;
+};
+
+__global__ void __launch_bounds__(256) moe_combine_kernel(const CombineParams p) {
+    const int t = blockIdx.x;
+    __shared__ uint32_t spos[32];
+    __shared__ float sw[32];
+    if (threadIdx.x < p.topk) {
+        spos[threadIdx.x] = p.pos[(size_t)t * p.topk + threadIdx.x];
+        sw[threadIdx.x] = p.wts[(size_t)t * p.topk + threadIdx.x];
+    }
+    __syncthreads();
+    for (int d = threadIdx.x * 4; d < p.D; d += 1024) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < p.topk; k++) {
+            const float4 y = *reinterpret_cast<const float4*>(p.yd + (size_t)spos[k] * p.D + d);
+            const float w = sw[k];
+            a.x = fmaf(w, y.x, a.x); a.y = fmaf(w, y.y, a.y); a.z = fmaf(w, y.z, a.z); a.w = fmaf(w, y.w, a.w);
+        }
+        const size_t o = (size_t)t * p.ldo + d;
+        if (p.out_dtype == kF32) {
+            float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
+            if (p.accumulate) {
+                const float4 c = *op;
+                a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
+            }
+            *op = a;
+        } else if (p.out_dtype == kBF16) {
+            uint16_t* op = reinterpret_cast<uint16_t*>(p.out) + o;
+            float r[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                op[j] = (uint16_t)f32_to_bf16_bits(p.accumulate ? bf16_bits_to_f32(op[j]) + r[j] : r[j]);
+        } else {
+            __half* op = reinterpret_cast<__half*>(p.out) + o;
+            float r[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) op[j] = __float2half_rn(p.accumulate ? __half2float(op[j]) + r[j] : r[j]);
+        }
+    }
+}
+
+}  // namespace iq

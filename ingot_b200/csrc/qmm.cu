@@ -1,0 +1,191 @@
+// Host side of the tcgen05 GEMM: tensor maps, kernel selection, the iq_qmm entry point.
+#include "internal.h"
+#include "qmm_tc.cuh"
+
+namespace iq {
+
+namespace {
+
+typedef void (*QmmKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const QmmParams);
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct KernelEntry {
+    int32_t fmt;
+    int bn;
+    int epi;
+    QmmKernel fn;
+    int smem;
+};
+
+template <int FMT, int BN, int EPI>
+KernelEntry entry() {
+    return KernelEntry{FMT, BN, EPI, qmm_tc_kernel<FMT, BN, EPI>, QmmSmem<FMT, BN, EPI>::TOTAL};
+}
+
+const KernelEntry* table(int* n) {
+    static const KernelEntry t[] = {
+        entry<kFmtAffine4, 256, kEpiStore>(), entry<kFmtAffine4, 128, kEpiStore>(),
+        entry<kFmtAffine8, 256, kEpiStore>(), entry<kFmtAffine8, 128, kEpiStore>(),
+        entry<kFmtMxfp4, 256, kEpiStore>(),   entry<kFmtMxfp4, 128, kEpiStore>(),
+        entry<kFmtAffine4, 128, kEpiGateUp>(), entry<kFmtMxfp4, 128, kEpiGateUp>(),
+    };
+    *n = (int)(sizeof(t) / sizeof(t[0]));
+    return t;
+}
+
+const KernelEntry* find(int32_t fmt, int bn, int epi) {
+    int n;
+    const KernelEntry* t = table(&n);
+    for (int i = 0; i < n; i++)
+        if (t[i].fmt == fmt && t[i].bn == bn && t[i].epi == epi) return &t[i];
+    return nullptr;
+}
+
+}  // namespace
+
+int32_t qmm_init(iq_ctx* ctx) {
+    int n;
+    const KernelEntry* t = table(&n);
+    for (int i = 0; i < n; i++) {
+        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(t[i].fn),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, t[i].smem);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmm)");
+    }
+    return kOk;
+}
+
+// 2-D tensor map over a row-major matrix: `inner` elements per row, `rows` rows, `row_bytes` between rows.
+int32_t make_map_2d(iq_ctx* ctx, CUtensorMap* map, const void* base, bool f16, uint64_t inner, uint64_t rows,
+                    uint64_t row_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128) {
+    if (ctx->encode_tiled == nullptr) return fail(ctx, kErrCuda, "cuTensorMapEncodeTiled is not available");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || row_bytes % 16 != 0)
+        return fail(ctx, kErrInvalidArg, "qmm: TMA needs a 16-byte aligned base and row pitch");
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
+        map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ctx, kErrCuda, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return kOk;
+}
+
+// One launch of the tensor-core GEMM. x16: fp16 activations [x_rows, ldx]; w[i]: stacked [experts * N, K] codes.
+struct QmmCall {
+    int32_t fmt = 0;
+    int epi = kEpiStore;
+    int bn = 256;
+    const void* x16 = nullptr;
+    int64_t ldx = 0;
+    int64_t x_rows = 0;
+    const void* w[2] = {nullptr, nullptr};
+    const void* s[2] = {nullptr, nullptr};
+    const void* b[2] = {nullptr, nullptr};
+    int32_t experts = 1;
+    int32_t N = 0, K = 0, M = 0;
+    const Tile* tiles = nullptr;
+    const uint32_t* ntiles = nullptr;
+    void* y = nullptr;
+    int32_t y_dtype = 0;
+    int64_t ldy = 0;
+    int32_t accumulate = 0;
+    const float* ebias[2] = {nullptr, nullptr};
+    float limit = 0.f;
+};
+
+int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
+    const KernelEntry* ke = find(c.fmt, c.bn, c.epi);
+    if (ke == nullptr) return fail(ctx, kErrNoKernel, "qmm: no kernel for format %d, tile %d, epilogue %d", c.fmt, c.bn, c.epi);
+    const int pack_row = c.fmt == kFmtAffine8 ? 64 : 32;
+    const uint64_t row_bytes = (uint64_t)c.K / kBK * pack_row;
+    CUtensorMap mx, mw0, mw1;
+    int32_t r = make_map_2d(ctx, &mx, c.x16, true, (uint64_t)c.K, (uint64_t)c.x_rows, (uint64_t)c.ldx * 2, kBK, c.bn, true);
+    if (r != kOk) return r;
+    r = make_map_2d(ctx, &mw0, c.w[0], false, row_bytes, (uint64_t)c.experts * c.N, row_bytes, pack_row, kWRows, false);
+    if (r != kOk) return r;
+    r = make_map_2d(ctx, &mw1, c.w[1] ? c.w[1] : c.w[0], false, row_bytes, (uint64_t)c.experts * c.N, row_bytes, pack_row,
+                    kWRows, false);
+    if (r != kOk) return r;
+    QmmParams p;
+    for (int i = 0; i < 2; i++) {
+        p.s[i] = c.s[i] ? c.s[i] : c.s[0];
+        p.b[i] = c.b[i] ? c.b[i] : c.b[0];
+        p.ebias[i] = c.ebias[i];
+    }
+    p.s_estride = 0;
+    p.N = c.N; p.K = c.K; p.M = c.M;
+    p.tiles = c.tiles; p.ntiles = c.ntiles;
+    p.y = c.y; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
+    p.limit = c.limit;
+    p.status = ctx->d_status;
+    int grid = ctx->sms;
+    if (c.tiles == nullptr) {
+        const int work = ((c.M + c.bn - 1) / c.bn) * ((c.N + kWRows - 1) / kWRows);
+        if (work < grid) grid = work;
+    }
+    ke->fn<<<grid, kQmmThreads, ke->smem, st>>>(mx, mw0, mw1, p);
+    return check_cuda(ctx, cudaGetLastError(), "qmm launch");
+}
+
+}  // namespace iq
+
+using namespace iq;
+
+extern "C" int32_t iq_qmm_workspace_bytes(iq_ctx* ctx, const iq_qlinear* m, int32_t rows, int32_t x_dtype, size_t* bytes) {
+    if (ctx == nullptr || m == nullptr || bytes == nullptr || rows < 1) return kErrInvalidArg;
+    *bytes = x_dtype == IQ_F16 ? 0 : round_up_sz((size_t)rows * m->k * 2, 256);
+    return kOk;
+}
+
+extern "C" int32_t iq_qmm(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx, const iq_qlinear* m,
+                          void* y, int32_t y_dtype, int64_t ldy, int32_t rows, uint32_t flags, void* workspace,
+                          size_t workspace_bytes) {
+    if (ctx == nullptr) return kErrInvalidArg;
+    if (x == nullptr || y == nullptr || m == nullptr || m->w == nullptr || m->scales == nullptr)
+        return fail(ctx, kErrInvalidArg, "qmm: null pointer");
+    const int32_t fmt = format_of(m);
+    if (fmt < 0)
+        return fail(ctx, kErrUnsupported, "qmm: %d-bit group %d mode %d has no kernel (affine 4/8-bit g64, mxfp4 g32)",
+                    m->bits, m->group, m->mode);
+    if (fmt != kFmtMxfp4 && m->biases == nullptr) return fail(ctx, kErrInvalidArg, "qmm: affine layer without biases");
+    // the reference's preconditions (Layers/Linear.swift:695)
+    if (rows < 64 || rows % 64 != 0) return fail(ctx, kErrInvalidArg, "qmm: rows = %d must be a multiple of 64", rows);
+    if (m->n % 64 != 0 || m->k % 64 != 0 || m->n <= 0 || m->k <= 0)
+        return fail(ctx, kErrInvalidArg, "qmm: n = %d and k = %d must be multiples of 64", m->n, m->k);
+    if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return fail(ctx, kErrInvalidArg, "qmm: dtype");
+    if (ldx < m->k || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0 || ldy < m->n)
+        return fail(ctx, kErrInvalidArg, "qmm: x must be 16-byte aligned with ldx >= k, ldx %% 8 == 0; ldy >= n");
+    cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+    const void* x16 = x;
+    int64_t ld16 = ldx;
+    if (x_dtype != IQ_F16) {
+        size_t need = 0;
+        iq_qmm_workspace_bytes(ctx, m, rows, x_dtype, &need);
+        if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+            return fail(ctx, kErrWorkspace, "qmm: workspace %zu < %zu (256-byte aligned)", workspace_bytes, need);
+        const size_t units = (size_t)rows * m->k / 8;
+        convert_x_f16_kernel<<<(unsigned)((units + 255) / 256), 256, 0, cs>>>(x, x_dtype, ldx, static_cast<__half*>(workspace),
+                                                                             rows, m->k);
+        int32_t st = check_cuda(ctx, cudaGetLastError(), "convert_x launch");
+        if (st != kOk) return st;
+        x16 = workspace;
+        ld16 = m->k;
+    }
+    QmmCall c;
+    c.fmt = fmt;
+    c.epi = kEpiStore;
+    c.bn = rows >= 256 ? 256 : 128;
+    c.x16 = x16; c.ldx = ld16; c.x_rows = rows;
+    c.w[0] = m->w; c.s[0] = m->scales; c.b[0] = m->biases;
+    c.experts = 1;
+    c.N = m->n; c.K = m->k; c.M = rows;
+    c.y = y; c.y_dtype = y_dtype; c.ldy = ldy;
+    c.accumulate = (flags & IQ_FLAG_ACCUMULATE) ? 1 : 0;
+    return launch_qmm(ctx, cs, c);
+}

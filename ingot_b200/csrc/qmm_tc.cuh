@@ -1,0 +1,464 @@
+// Prefill quantized GEMM on the 5th-generation tensor cores (tcgen05 + tensor memory), dense and grouped (MoE).
+//
+//   D[128 weight rows, BN tokens] += Wd[128, 64] * X[BN, 64]^T      per K step of 64 inputs
+//
+// The weight tile is the M = 128 side of the MMA and the tokens are its N side (16..256 in steps of 16), so a ragged
+// number of tokens per expert costs no padding rows and every weight byte is dequantised once per token tile.
+// Warp roles inside one persistent CTA (448 threads):
+//   warp 0      TMA producer: per stage, the fp16 activation tile X[BN, 64] (128-byte swizzle, the layout the MMA
+//               reads) and the packed codes of the weight tile(s) ([128, 64 inputs] as raw bytes)
+//   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits stages and accumulators
+//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator, apply bias / activation, store (coalesced along the
+//               weight-row dimension, which is the fast dimension of Y)
+//   warps 6-13  dequantisers: packed codes (shared memory) -> fp16 w = fma(q, s, b) -> swizzled K-major tile
+// Stages are recycled by tcgen05.commit on an mbarrier; two accumulators in tensor memory let the epilogue of one
+// tile overlap the main loop of the next. Every wait is bounded: on a timeout the kernel writes a status word, all
+// roles drain and tensor memory is released.
+//
+// Replaces qmm_t_nax3* (Shaders/qmm_nax_v3.metal:107-256) and, with a tile list, moe_gateup_swiglu2* / moe_down2*
+// (Shaders/qmm_nax_moe.metal:442-717) of the reference.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gqmv.cuh"
+
+namespace iq {
+
+constexpr int kQmmThreads = 448;
+constexpr int kBK = 64;              // inputs per K step (= one affine group, two mxfp4 groups)
+constexpr int kWRows = 128;          // weight rows per tile (MMA M)
+constexpr uint64_t kWaitCycles = 4000000000ull;  // about two seconds
+
+enum : int { kEpiStore = 0, kEpiGateUp = 1 };
+
+struct QmmParams {
+    // scales / biases are read straight from global memory by the dequantisers
+    const void* s[2];
+    const void* b[2];
+    int64_t s_estride;       // scale elements between experts
+    int32_t N, K;            // weight rows per expert, inputs
+    int32_t M;               // token rows (dense) / total sorted rows (grouped)
+    // work list: null = dense tiling over (N / 128) x (M / BN)
+    const Tile* tiles;
+    const uint32_t* ntiles;
+    // output
+    void* y;
+    int32_t y_dtype;
+    int64_t ldy;
+    int32_t accumulate;
+    const float* ebias[2];   // fp32 [E, N] or null
+    float limit;
+    int32_t* status;         // device status word (0 = ok)
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false when the wait gave up or another role already did.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if ((unsigned long long)(clock64() - t0) > kWaitCycles) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+        "%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes
+// apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;              // leading byte offset (unused with a swizzled K-major tile)
+    d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset
+    d |= (uint64_t)1 << 46;              // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;              // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor, kind::f16: D = f32, A = B = f16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kWRows >> 4) << 24);
+}
+
+// ---- dequantisation of 32 consecutive inputs of one weight row into four 16-byte chunks --------------------------
+template <int FMT>
+__device__ __forceinline__ void dequant32(const unsigned char* packed_row_half, uint32_t sc_raw, uint32_t bi_raw,
+                                          uint4 (&out)[4]) {
+    if (FMT == kFmtAffine4) {
+        const uint4 v = *reinterpret_cast<const uint4*>(packed_row_half);
+        const float s = bf16_bits_to_f32(sc_raw), b = bf16_bits_to_f32(bi_raw);
+        const uint32_t s2 = pack_half2(s, s * 0.0625f), b2 = pack_half2(b, b);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                // byte j of the word holds inputs 2j (low nibble) and 2j + 1: (1024 + q_lo, 1024 + 16 q_hi)
+                const uint32_t t = (__byte_perm(w[i], 0u, 0x4040 + 0x0101 * j) & 0x00F0000Fu) | 0x64006400u;
+                __half2 q = __hsub2(*reinterpret_cast<const __half2*>(&t), __half2half2(__ushort_as_half(0x6400)));
+                __half2 r = __hfma2(q, *reinterpret_cast<const __half2*>(&s2), *reinterpret_cast<const __half2*>(&b2));
+                o[j] = *reinterpret_cast<uint32_t*>(&r);
+            }
+            out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    } else if (FMT == kFmtAffine8) {
+        const uint4 v0 = *reinterpret_cast<const uint4*>(packed_row_half);
+        const uint4 v1 = *reinterpret_cast<const uint4*>(packed_row_half + 16);
+        const float s = bf16_bits_to_f32(sc_raw), b = bf16_bits_to_f32(bi_raw);
+        const uint32_t s2 = pack_half2(s, s), b2 = pack_half2(b, b);
+        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint32_t t = __byte_perm(w[2 * i + (j >> 1)], 0x64646464u, (j & 1) ? 0x4342 : 0x4140);
+                __half2 q = __hsub2(*reinterpret_cast<const __half2*>(&t), __half2half2(__ushort_as_half(0x6400)));
+                __half2 r = __hfma2(q, *reinterpret_cast<const __half2*>(&s2), *reinterpret_cast<const __half2*>(&b2));
+                o[j] = *reinterpret_cast<uint32_t*>(&r);
+            }
+            out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    } else {
+        const uint4 v = *reinterpret_cast<const uint4*>(packed_row_half);
+        const DqConst d = make_dq<kFmtMxfp4>(sc_raw);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint32_t h[4];
+            cvt_e2m1x8(w[i], h);
+            out[i] = make_uint4(hmul2_u32(h[0], d.s2), hmul2_u32(h[1], d.s2), hmul2_u32(h[2], d.s2),
+                                hmul2_u32(h[3], d.s2));
+        }
+    }
+}
+
+template <int FMT, int BN, int EPI>
+struct QmmSmem {
+    static constexpr int NWT = EPI == kEpiGateUp ? 2 : 1;                 // weight tiles per stage
+    static constexpr int PACK_ROW = FMT == kFmtAffine8 ? 64 : 32;         // packed bytes per row per K step
+    static constexpr int X_BYTES = BN * 128;
+    static constexpr int WD_BYTES = kWRows * 128;
+    static constexpr int WP_BYTES = kWRows * PACK_ROW;
+    static constexpr int STAGE_BYTES = X_BYTES + NWT * (WD_BYTES + WP_BYTES);
+    static constexpr int kMaxDyn = 232448 - 1280;                         // opt-in limit minus alignment + barriers
+    static constexpr int STAGES = kMaxDyn / STAGE_BYTES > 6 ? 6 : kMaxDyn / STAGE_BYTES;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int ACC_COLS = NWT * BN;                             // tensor-memory columns per accumulator
+    static_assert(2 * ACC_COLS <= 512, "two accumulators must fit tensor memory");
+    static_assert(STAGES >= 2, "need at least two stages");
+};
+
+template <int FMT, int BN, int EPI>
+__global__ void __launch_bounds__(kQmmThreads, 1)
+    qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w0,
+                  const __grid_constant__ CUtensorMap map_w1, const QmmParams p) {
+    using S = QmmSmem<FMT, BN, EPI>;
+    constexpr int NWT = S::NWT, STAGES = S::STAGES;
+    extern __shared__ unsigned char smem_raw[];
+    // 1024-byte alignment for the swizzled tiles
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+    // barrier slots: full[STAGES], ready[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+    const uint32_t bar_full = smem_u32(bars), bar_ready = bar_full + 8 * STAGES, bar_empty = bar_ready + 8 * STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_ready + 8 * s, 8);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tempty + 8 * a, 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // ---- work list --------------------------------------------------------------------------------------------
+    const int n_tiles_n = (p.N + kWRows - 1) / kWRows;
+    int total_work;
+    int m_tiles = 0;
+    if (p.tiles != nullptr) {
+        total_work = (int)(*p.ntiles) * n_tiles_n;
+    } else {
+        m_tiles = (p.M + BN - 1) / BN;
+        total_work = m_tiles * n_tiles_n;
+    }
+    const int ksteps = p.K / kBK;
+    const int row_groups = p.K / (FMT == kFmtMxfp4 ? 32 : 64);
+
+    // Decodes work item `wi` into (expert, first token row, live token rows, first weight row).
+    auto decode = [&](int wi, uint32_t& expert, int& row0, int& rows, int& n0) {
+        if (p.tiles != nullptr) {
+            const Tile t = p.tiles[wi / n_tiles_n];
+            expert = t.expert; row0 = (int)t.start; rows = (int)t.count;
+            n0 = (wi % n_tiles_n) * kWRows;
+        } else {
+            const int tm = wi % m_tiles;
+            expert = 0; row0 = tm * BN; rows = min(BN, p.M - row0);
+            n0 = (wi / m_tiles) * kWRows;
+        }
+    };
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int wi = blockIdx.x; wi < total_work && ok; wi += gridDim.x) {
+                uint32_t expert; int row0, rows, n0;
+                decode(wi, expert, row0, rows, n0);
+                for (int ks = 0; ks < ksteps; ks++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag))) break;
+                    unsigned char* st = smem + s * S::STAGE_BYTES;
+                    mbar_arrive_expect_tx(bar_full + 8 * s, S::X_BYTES + NWT * S::WP_BYTES);
+                    tma_load_2d(smem_u32(st), &map_x, bar_full + 8 * s, ks * kBK, row0);
+                    const int wrow = (int)expert * p.N + n0;
+                    tma_load_2d(smem_u32(st + S::X_BYTES + NWT * S::WD_BYTES), &map_w0, bar_full + 8 * s,
+                                ks * S::PACK_ROW, wrow);
+                    if (NWT == 2)
+                        tma_load_2d(smem_u32(st + S::X_BYTES + NWT * S::WD_BYTES + S::WP_BYTES), &map_w1,
+                                    bar_full + 8 * s, ks * S::PACK_ROW, wrow);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int wi = blockIdx.x; wi < total_work && ok; wi += gridDim.x, tcount++) {
+                uint32_t expert; int row0, rows, n0;
+                decode(wi, expert, row0, rows, n0);
+                const int nmma = min(BN, (rows + 15) & ~15);
+                const uint32_t idesc = make_idesc(nmma);
+                const int a = tcount & 1;
+                const uint32_t aph = (tcount >> 1) & 1;
+                if (!(ok = mbar_wait(bar_tempty + 8 * a, aph ^ 1, abort_flag))) break;
+                tc_fence_after();
+                const uint32_t tacc = tmem_base + a * S::ACC_COLS;
+                for (int ks = 0; ks < ksteps; ks++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag))) break;
+                    if (!(ok = mbar_wait(bar_ready + 8 * s, ph, abort_flag))) break;
+                    tc_fence_after();
+                    unsigned char* st = smem + s * S::STAGE_BYTES;
+                    const uint64_t bdesc = make_sw128_desc(smem_u32(st));
+#pragma unroll
+                    for (int wt = 0; wt < NWT; wt++) {
+                        const uint64_t adesc = make_sw128_desc(smem_u32(st + S::X_BYTES + wt * S::WD_BYTES));
+#pragma unroll
+                        for (int kk = 0; kk < kBK / 16; kk++)
+                            umma_f16(tacc + wt * BN, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
+                    }
+                    umma_commit(bar_empty + 8 * s);  // the stage is free once these MMAs have read it
+                }
+                if (ok) umma_commit(bar_tfull + 8 * a);
+            }
+        }
+    } else if (warp < 6) {
+        // ================= epilogue =================
+        const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (int wi = blockIdx.x; wi < total_work && ok; wi += gridDim.x, tcount++) {
+            uint32_t expert; int row0, rows, n0;
+            decode(wi, expert, row0, rows, n0);
+            const int a = tcount & 1;
+            const uint32_t aph = (tcount >> 1) & 1;
+            if (!(ok = mbar_wait(bar_tfull + 8 * a, aph, abort_flag))) break;
+            tc_fence_after();
+            const int n = n0 + 32 * q + lane;  // weight row = output feature of this thread
+            const bool n_ok = n < p.N;
+            float bias0 = 0.f, bias1 = 0.f;
+            if (n_ok && p.ebias[0] != nullptr) bias0 = p.ebias[0][(size_t)expert * p.N + n];
+            if (EPI == kEpiGateUp && n_ok && p.ebias[1] != nullptr) bias1 = p.ebias[1][(size_t)expert * p.N + n];
+            const uint32_t tbase = tmem_base + ((uint32_t)(32 * q) << 16) + a * S::ACC_COLS;
+            for (int c0 = 0; c0 < rows; c0 += 32) {
+                uint32_t r0[32], r1[32];
+                tmem_ld32(tbase + c0, r0);
+                if (EPI == kEpiGateUp) tmem_ld32(tbase + BN + c0, r1);
+                tmem_ld_wait();
+                if (!n_ok) continue;
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    if (c0 + j >= rows) break;
+                    float v = __uint_as_float(r0[j]) + bias0;
+                    if (EPI == kEpiGateUp) {
+                        // the reference's prefill kernels round gate and up to half before the activation
+                        // (GU_HALF, Shaders/qmm_nax_moe.metal:491-505)
+                        const float g = __half2float(__float2half_rn(v));
+                        const float u = __half2float(__float2half_rn(__uint_as_float(r1[j]) + bias1));
+                        v = p.limit > 0.f ? glu<kActSwigluOai>(g, u, p.limit) : glu<kActSilu>(g, u, 0.f);
+                    }
+                    const size_t o = (size_t)(row0 + c0 + j) * p.ldy + n;
+                    if (p.y_dtype == kF32) {
+                        float* yp = reinterpret_cast<float*>(p.y) + o;
+                        *yp = p.accumulate ? *yp + v : v;
+                    } else if (p.y_dtype == kF16) {
+                        __half* yp = reinterpret_cast<__half*>(p.y) + o;
+                        *yp = __float2half_rn(p.accumulate ? __half2float(*yp) + v : v);
+                    } else {
+                        uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + o;
+                        *yp = (uint16_t)f32_to_bf16_bits(p.accumulate ? bf16_bits_to_f32(*yp) + v : v);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * a);
+        }
+    } else {
+        // ================= dequantisers (256 threads) =================
+        const int dt = threadIdx.x - 6 * 32;      // 0..255
+        const int row = dt >> 1, half = dt & 1;   // weight row inside the tile, which 32 inputs of the K step
+        const int sw = row & 7;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int wi = blockIdx.x; wi < total_work && ok; wi += gridDim.x) {
+            uint32_t expert; int row0, rows, n0;
+            decode(wi, expert, row0, rows, n0);
+            const bool r_ok = n0 + row < p.N;
+            const size_t srow = ((size_t)expert * p.N + (r_ok ? n0 + row : 0)) * row_groups;
+            for (int ks = 0; ks < ksteps; ks++, it++) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                // scales first: their latency hides behind the barrier waits
+                uint32_t sc[NWT], bi[NWT];
+#pragma unroll
+                for (int wt = 0; wt < NWT; wt++) {
+                    if (FMT == kFmtMxfp4) {
+                        sc[wt] = r_ok ? ldg_nc_u8(reinterpret_cast<const unsigned char*>(p.s[wt]) + srow + 2 * ks + half)
+                                      : 127u;
+                        bi[wt] = 0;
+                    } else {
+                        sc[wt] = r_ok ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.s[wt]) + srow + ks) : 0u;
+                        bi[wt] = r_ok ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.b[wt]) + srow + ks) : 0u;
+                    }
+                }
+                if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag))) break;     // packed codes landed
+                if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag))) break;  // fp16 tile no longer read
+                unsigned char* st = smem + s * S::STAGE_BYTES;
+#pragma unroll
+                for (int wt = 0; wt < NWT; wt++) {
+                    const unsigned char* pk = st + S::X_BYTES + NWT * S::WD_BYTES + wt * S::WP_BYTES +
+                                              row * S::PACK_ROW + half * (S::PACK_ROW / 2);
+                    uint4 o[4];
+                    dequant32<FMT>(pk, sc[wt], bi[wt], o);
+                    unsigned char* wd = st + S::X_BYTES + wt * S::WD_BYTES + (row >> 3) * 1024 + sw * 128;
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        *reinterpret_cast<uint4*>(wd + (((half * 4 + j) ^ sw) << 4)) = o[j];
+                }
+                fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async-proxy reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_ready + 8 * s);
+            }
+        }
+    }
+
+    // ---- teardown ------------------------------------------------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, kErrTimeout);
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// fp32 / bf16 activations -> fp16, row-major [rows, k] contiguous (the MMA's B operand type)
+__global__ void convert_x_f16_kernel(const void* __restrict__ x, int32_t x_dtype, int64_t ldx, __half* __restrict__ out,
+                                     int rows, int k) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= (size_t)rows * k) return;
+    const size_t r = i / k, c = i % k;
+    float v[8];
+    load_x8(x, x_dtype, r * ldx + c, v);
+    uint4 o;
+    o.x = pack_half2(v[0], v[1]); o.y = pack_half2(v[2], v[3]); o.z = pack_half2(v[4], v[5]); o.w = pack_half2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(out + i) = o;
+}
+
+}  // namespace iq

@@ -1,0 +1,153 @@
+"""Host-side mirror of the reference's quantized-linear operators (Sources/Ingot/Layers/Linear.swift, Dense.swift).
+
+`DenseQ` is the device container (three buffers + N, K, bits, group size, Linear.swift:17-33); `VQMV.encode` is the
+decode GEMV launcher (Linear.swift:287-444); `DenseQ.encode_qmm_f32` the prefill GEMM launcher (Linear.swift:688-713);
+`DenseMLP` the gated FFN (Dense.swift:9-96). Where the reference encodes a Metal dispatch onto a command encoder,
+these enqueue CUDA kernels of libingot_qmm.so on a CUDA stream through the C ABI. torch is used for device memory and
+streams only. There is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import capi
+
+_DT = {torch.float32: capi.IQ_F32, torch.float16: capi.IQ_F16, torch.bfloat16: capi.IQ_BF16}
+
+
+def _dtype_id(t: torch.Tensor) -> int:
+    if t.dtype not in _DT:
+        raise TypeError(f"unsupported element type {t.dtype} (float32, float16, bfloat16)")
+    return _DT[t.dtype]
+
+
+def _stream_ptr(stream: Optional[torch.cuda.Stream]) -> int:
+    return (stream or torch.cuda.current_stream()).cuda_stream
+
+
+def _need_cuda(*ts: torch.Tensor):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("tensors must live on a CUDA device: the operators have no CPU path")
+
+
+class DenseQ:
+    """A quantized matrix on the device in MLX layout (Linear.swift:17-33; Loader/Quant.swift:4-12).
+
+    w: int32/uint32 tensor [experts?, N, K*bits/32] holding the packed codes; scales/biases bf16 [.., N, K/group]
+    (affine) or scales uint8 [.., N, K/32] (mxfp4, biases None)."""
+
+    def __init__(self, w: torch.Tensor, scales: torch.Tensor, biases: Optional[torch.Tensor], N: int, K: int, bits: int,
+                 gs: int = 64, mode: str = "affine", experts: int = 1):
+        _need_cuda(w, scales, biases)
+        if mode not in ("affine", "mxfp4"):
+            raise ValueError(f"quantization mode «{mode}» not supported (affine and mxfp4)")
+        if w.dtype not in (torch.int32, torch.uint32):
+            raise TypeError("packed codes must be 32-bit words")
+        words = K * bits // 32
+        if w.numel() != experts * N * words:
+            raise ValueError(f"bits do not add up (packed {tuple(w.shape)}, N {N}, K {K}, bits {bits})")
+        if mode == "mxfp4":
+            if bits != 4 or gs != 32 or scales.dtype != torch.uint8 or biases is not None:
+                raise ValueError("not an MLX mxfp4 layer (4 bits g32, uint8 scales, no biases)")
+        else:
+            if scales.dtype != torch.bfloat16 or biases is None or biases.dtype != torch.bfloat16:
+                raise ValueError("affine scales/biases must be bf16")
+            if biases.numel() != scales.numel():
+                raise ValueError("scales and biases differ in shape")
+        if scales.numel() != experts * N * (K // gs):
+            raise ValueError(f"scales shape {tuple(scales.shape)} does not match N {N}, K {K}, group {gs}")
+        self.w, self.s, self.b = w.contiguous(), scales.contiguous(), None if biases is None else biases.contiguous()
+        self.N, self.K, self.bits, self.gs, self.mode, self.experts = N, K, bits, gs, mode, experts
+
+    def qlinear(self) -> capi.QLinear:
+        return capi.QLinear(self.w.data_ptr(), self.s.data_ptr(), 0 if self.b is None else self.b.data_ptr(), self.N,
+                            self.K, self.bits, self.gs, capi.IQ_MODE_MXFP4 if self.mode == "mxfp4" else capi.IQ_MODE_AFFINE,
+                            self.experts)
+
+    @property
+    def device_index(self) -> int:
+        return self.w.device.index or 0
+
+    def weight_bytes(self) -> int:
+        """Bytes of codes + scales + biases (what one pass over the matrix reads)."""
+        n = self.w.numel() * 4 + self.s.numel() * self.s.element_size()
+        return n + (0 if self.b is None else self.b.numel() * 2)
+
+    # ---- prefill GEMM (Linear.swift:688-713) --------------------------------------------------------------------
+    def qmm_workspace_bytes(self, rows: int, x_dtype: torch.dtype) -> int:
+        ctx = capi.context(self.device_index)
+        n = C.c_size_t()
+        ql = self.qlinear()
+        ctx.check(capi.lib().iq_qmm_workspace_bytes(ctx.handle, C.byref(ql), rows, _DT[x_dtype], C.byref(n)))
+        return n.value
+
+    def encode_qmm_f32(self, x: torch.Tensor, y: torch.Tensor, rows: int, accumulate: bool = False,
+                       workspace: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None):
+        """Y[rows, N] (+)= X[rows, K] · Wᵀ on the tensor cores. y may be float32 (the reference's default), float16
+        (`halfOut`) or bfloat16. rows must be a multiple of 64 (Linear.swift:695)."""
+        _need_cuda(x, y)
+        ctx = capi.context(self.device_index)
+        ql = self.qlinear()
+        ws_ptr, ws_bytes = (0, 0) if workspace is None else (workspace.data_ptr(), workspace.numel() * workspace.element_size())
+        ctx.check(capi.lib().iq_qmm(ctx.handle, _stream_ptr(stream), x.data_ptr(), _dtype_id(x), x.stride(0), C.byref(ql),
+                                    y.data_ptr(), _dtype_id(y), y.stride(0), rows,
+                                    capi.IQ_FLAG_ACCUMULATE if accumulate else 0, ws_ptr, ws_bytes))
+
+
+class VQMV:
+    """Decode GEMV launcher (Linear.swift:287-444)."""
+
+    MAX_ROWS = 16
+
+    @staticmethod
+    def encode(x: torch.Tensor, m: DenseQ, y: torch.Tensor, rows: int, ldx: Optional[int] = None,
+               ldy: Optional[int] = None, accumulate: bool = False, n_prefix: Optional[int] = None,
+               stream: Optional[torch.cuda.Stream] = None):
+        """Y[rows, N] (+)= X[rows, K] · Wᵀ, rows ≤ 16. `ldx`/`ldy` are row strides in elements (default: the tensors'),
+        `n_prefix` computes only the first rows of W (Linear.swift:350-366)."""
+        _need_cuda(x, y)
+        ctx = capi.context(m.device_index)
+        ql = m.qlinear()
+        ctx.check(capi.lib().iq_qmv(ctx.handle, _stream_ptr(stream), x.data_ptr(), _dtype_id(x),
+                                    ldx if ldx is not None else (x.stride(0) if x.dim() > 1 else m.K), C.byref(ql),
+                                    y.data_ptr(), _dtype_id(y),
+                                    ldy if ldy is not None else (y.stride(0) if y.dim() > 1 else m.N), rows,
+                                    capi.IQ_FLAG_ACCUMULATE if accumulate else 0, n_prefix or 0))
+
+
+class DenseMLP:
+    """Dense gated FFN with gate|up concatenated by rows ([2·I, D], gate rows first; Dense.swift:4-6,21-49)."""
+
+    def __init__(self, gate_up: DenseQ, down: DenseQ, act: str = "silu", limit: float = 7.0):
+        if gate_up.N % 2 or gate_up.N // 2 != down.K or gate_up.K != down.N:
+            raise ValueError("gate|up and down do not chain")
+        self.gate_up, self.down = gate_up, down
+        self.act = {"silu": capi.IQ_ACT_SILU, "swiglu_oai": capi.IQ_ACT_SWIGLU_OAI}[act]
+        self.limit = limit
+        self._ws = None
+
+    def _workspace(self, rows: int, x_dtype: torch.dtype) -> torch.Tensor:
+        ctx = capi.context(self.gate_up.device_index)
+        n = C.c_size_t()
+        a, b = self.gate_up.qlinear(), self.down.qlinear()
+        ctx.check(capi.lib().iq_dense_ffn_workspace_bytes(ctx.handle, C.byref(a), C.byref(b), rows, _DT[x_dtype], C.byref(n)))
+        if self._ws is None or self._ws.numel() < n.value:
+            self._ws = torch.empty(max(n.value, 256), dtype=torch.uint8, device=self.gate_up.w.device)
+        return self._ws
+
+    def encode(self, x: torch.Tensor, out: torch.Tensor, rows: int, accumulate: bool = False,
+               stream: Optional[torch.cuda.Stream] = None):
+        """out[rows, D] (+)= down(act(gate x)·up x) (Dense.swift:56-96). rows ≤ 16 runs the GEMV kernels, larger
+        multiples of 64 the GEMM kernels. Scratch is sized on first use and reused."""
+        _need_cuda(x, out)
+        ctx = capi.context(self.gate_up.device_index)
+        ws = self._workspace(rows, x.dtype)
+        a, b = self.gate_up.qlinear(), self.down.qlinear()
+        ctx.check(capi.lib().iq_dense_ffn(ctx.handle, _stream_ptr(stream), x.data_ptr(), _dtype_id(x), x.stride(0),
+                                          C.byref(a), C.byref(b), self.act, self.limit, out.data_ptr(), _dtype_id(out),
+                                          out.stride(0), rows, capi.IQ_FLAG_ACCUMULATE if accumulate else 0,
+                                          ws.data_ptr(), ws.numel()))
