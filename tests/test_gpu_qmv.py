@@ -1,0 +1,164 @@
+"""Decode GEMV (iq_qmv through VQMV.encode) against the CPU oracle. Mirrors the reference's qmv kernel cases
+(Tests/IngotTests/KernelCaseG32.swift:21-78, KernelCaseMixedBits.swift:73-121, KernelCaseTests.swift:68-86,614-621)."""
+import numpy as np
+import pytest
+import torch
+
+from ingot_b200 import capi, synth
+from ingot_b200.linear import VQMV
+from oracle import qref
+from gpu_util import TOL, affine_case, deq, mxfp4_case, x_tensor
+
+pytestmark = pytest.mark.gpu
+
+
+def run(m, x, rows, y_dtype=torch.float32, **kw):
+    y = torch.zeros(rows, kw.pop("n_out", m.N), dtype=y_dtype, device=x.device)
+    VQMV.encode(x, m, y, rows, **kw)
+    torch.cuda.synchronize()
+    return y
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("N,K", [(16, 64), (64, 128), (256, 512), (1024, 4096), (80, 2880)])
+@pytest.mark.parametrize("rows", [1, 3, 8, 9, 16])
+def test_qmv_affine_matches_oracle(cuda_device, bits, N, K, rows):
+    rng = np.random.default_rng(1000 * bits + N + K + rows)
+    m, host = affine_case(rng, N, K, bits, cuda_device)
+    x = synth.activations_np(rng, rows, K)
+    y = run(m, x_tensor(x, cuda_device), rows)
+    ref = qref.matmul_t(x, deq(host, bits))
+    assert qref.max_rel(y.cpu().numpy(), ref) <= TOL
+
+
+def test_qmv_c0_shape_seed0(cuda_device):
+    """The decode configuration itself: x bf16 [1, 4096], W [14336, 4096] 4-bit g64, seed 0."""
+    rng = np.random.default_rng(0)
+    m, host = affine_case(rng, 14336, 4096, 4, cuda_device)
+    x = synth.activations_np(rng, 1, 4096)
+    xt = x_tensor(x, cuda_device)
+    y = run(m, xt, 1)
+    ref = qref.matmul_t(x, deq(host, 4))
+    err = qref.max_rel(y.cpu().numpy(), ref)
+    assert err <= TOL, err
+    # bf16 output = round-to-nearest-even of the kernel's own fp32 result
+    yb = run(m, xt, 1, y_dtype=torch.bfloat16)
+    assert torch.equal(yb, y.to(torch.bfloat16))
+
+
+def test_qmv_down_projection_shape(cuda_device):
+    rng = np.random.default_rng(5)
+    m, host = affine_case(rng, 4096, 14336, 4, cuda_device)
+    x = synth.activations_np(rng, 2, 14336)
+    y = run(m, x_tensor(x, cuda_device), 2)
+    assert qref.max_rel(y.cpu().numpy(), qref.matmul_t(x, deq(host, 4))) <= TOL
+
+
+@pytest.mark.parametrize("N,K,rows", [(64, 64, 1), (2880, 2880, 1), (576, 192, 7), (128, 2880, 16)])
+def test_qmv_mxfp4_matches_oracle(cuda_device, N, K, rows):
+    rng = np.random.default_rng(N + K + rows)
+    m, host = mxfp4_case(rng, N, K, cuda_device)
+    x = synth.activations_np(rng, rows, K)
+    y = run(m, x_tensor(x, cuda_device), rows)
+    assert qref.max_rel(y.cpu().numpy(), qref.matmul_t(x, deq(host))) <= TOL
+
+
+def test_qmv_mxfp4_golden_codes(cuda_device):
+    """One-hot activations read the dequantised weights back: the reference's MXFP4 known-answer vector, bit for bit."""
+    import json, os
+    g = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "mxfp4_kat.json")))
+    w = np.zeros((1, 16, 8), dtype=np.uint32)
+    s = np.full((1, 16, 2), 127, dtype=np.uint8)
+    w[0, :2] = np.array(g["words"], dtype=np.uint32).reshape(2, 8)
+    s[0, :2] = np.array(g["scales"], dtype=np.uint8).reshape(2, 2)
+    m = synth.dense_q_mxfp4(w, s, cuda_device)
+    x = torch.eye(64, dtype=torch.float16, device=cuda_device)
+    want = np.array(g["values"], dtype=np.float32).reshape(2, 64)
+    for r0 in range(0, 64, 16):
+        y = run(m, x[r0:r0 + 16].contiguous(), 16)
+        got = y[:, :2].cpu().numpy().T  # [2, 16]
+        assert np.array_equal(got, want[:, r0:r0 + 16])
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_qmv_unpacked_codes_bit_exact(cuda_device, bits):
+    """With scale 1 and bias 0, one-hot activations return the codes themselves: unpacking is bit-exact."""
+    rng = np.random.default_rng(bits)
+    N, K = 32, 128
+    q = rng.integers(0, 1 << bits, size=(1, N, K))
+    w = qref.pack_q(q, bits)
+    one = synth.to_bf16_bits(np.ones((1, N, K // 64), dtype=np.float32))
+    zero = synth.to_bf16_bits(np.zeros((1, N, K // 64), dtype=np.float32))
+    m = synth.dense_q_affine(w, one, zero, bits, cuda_device)
+    x = torch.eye(K, dtype=torch.float16, device=cuda_device)
+    for r0 in range(0, K, 16):
+        y = run(m, x[r0:r0 + 16].contiguous(), 16)
+        assert np.array_equal(y.cpu().numpy().T, q[0][:, r0:r0 + 16].astype(np.float32))
+
+
+def test_qmv_row_invariance(cuda_device):
+    """Row i gives the same bits alone, with i + 1 rows and with 16 rows and other neighbours."""
+    rng = np.random.default_rng(11)
+    m, _ = affine_case(rng, 512, 2048, 4, cuda_device)
+    x = x_tensor(synth.activations_np(rng, 16, 2048), cuda_device)
+    full = run(m, x, 16)
+    for i in (0, 3, 7, 8, 15):
+        part = run(m, x[: i + 1].contiguous(), i + 1)
+        assert torch.equal(part[i], full[i])
+        alone = run(m, x[i:i + 1].contiguous(), 1)
+        assert torch.equal(alone[0], full[i])
+
+
+def test_qmv_strides_accumulate_prefix_dtypes(cuda_device):
+    rng = np.random.default_rng(12)
+    N, K, rows = 256, 512, 5
+    m, host = affine_case(rng, N, K, 4, cuda_device)
+    xh = synth.activations_np(rng, rows, K)
+    ref = qref.matmul_t(xh, deq(host, 4))
+    # padded row strides
+    xp = torch.zeros(rows, K + 64, dtype=torch.bfloat16, device=cuda_device)
+    xp[:, :K] = x_tensor(xh, cuda_device)
+    yp = torch.full((rows, N + 48), 7.0, dtype=torch.float32, device=cuda_device)
+    VQMV.encode(xp, m, yp, rows)
+    torch.cuda.synchronize()
+    assert qref.max_rel(yp[:, :N].cpu().numpy(), ref) <= TOL
+    assert (yp[:, N:] == 7.0).all()
+    # accumulate
+    y0 = torch.from_numpy(rng.normal(size=(rows, N)).astype(np.float32)).to(cuda_device)
+    y = y0.clone()
+    VQMV.encode(x_tensor(xh, cuda_device), m, y, rows, accumulate=True)
+    torch.cuda.synchronize()
+    assert qref.max_rel((y - y0).cpu().numpy(), ref) <= TOL
+    # n_prefix: only the first rows of W
+    y = torch.full((rows, N), -1.0, dtype=torch.float32, device=cuda_device)
+    VQMV.encode(x_tensor(xh, cuda_device), m, y, rows, n_prefix=64)
+    torch.cuda.synchronize()
+    assert qref.max_rel(y[:, :64].cpu().numpy(), ref[:, :64]) <= TOL and (y[:, 64:] == -1.0).all()
+    # fp16 and fp32 activations
+    for dt in (torch.float16, torch.float32):
+        y = run(m, x_tensor(xh, cuda_device, dt), rows)
+        assert qref.max_rel(y.cpu().numpy(), ref) <= TOL
+
+
+def test_qmv_rejects_what_the_reference_rejects(cuda_device):
+    rng = np.random.default_rng(13)
+    m, _ = affine_case(rng, 64, 128, 4, cuda_device)
+    x = torch.zeros(17, 128, dtype=torch.bfloat16, device=cuda_device)
+    y = torch.zeros(17, 64, dtype=torch.float32, device=cuda_device)
+    with pytest.raises(capi.IngotError) as e:
+        VQMV.encode(x, m, y, 17)  # rows <= 16 (Linear.swift precondition)
+    assert e.value.status == -1
+    with pytest.raises(capi.IngotError):
+        VQMV.encode(x, m, y, 4, n_prefix=24)
+
+
+def test_qmv_negative_control(cuda_device):
+    """A perturbed input must make the parity check fail (the reference's --perturb controls)."""
+    rng = np.random.default_rng(14)
+    m, host = affine_case(rng, 64, 256, 4, cuda_device)
+    x = synth.activations_np(rng, 1, 256)
+    w2 = host[0].copy()
+    w2[0, 5, 3] ^= 0x000000F0
+    ref_bad = qref.matmul_t(x, qref.dequant_affine(w2[0], host[1][0], host[2][0], 4))
+    y = run(m, x_tensor(x, cuda_device), 1)
+    assert qref.max_rel(y.cpu().numpy(), ref_bad) > TOL
