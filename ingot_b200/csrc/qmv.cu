@@ -2,8 +2,12 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <stdlib.h>
+#include <string.h>
+
 #include "gqmv.cuh"
 #include "internal.h"
+#include "qmv_stream.cuh"
 
 namespace iq {
 
@@ -51,6 +55,108 @@ GqmvKernel pick(int32_t fmt, int mh, int mode, int wk) {
 
 constexpr int kSmemBudget = 200 * 1024;
 
+// ---- streaming (TMA ring) path --------------------------------------------------------------------------------------
+typedef void (*QsKernel)(const QsParams);
+
+template <int FMT, int MH>
+QsKernel qs_pick_mode(int mode) {
+    switch (mode) {
+        case kModeGateUp: return qmv_stream_kernel<FMT, MH, kModeGateUp>;
+        case kModeDown: return qmv_stream_kernel<FMT, MH, kModeDown>;
+        default: return qmv_stream_kernel<FMT, MH, kModePlain>;
+    }
+}
+QsKernel qs_pick(int32_t fmt, int mh, int mode) {
+    switch (fmt) {
+        case kFmtAffine4: return mh == 2 ? qs_pick_mode<kFmtAffine4, 2>(mode) : qs_pick_mode<kFmtAffine4, 1>(mode);
+        case kFmtAffine8: return mh == 2 ? qs_pick_mode<kFmtAffine8, 2>(mode) : qs_pick_mode<kFmtAffine8, 1>(mode);
+        case kFmtMxfp4: return mh == 2 ? qs_pick_mode<kFmtMxfp4, 2>(mode) : qs_pick_mode<kFmtMxfp4, 1>(mode);
+        default: return nullptr;
+    }
+}
+constexpr int kQsSmemMax = 226 * 1024;
+
+// 0: choose per shape; 1: always the register-staged kernel; 2: the streaming kernel wherever it applies
+int g_path = 0;
+
+// Returns kOk after a launch, 1 when the shape does not fit this path (the caller falls back), or an error.
+int32_t launch_qmv_stream(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
+    const bool has_bias = c.fmt != kFmtMxfp4;
+    const int nw = c.mode == kModeGateUp ? 2 : 1;
+    const int mh = c.max_rows > 8 ? 2 : 1;
+    const int ck = c.fmt == kFmtAffine8 ? 16 : 32;
+    const int qu = ck == 32 ? 4 : 2;
+    const int row_bytes = c.fmt == kFmtAffine8 ? c.K : c.K / 2;
+    const int srow_bytes = c.fmt == kFmtMxfp4 ? c.K / 32 : c.K / 64 * 2;
+    const int per_row = row_bytes + srow_bytes * (has_bias ? 2 : 1);
+    for (int i = 0; i < nw; i++) {
+        if ((reinterpret_cast<uintptr_t>(c.w[i] ? c.w[i] : c.w[0]) & 15) || (reinterpret_cast<uintptr_t>(c.s[i] ? c.s[i] : c.s[0]) & 15) ||
+            (has_bias && (reinterpret_cast<uintptr_t>(c.b[i] ? c.b[i] : c.b[0]) & 15)))
+            return 1;
+    }
+    int rgs = 1;
+    while (rgs < 8 && 16 * rgs * per_row * nw < 24 * 1024 && 16 * rgs * 2 <= c.N) rgs *= 2;
+    const int R = 16 * rgs;
+    const int mat_bytes = round_up(R * per_row, 128);
+    const int stage_bytes = nw * mat_bytes;
+    const int nsteps = (row_bytes / 16 + 3) / 4;
+    const int xs_bytes = round_up(nsteps * qu * c.max_rows * 4 * 16, 128);
+    const int gp = round_up(c.K / 64, 16);
+    const int xsum_bytes = has_bias ? round_up(2 * c.max_rows * gp * 2, 128) : 0;
+    const int red_bytes = 2 * 8 * nw * mh * 4 * 32 * 4;
+    const int fixed = xs_bytes + xsum_bytes + red_bytes + 256;  // + barriers, abort flag, zero block
+    if (stage_bytes > 80 * 1024) return 1;
+    // two CTAs per SM when the activations are small: twice the warps to hide dependency and barrier stalls
+    int ctas_per_sm = 1;
+    int nstages = (kQsSmemMax - fixed) / stage_bytes;
+    if (mh == 1 && nw == 1 && (kQsSmemMax / 2 - 1024 - fixed) / stage_bytes >= 2) {
+        ctas_per_sm = 2;
+        nstages = (kQsSmemMax / 2 - 1024 - fixed) / stage_bytes;
+    }
+    if (nstages < 2) return 1;
+    if (nstages > 8) nstages = 8;
+    QsKernel k = qs_pick(c.fmt, mh, c.mode);
+    if (k == nullptr) return 1;
+
+    QsParams p;
+    memset(&p, 0, sizeof(p));
+    for (int i = 0; i < 2; i++) {
+        p.w[i] = reinterpret_cast<const unsigned char*>(c.w[i] ? c.w[i] : c.w[0]);
+        p.s[i] = reinterpret_cast<const unsigned char*>(c.s[i] ? c.s[i] : c.s[0]);
+        p.b[i] = reinterpret_cast<const unsigned char*>(c.b[i] ? c.b[i] : c.b[0]);
+        p.ebias[i] = c.ebias[i];
+    }
+    p.w_ebytes = c.w_estride * 4;
+    p.s_ebytes = c.s_estride * (c.fmt == kFmtMxfp4 ? 1 : 2);
+    p.N = c.N; p.K = c.K;
+    p.x = c.x; p.x_dtype = c.x_dtype; p.ldx = c.ldx;
+    p.row_map = c.row_map; p.topk = c.topk;
+    p.tiles = c.tiles; p.ntiles = c.ntiles; p.M = c.rows;
+    p.y = c.y; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
+    p.limit = c.limit;
+    p.R = R; p.NB = (c.N + R - 1) / R; p.rgs = rgs; p.wk = 8 / rgs;
+    p.row_bytes = row_bytes; p.srow_bytes = srow_bytes; p.mat_bytes = mat_bytes; p.stage_bytes = stage_bytes;
+    p.nstages = nstages;
+    p.xs_bytes = xs_bytes; p.xsum_bytes = xsum_bytes; p.gp = gp; p.red_bytes = red_bytes;
+    p.status = ctx->d_status;
+
+    const int64_t items = (int64_t)p.NB * c.grid_tiles;
+    const int64_t slots = (int64_t)ctx->sms * ctas_per_sm;
+    const int grid = (int)(items < slots ? items : slots);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kQsThreads, 1, 1);
+    cfg.dynamicSmemBytes = fixed + nstages * stage_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return check_cuda(ctx, cudaLaunchKernelEx(&cfg, k, p), "qmv_stream launch");
+}
+
 }  // namespace
 
 int32_t gqmv_init(iq_ctx* ctx) {
@@ -63,10 +169,23 @@ int32_t gqmv_init(iq_ctx* ctx) {
                                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 20480);
                     if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(gqmv)");
                 }
+    for (int fmt = 0; fmt < 3; fmt++)
+        for (int mh = 1; mh <= 2; mh++)
+            for (int mode = 0; mode < 3; mode++) {
+                cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(qs_pick(fmt, mh, mode)),
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kQsSmemMax);
+                if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_stream)");
+            }
+    const char* env = getenv("INGOT_QMV_PATH");
+    g_path = env == nullptr ? 0 : (strcmp(env, "legacy") == 0 ? 1 : (strcmp(env, "stream") == 0 ? 2 : 0));
     return kOk;
 }
 
 int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
+    if (g_path != 1) {
+        const int32_t r = launch_qmv_stream(ctx, st, c);
+        if (r != 1) return r;
+    }
     const int ck = c.fmt == kFmtAffine8 ? 16 : 32;  // inputs per 16-byte chunk
     const int mh = c.max_rows > 8 ? 2 : 1;
     const int nw = c.mode == kModeGateUp ? 2 : 1;
