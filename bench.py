@@ -1,0 +1,424 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-matmul hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W          (N > 1: launched by torch.distributed.run, one rank per GPU)
+    python bench.py --impl reference --gpus N --steps K --warmup W
+
+Headline workload (`config.workload`): the 48-layer stack of the MoE FFN configuration (128 experts, top-8, d_model
+2048, expert d_ff 768, 4-bit g64, SiLU-SwiGLU, bf16 router ~ N(0, 0.02), per layer r += MoE(RMSNorm(r)) on an fp32
+residual), prefill of 4096 tokens, seeded synthetic weights and activations. One step = one pass of the 4096 tokens
+through the 48 layers. With N GPUs the experts are sharded 128/N per GPU and the tokens 4096/N per rank (total work
+fixed: "strong" scaling); `value` is whole-job tokens/s. The same JSON line carries the other two parts of the
+metric: `qmv` (decode GEMV x[1,4096] · W[14336,4096]ᵀ 4-bit, HBM GB/s) and `qmm` (prefill GEMM M=2048, TFLOP/s), each
+with its own roofline fraction, plus `decode` (the stack at batch 64).
+
+`--impl reference` times the reference's CPU path: ingot has only a Metal implementation, so the CPU path is the C
+restatement under oracle/ of its fp32 semantics ("port"), run with all host threads on a bounded sample of the same
+workload (one layer of the stack per step).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+E, TOPK, D, I = 128, 8, 2048, 768
+LAYERS = 48
+PREFILL_TOKENS = 4096
+DECODE_TOKENS = 64
+
+
+def measured_peaks():
+    """Roofline denominators: the driver's measurement on this pool if present, else the stated fallback."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            f = [v.strip() for v in s.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# GPU arm
+
+
+def build_stack(torch, dev, rank: int, world: int, max_local_tokens: int, layers: int):
+    """The stack's weights, seeded per layer and identical whatever the number of ranks: every rank draws the full
+    expert tensors of a layer on its device and keeps its own contiguous slice."""
+    from ingot_b200 import ep, synth
+    from ingot_b200.linear import DenseQ
+    from ingot_b200.moe import MoELayer, RouterSpec
+
+    lo, per = ep.expert_range(rank, world, E)
+    out, first, first_ep = [], None, None
+    for li in range(layers):
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(li)
+        router = synth.router_cuda(gen, E, D)
+        mats = []
+        for (n, k) in ((I, D), (I, D), (D, I)):
+            full = synth.affine_cuda(gen, n, k, 4, E)
+            mats.append(DenseQ(full.w[lo:lo + per].clone(), full.s[lo:lo + per].clone(), full.b[lo:lo + per].clone(), n, k,
+                               4, 64, "affine", per))
+            del full
+        layer = MoELayer(RouterSpec(E, TOPK), router, mats[0], mats[1], mats[2], expert_lo=lo,
+                         max_tokens=max_local_tokens if first is None else 1)
+        if first is None:
+            first = layer
+        else:
+            layer.share_scratch(first)
+        epl = ep.ExpertParallelMoE(layer, None, max_local_tokens, PREFILL_TOKENS * TOPK if world > 1 else 1, shared=first_ep)
+        if first_ep is None:
+            first_ep = epl
+        out.append(epl)
+    return ep.MoEStack(out, max_local_tokens)
+
+
+def time_steps(torch, dist, world, fn, steps, warmup):
+    """W untimed + K timed calls of fn between barriers, CUDA events on the current stream, max over ranks (ms/step)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def graph_time_us(torch, fn, n_in_graph: int, reps: int = 20) -> float:
+    """Average device time of one call of fn(i): n_in_graph calls captured into a CUDA graph and replayed, which takes
+    the host's launch cost out of a microsecond-scale kernel's timing."""
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for i in range(n_in_graph):
+                fn(i)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (reps * n_in_graph) * 1e3
+
+
+def bench_qmv(torch, dev, peaks):
+    """Decode GEMV: x bf16 [1, 4096], W [14336, 4096] 4-bit g64; eight distinct weight copies (264 MB > L2) in rotation."""
+    from ingot_b200 import synth
+    from ingot_b200.linear import VQMV
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0)
+    N, K = 14336, 4096
+    ms = [synth.affine_cuda(gen, N, K, 4) for _ in range(8)]
+    x = synth.activations_cuda(gen, 1, K)
+    y = torch.zeros(1, N, dtype=torch.bfloat16, device=dev)
+    us = graph_time_us(torch, lambda i: VQMV.encode(x, ms[i % 8], y, 1), 64)
+    nbytes = ms[0].weight_bytes() + K * 2 + N * 2  # codes + scales + biases + x + y = 33,067,008 B
+    gbs = nbytes / us / 1e3
+    return {"workload": "qmv x[1,4096] W[14336,4096] 4-bit g64, bf16 in/out", "us_per_call": round(us, 3),
+            "bytes_per_call": nbytes, "gbs": round(gbs, 1),
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(gbs / peaks["hbm_gbs"], 4), "frac_of_8TBs_nominal": round(gbs / 8000.0, 4),
+                         "traffic": 33075968, "peak_source": peaks["source"]},
+            "l2": "8 weight copies in rotation (264 MB > 126 MB L2)", "timing": "CUDA graph of 64 calls, CUDA events"}
+
+
+def bench_qmm(torch, dev, peaks):
+    """Prefill GEMM: x bf16 [M, 4096], W [14336, 4096], 4- and 8-bit, and the transposed down projection."""
+    from ingot_b200 import synth
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1)
+    res = []
+    for (M, N, K, bits) in ((2048, 14336, 4096, 4), (512, 14336, 4096, 4), (2048, 14336, 4096, 8), (2048, 4096, 14336, 4)):
+        ws_ = [synth.affine_cuda(gen, N, K, bits) for _ in range(3)]  # three copies: > L2 together with x and y
+        x = synth.activations_cuda(gen, M, K)
+        y = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        wk = torch.empty(max(ws_[0].qmm_workspace_bytes(M, x.dtype), 256), dtype=torch.uint8, device=dev)
+        us = graph_time_us(torch, lambda i: ws_[i % 3].encode_qmm_f32(x, y, M, workspace=wk), 6, reps=5)
+        tf = 2.0 * M * N * K / us / 1e6
+        res.append({"M": M, "N": N, "K": K, "bits": bits, "us_per_call": round(us, 1), "tflops": round(tf, 1),
+                    "frac_burst": round(tf / peaks["bf16_tflops"], 4),
+                    "frac_sustained": round(tf / peaks["bf16_tflops_sustained"], 4)})
+        del ws_
+    head = res[0]
+    return {"workload": "qmm x[2048,4096] W[14336,4096] 4-bit g64, bf16 in/out (includes the bf16->fp16 pass)",
+            "tflops": head["tflops"],
+            "roofline": {"bound": "tensor", "achieved": head["tflops"], "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": head["frac_burst"], "traffic": None, "peak_source": peaks["source"]},
+            "cases": res}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from ingot_b200 import ep
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N > 1 with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl")
+    peaks = measured_peaks()
+    T = args.tokens
+    t_lo, t_n = ep.token_slice(rank, world, T)
+    d_lo, d_n = ep.token_slice(rank, world, DECODE_TOKENS)
+    stack = build_stack(torch, dev, rank, world, max(t_n, 1), args.layers)
+
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(1234)
+    r0_host = torch.randn(T, D, generator=gen)                     # residual r0 ~ N(0, 1), the same on every rank
+    r0_pinned = r0_host[t_lo:t_lo + t_n].contiguous().pin_memory()
+    r0_dev = r0_pinned.to(dev)
+    r = torch.empty_like(r0_dev)
+    out_pinned = torch.empty_like(r0_pinned).pin_memory()
+
+    def step():
+        r.copy_(r0_dev)
+        stack.forward(r, t_n)
+
+    def step_e2e():  # host buffers in, host buffer out: the public API a caller drives
+        r.copy_(r0_pinned, non_blocking=True)
+        stack.forward(r, t_n)
+        out_pinned.copy_(r, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = time_steps(torch, dist, world, step, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e = time_steps(torch, dist, world, step_e2e, args.steps, 1)
+    finite = bool(torch.isfinite(r).all().item())
+
+    # decode batch of 64 through the same stack
+    dec = None
+    if d_n > 0:
+        rd0 = r0_dev[:d_n].clone() if t_n >= d_n else torch.randn(d_n, D, device=dev)
+        rd = torch.empty_like(rd0)
+
+        def step_dec():
+            rd.copy_(rd0)
+            stack.forward(rd, d_n)
+
+        ms_dec = time_steps(torch, dist, world, step_dec, max(args.steps, 3), args.warmup)
+        dec = {"tokens": DECODE_TOKENS, "ms_per_step": round(ms_dec, 3), "tokens_per_s": round(DECODE_TOKENS / ms_dec * 1e3, 1)}
+
+    # the dominant kernel of the prefill stack: the experts' gate+up GEMM; timed alone over the layers (rank 0's share)
+    roof = None
+    launches_per_layer = 8 if world == 1 else 10
+    if world == 1:
+        xn = stack.xn
+
+        def gateup_all():
+            for l in stack.layers:
+                l.layer.encode(xn, r, t_n, only="gateup")
+
+        step()
+        ms_gu = time_steps(torch, dist, 1, gateup_all, max(2, args.steps // 2), 1) / len(stack.layers)
+        flops = 2.0 * t_n * TOPK * (2 * I) * D
+        tf = flops / (ms_gu * 1e-3) / 1e12
+        roof = {"kernel": "experts gate+up+SwiGLU (grouped)", "bound": "tensor", "achieved": round(tf, 2),
+                "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": round(tf / peaks["bf16_tflops_sustained"], 4),
+                "traffic": None, "ms_per_launch": round(ms_gu, 4), "flops_per_launch": flops,
+                "peak_source": peaks["source"] + " (sustained: the kernel runs inside a long step)"}
+
+    line = None
+    if rank == 0:
+        qmv = bench_qmv(torch, dev, peaks)
+        qmm = bench_qmm(torch, dev, peaks)
+        from ingot_b200 import capi
+        status = capi.context(local).device_status()
+        line = {
+            "metric": "moe_ffn_tokens_per_s", "value": round(T / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate (4-bit codes)",
+            "data": "synthetic",
+            "config": {"workload": f"{args.layers}-layer MoE FFN stack, prefill {T} tokens: 128 experts top-8 d_model 2048 "
+                                   "d_ff 768 4-bit g64, r += MoE(RMSNorm(r))",
+                       "parallelism": f"ep{world}" if world > 1 else "single", "tokens": T, "layers": args.layers,
+                       "l2": "per-step working set (weights of all layers) is far larger than L2"},
+            "e2e": {"value": round(T / ms_e2e * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 3),
+                    "h2d_bytes_per_step": int(t_n * D * 4), "d2h_bytes_per_step": int(t_n * D * 4)},
+            "gpu_launches": launches_per_layer * args.layers * args.steps,
+            "clocks": clocks, "finite": finite, "device_status": status,
+            "roofline": roof if roof is not None else {"bound": "tensor", "achieved": None, "peak": peaks["bf16_tflops_sustained"],
+                                                        "unit": "TFLOP/s", "frac": None, "traffic": None,
+                                                        "note": "per-kernel timing is taken at N=1"},
+            "decode": dec, "qmv": qmv, "qmm": qmm,
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline(sample_tokens=args.cpu_tokens, reps=1)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# CPU arm: the C restatement of the reference's fp32 semantics, all host threads
+
+
+def cpu_layer_once(sample_tokens: int, seed: int = 0):
+    """One layer of the stack on the CPU (router logits, top-k, gate/up/SwiGLU, down, combine; dequantisation inside the
+    timed region). Returns (seconds, threads)."""
+    import numpy as np
+
+    from ingot_b200 import synth
+    from oracle import cref, qref
+
+    rng = np.random.default_rng(seed)
+    g, u, d = synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, D, I, 4, E)
+    wr = synth.router_np(rng, E, D)
+    x = synth.activations_np(rng, sample_tokens, D)
+    cref.lib()
+    t0 = time.perf_counter()
+    logits = qref.router_logits(x, wr)
+    inds, wts = cref.route(logits, E, TOPK)
+    y, threads = cref.moe_ffn(x, inds, wts, g, u, d, "affine")
+    dt = time.perf_counter() - t0
+    assert np.isfinite(y).all()
+    return dt, threads
+
+
+def cpu_baseline(sample_tokens: int, reps: int = 1):
+    best, threads = None, 1
+    for _ in range(reps):
+        dt, threads = cpu_layer_once(sample_tokens)
+        best = dt if best is None else min(best, dt)
+    return {"value": round(sample_tokens / (best * LAYERS), 2), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"one layer of the 48 at {sample_tokens} tokens on the host ({best:.2f} s), scaled to 48 layers; "
+                      "C restatement under oracle/, OpenMP"}
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path. ingot itself is Metal-only (no CPU or CUDA path to install), so
+    this is the oracle port; one step = one layer of the stack at `--cpu-tokens` tokens, scaled to 48 layers."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n = args.cpu_tokens
+    for _ in range(min(args.warmup, 1)):
+        cpu_layer_once(n)
+    times, threads = [], 1
+    for _ in range(args.steps):
+        dt, threads = cpu_layer_once(n)
+        times.append(dt)
+    sec = sum(times) / len(times)
+    value = round(n / (sec * LAYERS), 2)
+    line = {
+        "impl": "reference", "metric": "moe_ffn_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3 * LAYERS * (args.tokens / n), 1),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{LAYERS}-layer MoE FFN stack, prefill {args.tokens} tokens: 128 experts top-8 d_model 2048 "
+                               "d_ff 768 4-bit g64, r += MoE(RMSNorm(r))", "tokens": args.tokens, "layers": LAYERS},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"one layer at {n} tokens per step, scaled to {LAYERS} layers"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "ingot has no CPU or CUDA implementation to install (Swift + Metal only); this arm runs the C restatement "
+                "of its fp32 semantics kept under oracle/",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS)
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--cpu-tokens", type=int, default=1024, help="tokens of the bounded CPU sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

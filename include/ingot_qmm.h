@@ -188,6 +188,36 @@ int32_t iq_moe_route(iq_moe* layer, void* stream, const float* logits, int32_t l
 int32_t iq_moe_set_external_routing(iq_moe* layer, const uint32_t* inds, const float* wts);
 int32_t iq_moe_get_views(const iq_moe* layer, void* workspace, int32_t tokens, iq_moe_views* out);
 
+/* ---- expert parallelism --------------------------------------------------------------------------------------------
+ * The reference runs on one GPU and has no counterpart for these (its nearest notion is the expert -> slot table
+ * `smap`, Layers/MoE.swift:104). With experts sharded in contiguous ranges over the ranks of one box, a layer is:
+ *   sender:   iq_moe_forward(ROUTER|ROUTE|GROUP) on its tokens, iq_moe_pack_rows -> rows in expert order, which is
+ *             one contiguous segment per destination rank; all-to-all of the rows (the host's collective);
+ *   owner:    iq_moe_experts on the rows it received (source-major, expert order inside a source) -> yd rows;
+ *             all-to-all back;
+ *   sender:   iq_moe_combine_rows on the returned rows, in its own expert order.
+ * Routing is computed by every rank for its own tokens with the full router, so indices do not depend on the number
+ * of ranks. */
+/* rows_f16[pos[pair], :] = fp16(x[pair / top_k, :]) for the routing that GROUP left in `workspace`. */
+int32_t iq_moe_pack_rows(iq_moe* layer, void* stream, const void* x, int32_t x_dtype, int64_t ldx, int32_t tokens,
+                         void* workspace, size_t workspace_bytes, void* rows_f16);
+int32_t iq_moe_experts_workspace_bytes(const iq_moe* layer, int32_t max_rows, int32_t sources, size_t* bytes);
+/* Gate/up/activation/down of the layer's own experts on received rows. rows_f16: fp16 [total_rows, d_model];
+ * counts: device uint32 [sources, experts], counts[s*experts + e] = rows source s sent for expert e (rows are ordered
+ * by source, then expert); yd: fp16 or fp32 [total_rows, d_model]. */
+int32_t iq_moe_experts(iq_moe* layer, void* stream, const void* rows_f16, int32_t total_rows, int32_t max_rows,
+                       const uint32_t* counts, int32_t sources, void* yd, int32_t yd_dtype, void* workspace,
+                       size_t workspace_bytes);
+/* out[t, :] (+)= sum_k wts[t, k] * yd_rows[pos[t*top_k + k], :] with the routing in `workspace`. */
+int32_t iq_moe_combine_rows(iq_moe* layer, void* stream, const void* yd_rows, int32_t yd_dtype, int32_t tokens, void* out,
+                            int32_t out_dtype, int64_t ldo, uint32_t flags, void* workspace, size_t workspace_bytes);
+
+/* ---- layer-stack helper ----------------------------------------------------------------------------------------------
+ * out = x / sqrt(mean(x^2) + eps) per row, unit weight: the input normalisation between the fp32 residual and an FFN
+ * (the reference's rmsnorm kernels, Shaders/verify.metal:503-523; used by the 48-layer benchmark stack). */
+int32_t iq_rmsnorm(iq_ctx* ctx, void* stream, const float* x, int64_t ldx, void* out, int32_t out_dtype, int64_t ldo,
+                   int32_t rows, int32_t d, float eps);
+
 #ifdef __cplusplus
 }
 #endif

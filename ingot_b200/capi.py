@@ -20,7 +20,8 @@ SYMBOLS = [
     "iq_ctx_create", "iq_ctx_destroy", "iq_strerror", "iq_last_error", "iq_ctx_status", "iq_abi_version", "iq_qmv",
     "iq_qmm_workspace_bytes", "iq_qmm", "iq_dense_ffn_workspace_bytes", "iq_dense_ffn", "iq_moe_create",
     "iq_moe_destroy", "iq_moe_workspace_bytes", "iq_moe_forward", "iq_moe_route", "iq_moe_set_external_routing",
-    "iq_moe_get_views",
+    "iq_moe_get_views", "iq_moe_pack_rows", "iq_moe_experts_workspace_bytes", "iq_moe_experts", "iq_moe_combine_rows",
+    "iq_rmsnorm",
 ]
 
 
@@ -87,6 +88,14 @@ def lib() -> C.CDLL:
         l.iq_moe_route.argtypes = [vp, vp, vp, i32, i32, vp, vp]
         l.iq_moe_set_external_routing.argtypes = [vp, vp, vp]
         l.iq_moe_get_views.argtypes = [vp, vp, i32, C.POINTER(MoeViews)]
+        l.iq_moe_pack_rows.argtypes = [vp, vp, vp, i32, i64, i32, vp, sz, vp]
+        l.iq_moe_experts_workspace_bytes.argtypes = [vp, i32, i32, C.POINTER(sz)]
+        l.iq_moe_experts.argtypes = [vp, vp, vp, i32, i32, vp, i32, vp, i32, vp, sz]
+        l.iq_moe_combine_rows.argtypes = [vp, vp, vp, i32, i32, vp, i32, i64, u32, vp, sz]
+        l.iq_rmsnorm.argtypes = [vp, vp, vp, i64, vp, i32, i64, i32, i32, C.c_float]
+        for name in ("iq_moe_pack_rows", "iq_moe_experts_workspace_bytes", "iq_moe_experts", "iq_moe_combine_rows",
+                     "iq_rmsnorm"):
+            getattr(l, name).restype = i32
         for name in ("iq_ctx_create", "iq_qmv", "iq_qmm_workspace_bytes", "iq_qmm", "iq_dense_ffn_workspace_bytes",
                      "iq_dense_ffn", "iq_moe_create", "iq_moe_workspace_bytes", "iq_moe_forward", "iq_moe_route",
                      "iq_moe_set_external_routing", "iq_moe_get_views"):

@@ -94,6 +94,63 @@ int32_t launch_route(iq_moe* l, cudaStream_t st, const float* logits, int ld, in
     return check_cuda(l->ctx, cudaGetLastError(), "route_topk launch");
 }
 
+// Gate + up + activation of every tile: h[row, :] = half(act(x W_gate^T + b_g, x W_up^T + b_u)). Expert e's weights live
+// at local slot e - expert_lo: the offset is folded into the base pointers. row_map == nullptr: x rows are in place.
+int32_t run_gateup(iq_moe* l, cudaStream_t cs, const void* x, int32_t x_dtype, int64_t ldx, const uint32_t* row_map,
+                   const Tile* tiles, const uint32_t* ntiles, int max_tiles, int bm, __half* h) {
+    const iq_moe_desc& d = l->d;
+    const int64_t lo = d.expert_lo;
+    GqmvCall c;
+    c.mode = kModeGateUp;
+    c.fmt = l->fmt;
+    c.w_estride = (int64_t)d.d_ff * (d.d_model / 8);
+    c.s_estride = (int64_t)d.d_ff * (d.d_model / d.gate.group);
+    const size_t sb = l->fmt == kFmtMxfp4 ? 1 : 2;
+    c.w[0] = static_cast<const uint32_t*>(d.gate.w) - lo * c.w_estride;
+    c.w[1] = static_cast<const uint32_t*>(d.up.w) - lo * c.w_estride;
+    c.s[0] = static_cast<const char*>(d.gate.scales) - lo * c.s_estride * (int64_t)sb;
+    c.s[1] = static_cast<const char*>(d.up.scales) - lo * c.s_estride * (int64_t)sb;
+    if (d.gate.biases) {
+        c.b[0] = static_cast<const char*>(d.gate.biases) - lo * c.s_estride * 2;
+        c.b[1] = static_cast<const char*>(d.up.biases) - lo * c.s_estride * 2;
+    }
+    c.N = d.d_ff; c.K = d.d_model;
+    c.x = x; c.x_dtype = x_dtype; c.ldx = ldx;
+    c.row_map = row_map; c.topk = d.top_k;
+    c.tiles = tiles; c.ntiles = ntiles; c.grid_tiles = max_tiles;
+    c.rows = 0; c.max_rows = bm;
+    c.y = h; c.y_dtype = kF16; c.ldy = d.d_ff;
+    if (d.gate_bias) {
+        c.ebias[0] = d.gate_bias - lo * d.d_ff;
+        c.ebias[1] = d.up_bias - lo * d.d_ff;
+    }
+    c.limit = d.act == IQ_ACT_SWIGLU_OAI ? d.act_limit : 0.f;
+    return launch_gqmv(l->ctx, cs, c);
+}
+
+// Down projection of every tile: yd[row, :] = h[row, :] W_down^T + b_d.
+int32_t run_down(iq_moe* l, cudaStream_t cs, const __half* h, const Tile* tiles, const uint32_t* ntiles, int max_tiles,
+                 int bm, void* yd, int32_t yd_dtype) {
+    const iq_moe_desc& d = l->d;
+    const int64_t lo = d.expert_lo;
+    GqmvCall c;
+    c.mode = kModeDown;
+    c.fmt = l->fmt;
+    c.w_estride = (int64_t)d.d_model * (d.d_ff / 8);
+    c.s_estride = (int64_t)d.d_model * (d.d_ff / d.down.group);
+    const size_t sb = l->fmt == kFmtMxfp4 ? 1 : 2;
+    c.w[0] = static_cast<const uint32_t*>(d.down.w) - lo * c.w_estride;
+    c.s[0] = static_cast<const char*>(d.down.scales) - lo * c.s_estride * (int64_t)sb;
+    if (d.down.biases) c.b[0] = static_cast<const char*>(d.down.biases) - lo * c.s_estride * 2;
+    c.N = d.d_model; c.K = d.d_ff;
+    c.x = h; c.x_dtype = kF16; c.ldx = d.d_ff;
+    c.tiles = tiles; c.ntiles = ntiles; c.grid_tiles = max_tiles;
+    c.rows = 0; c.max_rows = bm;
+    c.y = yd; c.y_dtype = yd_dtype; c.ldy = d.d_model;
+    if (d.down_bias) c.ebias[0] = d.down_bias - lo * d.d_model;
+    return launch_gqmv(l->ctx, cs, c);
+}
+
 }  // namespace
 
 int32_t moe_init(iq_ctx* ctx) {
@@ -333,59 +390,17 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
     const int64_t max_tiles64 = (int64_t)d.expert_count + P / bm;
     const int max_tiles = (int)(max_tiles64 < P ? max_tiles64 : P);
     if (max_tiles > 65535) return fail(ctx, kErrInvalidArg, "moe: %d tokens give too many tiles for one launch", tokens);
-    // expert e's weights live at local slot e - expert_lo: fold the offset into the base pointers
-    const int64_t lo = d.expert_lo;
     if (pieces & IQ_PIECE_GATEUP) {
-        GqmvCall c;
-        c.mode = kModeGateUp;
-        c.fmt = l->fmt;
-        c.w_estride = (int64_t)d.d_ff * (d.d_model / 8);
-        c.s_estride = (int64_t)d.d_ff * (d.d_model / d.gate.group);
-        const size_t sb = l->fmt == kFmtMxfp4 ? 1 : 2;
-        c.w[0] = static_cast<const uint32_t*>(d.gate.w) - lo * c.w_estride;
-        c.w[1] = static_cast<const uint32_t*>(d.up.w) - lo * c.w_estride;
-        c.s[0] = static_cast<const char*>(d.gate.scales) - lo * c.s_estride * (int64_t)sb;
-        c.s[1] = static_cast<const char*>(d.up.scales) - lo * c.s_estride * (int64_t)sb;
-        if (d.gate.biases) {
-            c.b[0] = static_cast<const char*>(d.gate.biases) - lo * c.s_estride * 2;
-            c.b[1] = static_cast<const char*>(d.up.biases) - lo * c.s_estride * 2;
-        }
-        c.N = d.d_ff; c.K = d.d_model;
-        c.x = x; c.x_dtype = x_dtype; c.ldx = ldx;
-        c.row_map = w.row_map; c.topk = d.top_k;
-        c.tiles = w.tiles_a; c.ntiles = w.ntiles; c.grid_tiles = max_tiles;
-        c.rows = 0; c.max_rows = bm;
-        c.y = w.h; c.y_dtype = kF16; c.ldy = d.d_ff;
-        if (d.gate_bias) {
-            c.ebias[0] = d.gate_bias - lo * d.d_ff;
-            c.ebias[1] = d.up_bias - lo * d.d_ff;
-        }
-        c.limit = d.act == IQ_ACT_SWIGLU_OAI ? d.act_limit : 0.f;
-        st = launch_gqmv(ctx, cs, c);
+        st = run_gateup(l, cs, x, x_dtype, ldx, w.row_map, w.tiles_a, w.ntiles, max_tiles, bm, w.h);
         if (st != kOk) return st;
     }
     if (pieces & IQ_PIECE_DOWN) {
-        GqmvCall c;
-        c.mode = kModeDown;
-        c.fmt = l->fmt;
-        c.w_estride = (int64_t)d.d_model * (d.d_ff / 8);
-        c.s_estride = (int64_t)d.d_model * (d.d_ff / d.down.group);
-        const size_t sb = l->fmt == kFmtMxfp4 ? 1 : 2;
-        c.w[0] = static_cast<const uint32_t*>(d.down.w) - lo * c.w_estride;
-        c.s[0] = static_cast<const char*>(d.down.scales) - lo * c.s_estride * (int64_t)sb;
-        if (d.down.biases) c.b[0] = static_cast<const char*>(d.down.biases) - lo * c.s_estride * 2;
-        c.N = d.d_model; c.K = d.d_ff;
-        c.x = w.h; c.x_dtype = kF16; c.ldx = d.d_ff;
-        c.tiles = w.tiles_a; c.ntiles = w.ntiles; c.grid_tiles = max_tiles;
-        c.rows = 0; c.max_rows = bm;
-        c.y = w.yd; c.y_dtype = kF32; c.ldy = d.d_model;
-        if (d.down_bias) c.ebias[0] = d.down_bias - lo * d.d_model;
-        st = launch_gqmv(ctx, cs, c);
+        st = run_down(l, cs, w.h, w.tiles_a, w.ntiles, max_tiles, bm, w.yd, kF32);
         if (st != kOk) return st;
     }
     if (pieces & IQ_PIECE_COMBINE) {
         CombineParams cp;
-        cp.yd = w.yd; cp.pos = w.pos; cp.wts = wts;
+        cp.yd = w.yd; cp.yd_dtype = kF32; cp.pos = w.pos; cp.wts = wts;
         cp.out = out; cp.out_dtype = out_dtype; cp.ldo = ldo;
         cp.T = tokens; cp.D = d.d_model; cp.topk = d.top_k;
         cp.accumulate = (flags & IQ_FLAG_ACCUMULATE) ? 1 : 0;
@@ -394,4 +409,113 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
         if (st != kOk) return st;
     }
     return kOk;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Expert-parallel pieces and the stack helper
+
+extern "C" int32_t iq_moe_pack_rows(iq_moe* l, void* stream, const void* x, int32_t x_dtype, int64_t ldx, int32_t tokens,
+                                    void* workspace, size_t workspace_bytes, void* rows_f16) {
+    if (l == nullptr) return kErrInvalidArg;
+    iq_ctx* ctx = l->ctx;
+    const iq_moe_desc& d = l->d;
+    if (tokens < 1 || x == nullptr || rows_f16 == nullptr || x_dtype < 0 || x_dtype > 2 || ldx < d.d_model || ldx % 8 != 0 ||
+        (reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(rows_f16) & 15) != 0)
+        return fail(ctx, kErrInvalidArg, "moe_pack_rows: arguments");
+    MoeWs w = carve(l, workspace, tokens);
+    if (workspace == nullptr || workspace_bytes < w.bytes)
+        return fail(ctx, kErrWorkspace, "moe_pack_rows: workspace %zu < %zu", workspace_bytes, w.bytes);
+    const int P = tokens * d.top_k;
+    moe_pack_rows_kernel<<<P, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x, x_dtype, ldx, w.pos,
+                                                                                static_cast<__half*>(rows_f16), P,
+                                                                                d.d_model, d.top_k);
+    return check_cuda(ctx, cudaGetLastError(), "moe_pack_rows launch");
+}
+
+namespace {
+struct ExpertsWs {
+    Tile* tiles;
+    uint32_t* ntiles;
+    __half* h;
+    size_t bytes;
+};
+ExpertsWs carve_experts(const iq_moe* l, void* base, int max_rows, int sources) {
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        void* p = base ? static_cast<char*>(base) + off : nullptr;
+        off += round_up_sz(bytes, 256);
+        return p;
+    };
+    ExpertsWs w;
+    w.tiles = static_cast<Tile*>(take(((size_t)max_rows / 8 + (size_t)sources * l->d.expert_count + 1) * sizeof(Tile)));
+    w.ntiles = static_cast<uint32_t*>(take(16));
+    w.h = static_cast<__half*>(take((size_t)max_rows * l->d.d_ff * 2));
+    w.bytes = off;
+    return w;
+}
+}  // namespace
+
+extern "C" int32_t iq_moe_experts_workspace_bytes(const iq_moe* l, int32_t max_rows, int32_t sources, size_t* bytes) {
+    if (l == nullptr || bytes == nullptr || max_rows < 1 || sources < 1) return kErrInvalidArg;
+    *bytes = carve_experts(l, nullptr, max_rows, sources).bytes;
+    return kOk;
+}
+
+extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16, int32_t total_rows, int32_t max_rows,
+                                  const uint32_t* counts, int32_t sources, void* yd, int32_t yd_dtype, void* workspace,
+                                  size_t workspace_bytes) {
+    if (l == nullptr) return kErrInvalidArg;
+    iq_ctx* ctx = l->ctx;
+    const iq_moe_desc& d = l->d;
+    if (rows_f16 == nullptr || counts == nullptr || yd == nullptr || sources < 1 || sources * d.expert_count > 4096 ||
+        total_rows < 0 || total_rows > max_rows || (yd_dtype != kF32 && yd_dtype != kF16) ||
+        (reinterpret_cast<uintptr_t>(rows_f16) & 15) != 0)
+        return fail(ctx, kErrInvalidArg, "moe_experts: arguments");
+    if (total_rows == 0) return kOk;
+    ExpertsWs w = carve_experts(l, workspace, max_rows, sources);
+    if (workspace == nullptr || workspace_bytes < w.bytes)
+        return fail(ctx, kErrWorkspace, "moe_experts: workspace %zu < %zu", workspace_bytes, w.bytes);
+    cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+    const int64_t slots = (int64_t)sources * d.expert_count;
+    const int bm = total_rows <= slots * 6 ? 8 : 16;
+    ep_tiles_kernel<<<1, 512, 0, cs>>>(counts, sources, d.experts, d.expert_lo, d.expert_count, bm, w.tiles, w.ntiles);
+    int32_t st = check_cuda(ctx, cudaGetLastError(), "ep_tiles launch");
+    if (st != kOk) return st;
+    const int64_t mt = total_rows / bm + slots;
+    const int max_tiles = (int)(mt < total_rows ? mt : total_rows);
+    if (max_tiles > 65535) return fail(ctx, kErrInvalidArg, "moe_experts: too many tiles for one launch");
+    st = run_gateup(l, cs, rows_f16, kF16, d.d_model, nullptr, w.tiles, w.ntiles, max_tiles, bm, w.h);
+    if (st != kOk) return st;
+    return run_down(l, cs, w.h, w.tiles, w.ntiles, max_tiles, bm, yd, yd_dtype);
+}
+
+extern "C" int32_t iq_moe_combine_rows(iq_moe* l, void* stream, const void* yd_rows, int32_t yd_dtype, int32_t tokens,
+                                       void* out, int32_t out_dtype, int64_t ldo, uint32_t flags, void* workspace,
+                                       size_t workspace_bytes) {
+    if (l == nullptr) return kErrInvalidArg;
+    iq_ctx* ctx = l->ctx;
+    const iq_moe_desc& d = l->d;
+    if (yd_rows == nullptr || out == nullptr || tokens < 1 || (yd_dtype != kF32 && yd_dtype != kF16) || out_dtype < 0 ||
+        out_dtype > 2 || ldo < d.d_model || ldo % 4 != 0)
+        return fail(ctx, kErrInvalidArg, "moe_combine_rows: arguments");
+    MoeWs w = carve(l, workspace, tokens);
+    if (workspace == nullptr || workspace_bytes < w.bytes)
+        return fail(ctx, kErrWorkspace, "moe_combine_rows: workspace %zu < %zu", workspace_bytes, w.bytes);
+    CombineParams cp;
+    cp.yd = yd_rows; cp.yd_dtype = yd_dtype; cp.pos = w.pos; cp.wts = l->ext_wts ? l->ext_wts : w.wts;
+    cp.out = out; cp.out_dtype = out_dtype; cp.ldo = ldo;
+    cp.T = tokens; cp.D = d.d_model; cp.topk = d.top_k;
+    cp.accumulate = (flags & IQ_FLAG_ACCUMULATE) ? 1 : 0;
+    moe_combine_kernel<<<tokens, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(cp);
+    return check_cuda(ctx, cudaGetLastError(), "moe_combine launch");
+}
+
+extern "C" int32_t iq_rmsnorm(iq_ctx* ctx, void* stream, const float* x, int64_t ldx, void* out, int32_t out_dtype,
+                              int64_t ldo, int32_t rows, int32_t d, float eps) {
+    if (ctx == nullptr) return kErrInvalidArg;
+    if (x == nullptr || out == nullptr || rows < 1 || d < 4 || d % 4 != 0 || ldx < d || ldo < d || ldx % 4 != 0 ||
+        ldo % 4 != 0 || out_dtype < 0 || out_dtype > 2)
+        return fail(ctx, kErrInvalidArg, "rmsnorm: arguments");
+    rmsnorm_kernel<<<rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x, ldx, out, out_dtype, ldo, d, eps);
+    return check_cuda(ctx, cudaGetLastError(), "rmsnorm launch");
 }

@@ -301,7 +301,8 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const GroupParams p) {
 // Combine: out[t, :] (+)= sum_k wts[t, k] * Yd[pos[t*topk + k], :] in router rank order k = 0..topk-1, fp32
 // (Shaders/qmm_nax_moe.metal:371-396 of the reference). One block per token.
 struct CombineParams {
-    const float* yd;        // [P, D] expert outputs at sorted positions
+    const void* yd;         // [P, D] expert outputs at sorted positions, fp32 or fp16
+    int32_t yd_dtype;
     const uint32_t* pos;    // [P]
     const float* wts;       // [T, topk]
     void* out;              // [T, ldo]
@@ -322,7 +323,15 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const CombineParams p)
     for (int d = threadIdx.x * 4; d < p.D; d += 1024) {
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int k = 0; k < p.topk; k++) {
-            const float4 y = *reinterpret_cast<const float4*>(p.yd + (size_t)spos[k] * p.D + d);
+            float4 y;
+            if (p.yd_dtype == kF32) {
+                y = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.yd) + (size_t)spos[k] * p.D + d);
+            } else {
+                const uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(p.yd) + (size_t)spos[k] * p.D + d);
+                const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
+                const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+                y = make_float4(lo.x, lo.y, hi.x, hi.y);
+            }
             const float w = sw[k];
             a.x = fmaf(w, y.x, a.x); a.y = fmaf(w, y.y, a.y); a.z = fmaf(w, y.z, a.z); a.w = fmaf(w, y.w, a.w);
         }
@@ -345,6 +354,95 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const CombineParams p)
             float r[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
             for (int j = 0; j < 4; j++) op[j] = __float2half_rn(p.accumulate ? __half2float(op[j]) + r[j] : r[j]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Expert-parallel helpers.
+//
+// pack: rows[pos[pair], :] = fp16(x[pair / topk, :]) — the activations in expert-sorted order, i.e. one contiguous
+// segment per destination rank when experts are sharded in contiguous ranges.
+__global__ void __launch_bounds__(256) moe_pack_rows_kernel(const void* __restrict__ x, int32_t x_dtype, int64_t ldx,
+                                                           const uint32_t* __restrict__ pos, __half* __restrict__ rows,
+                                                           int P, int D, int topk) {
+    const int pair = blockIdx.x;
+    if (pair >= P) return;
+    const size_t src = (size_t)(pair / topk) * ldx;
+    __half* dst = rows + (size_t)pos[pair] * D;
+    for (int u = threadIdx.x; u < D / 8; u += 256) {
+        float v[8];
+        load_x8(x, x_dtype, src + u * 8, v);
+        uint4 o;
+        o.x = pack_half2(v[0], v[1]); o.y = pack_half2(v[2], v[3]); o.z = pack_half2(v[4], v[5]); o.w = pack_half2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(dst + u * 8) = o;
+    }
+}
+
+// Tile list of the rows a rank received: source-major, then by local expert; counts[s * E + e] rows from source s
+// for expert e. One block; entries = sources * local experts (at most 8 per thread with 512 threads).
+__global__ void __launch_bounds__(512) ep_tiles_kernel(const uint32_t* __restrict__ counts, int sources, int E, int e_lo,
+                                                       int e_cnt, int bm, Tile* __restrict__ tiles,
+                                                       uint32_t* __restrict__ ntiles) {
+    __shared__ uint32_t srows[512], stiles[512];
+    const int n = sources * e_cnt;
+    const int per = (n + 511) / 512;
+    const int b = threadIdx.x * per, e_end = min(n, b + per);
+    uint32_t rows = 0, tl = 0;
+    for (int i = b; i < e_end; i++) {
+        const uint32_t c = counts[(i / e_cnt) * E + e_lo + i % e_cnt];
+        rows += c;
+        tl += (c + bm - 1) / bm;
+    }
+    srows[threadIdx.x] = rows;
+    stiles[threadIdx.x] = tl;
+    __syncthreads();
+    uint32_t r0 = 0, t0 = 0;
+    for (int i = 0; i < (int)threadIdx.x; i++) { r0 += srows[i]; t0 += stiles[i]; }
+    for (int i = b; i < e_end; i++) {
+        const uint32_t e = e_lo + i % e_cnt;
+        const uint32_t c = counts[(i / e_cnt) * E + e];
+        for (uint32_t j = 0; j * bm < c; j++) tiles[t0++] = Tile{e, r0 + j * bm, min((uint32_t)bm, c - j * bm), 0};
+        r0 += c;
+    }
+    if (threadIdx.x == 511) ntiles[0] = t0;
+}
+
+// Unit-weight RMSNorm of fp32 rows (the layer-stack skeleton's input normalisation; Shaders/verify.metal:503-523 of
+// the reference): out = x / sqrt(mean(x^2) + eps), written as bf16 / fp16 / fp32. One block per row.
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x, int64_t ldx, void* __restrict__ out,
+                                                     int32_t out_dtype, int64_t ldo, int d, float eps) {
+    __shared__ float wsum[8];
+    const float* xr = x + (size_t)blockIdx.x * ldx;
+    float s = 0.f;
+    for (int i = threadIdx.x * 4; i < d; i += 1024) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + i);
+        s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = s;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += wsum[i];
+    const float r = rsqrtf(tot / (float)d + eps);
+    for (int i = threadIdx.x * 4; i < d; i += 1024) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + i);
+        const float o4[4] = {v.x * r, v.y * r, v.z * r, v.w * r};
+        const size_t o = (size_t)blockIdx.x * ldo + i;
+        if (out_dtype == kF32) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + o) = make_float4(o4[0], o4[1], o4[2], o4[3]);
+        } else if (out_dtype == kBF16) {
+            uint2 w;
+            w.x = f32_to_bf16_bits(o4[0]) | (f32_to_bf16_bits(o4[1]) << 16);
+            w.y = f32_to_bf16_bits(o4[2]) | (f32_to_bf16_bits(o4[3]) << 16);
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(out) + o) = w;
+        } else {
+            uint2 w;
+            w.x = pack_half2(o4[0], o4[1]);
+            w.y = pack_half2(o4[2], o4[3]);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(out) + o) = w;
         }
     }
 }

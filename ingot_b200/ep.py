@@ -1,0 +1,151 @@
+"""Expert-parallel MoE over the GPUs of one box and the layer stack used by the benchmark.
+
+One process per GPU, `torch.distributed` (NCCL over NVLink on GPUs, gloo in the CPU tests of the host logic) for the
+exchange. Experts are sharded in contiguous ranges: rank r of G holds experts [r·E/G, (r+1)·E/G). Tokens are data
+parallel: each rank routes its own T/G tokens with the full (replicated) router, so routing indices do not depend on
+G. A layer is: route + group (local) → pack rows in expert order (one contiguous segment per destination rank) →
+all-to-all of the rows → gate/up/activation/down on the owner → all-to-all back → ordered combine at the sender.
+
+The reference has no multi-GPU path; its nearest notion is the expert→slot table `smap` (Layers/MoE.swift:104).
+The column-split dense linear (output features split N/G per rank, all-gather of the slices) is `ColumnSplitLinear`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import capi
+from .linear import DenseQ, VQMV, _stream_ptr
+from .moe import MoELayer
+
+
+# ---- host logic (pure functions; exercised on CPU with gloo) -----------------------------------------------------------
+def expert_range(rank: int, world: int, experts: int) -> Tuple[int, int]:
+    """Experts owned by `rank`: a contiguous range; experts must divide evenly."""
+    if experts % world != 0:
+        raise ValueError(f"{experts} experts do not divide over {world} ranks")
+    per = experts // world
+    return rank * per, per
+
+
+def plan_exchange(counts_all: np.ndarray, rank: int) -> Tuple[List[int], List[int]]:
+    """counts_all[s, e] = rows rank s routes to expert e. Returns (send_splits, recv_splits) of `rank` in rows:
+    send_splits[d] = rows this rank sends to rank d, recv_splits[s] = rows it receives from rank s."""
+    world, experts = counts_all.shape
+    per = experts // world
+    send = [int(counts_all[rank, d * per:(d + 1) * per].sum()) for d in range(world)]
+    recv = [int(counts_all[s, rank * per:(rank + 1) * per].sum()) for s in range(world)]
+    return send, recv
+
+
+def token_slice(rank: int, world: int, tokens: int) -> Tuple[int, int]:
+    """Tokens [lo, lo + n) handled by `rank` (data parallel; the remainder goes to the first ranks)."""
+    base, rem = divmod(tokens, world)
+    lo = rank * base + min(rank, rem)
+    return lo, base + (1 if rank < rem else 0)
+
+
+# ---- device side ----------------------------------------------------------------------------------------------------------
+class ExpertParallelMoE:
+    """One rank's share of an MoE layer. `layer` holds this rank's experts (expert_lo/expert_count set)."""
+
+    def __init__(self, layer: MoELayer, group: Optional[dist.ProcessGroup], max_local_tokens: int, max_rows: int,
+                 shared: Optional["ExpertParallelMoE"] = None, yd_dtype: torch.dtype = torch.float16):
+        self.layer = layer
+        self.group = group
+        self.world = dist.get_world_size(group) if (group is not None or dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.max_rows = max_rows
+        layer.reserve(max_local_tokens)
+        dev = layer.device
+        E, k, D = layer.router.experts, layer.router.top_k, layer.D
+        if shared is not None:  # layers of a stack run in series and share their exchange buffers
+            self.buf = shared.buf
+        else:
+            P = max_local_tokens * k
+            self.buf = {
+                "send": torch.empty(P, D, dtype=torch.float16, device=dev),
+                "recv": torch.empty(max_rows, D, dtype=torch.float16, device=dev),
+                "yd": torch.empty(max_rows, D, dtype=yd_dtype, device=dev),
+                "back": torch.empty(P, D, dtype=yd_dtype, device=dev),
+                "counts_all": torch.zeros(self.world, E, dtype=torch.int32, device=dev),
+                "ws": torch.empty(layer.experts_workspace_bytes(max_rows, self.world), dtype=torch.uint8, device=dev),
+            }
+
+    def encode(self, x: torch.Tensor, out: torch.Tensor, rows: int, accumulate: bool = False):
+        if self.world == 1:
+            self.layer.encode(x, out, rows, accumulate=accumulate)
+            return
+        L, b = self.layer, self.buf
+        k = L.router.top_k
+        P = rows * k
+        L.encode(x, out, rows, only=("router", "route", "group"))
+        off = L.views(rows)["offsets"]
+        counts = (off[1:] - off[:-1]).contiguous()
+        dist.all_gather_into_tensor(b["counts_all"].view(-1), counts, group=self.group)
+        send, recv = plan_exchange(b["counts_all"].cpu().numpy(), self.rank)  # the one host synchronisation per layer
+        R = sum(recv)
+        if R > self.max_rows:
+            raise RuntimeError(f"rank {self.rank} received {R} rows, more than the {self.max_rows} reserved")
+        L.pack_rows(x, b["send"], rows)
+        dist.all_to_all_single(b["recv"][:R], b["send"][:P], recv, send, group=self.group)
+        L.experts(b["recv"], R, b["counts_all"], self.world, b["yd"], b["ws"])
+        dist.all_to_all_single(b["back"][:P], b["yd"][:R], send, recv, group=self.group)
+        L.combine_rows(b["back"], out, rows, accumulate=accumulate)
+
+
+def rmsnorm(x: torch.Tensor, out: torch.Tensor, rows: int, eps: float = 1e-6, stream=None):
+    """out = x / sqrt(mean(x²) + eps), fp32 in, bf16/fp16/fp32 out (unit weight)."""
+    ctx = capi.context(x.device.index or 0)
+    dt = {torch.float32: capi.IQ_F32, torch.float16: capi.IQ_F16, torch.bfloat16: capi.IQ_BF16}[out.dtype]
+    ctx.check(capi.lib().iq_rmsnorm(ctx.handle, _stream_ptr(stream), x.data_ptr(), x.stride(0), out.data_ptr(), dt,
+                                    out.stride(0), rows, x.shape[1], eps))
+
+
+class MoEStack:
+    """L MoE FFN layers on an fp32 residual: per layer xn = RMSNorm(r) (unit weight, eps 1e-6), r += MoE(xn) — the
+    reference's layer skeleton around its FFN (ModelRound.swift:194-221, accumulate: true)."""
+
+    def __init__(self, layers: Sequence[ExpertParallelMoE], max_local_tokens: int, x_dtype=torch.bfloat16):
+        self.layers = list(layers)
+        D = layers[0].layer.D
+        self.xn = torch.empty(max_local_tokens, D, dtype=x_dtype, device=layers[0].layer.device)
+
+    def forward(self, r: torch.Tensor, rows: int):
+        """r: fp32 [rows, D] residual of this rank's tokens, updated in place."""
+        for l in self.layers:
+            rmsnorm(r, self.xn, rows)
+            l.encode(self.xn, r, rows, accumulate=True)
+        return r
+
+
+class ColumnSplitLinear:
+    """A dense quantized linear split by output features: rank r holds rows [r·N/G, (r+1)·N/G) of w/scales/biases (a
+    contiguous byte range of each tensor, the layout being row-major by output feature), x is replicated, and the
+    slices of y are all-gathered. Decode (rows ≤ 16) uses the GEMV kernel, larger row counts the GEMM kernel."""
+
+    def __init__(self, shard: DenseQ, group: Optional[dist.ProcessGroup], max_rows: int):
+        self.shard, self.group = shard, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        dev = shard.w.device
+        self.y_local = torch.empty(max_rows, shard.N, dtype=torch.float32, device=dev)
+        self.y_all = torch.empty(self.world, max_rows, shard.N, dtype=torch.float32, device=dev)
+        self.ws = torch.empty(max(shard.qmm_workspace_bytes(max(max_rows, 64), torch.bfloat16), 256), dtype=torch.uint8,
+                              device=dev)
+        self.max_rows = max_rows
+
+    def encode(self, x: torch.Tensor, rows: int) -> torch.Tensor:
+        """Returns y_all [G, max_rows, N/G]: slice r holds output features [r·N/G, (r+1)·N/G) of the first `rows` rows."""
+        if rows <= VQMV.MAX_ROWS:
+            VQMV.encode(x, self.shard, self.y_local, rows)
+        else:
+            self.shard.encode_qmm_f32(x, self.y_local, rows, workspace=self.ws)
+        if self.world == 1:
+            self.y_all[0].copy_(self.y_local)
+        else:
+            dist.all_gather_into_tensor(self.y_all, self.y_local, group=self.group)
+        return self.y_all

@@ -81,6 +81,14 @@ class MoELayer:
         self.workspace = torch.empty(n.value, dtype=torch.uint8, device=self.device)
         self.max_tokens = max_tokens
 
+    def share_scratch(self, other: "MoELayer"):
+        """Layers of one model run in series and share their scratch (the reference binds per-layer weights into one
+        shared PrefillMoE, ModelPrefill.swift:367-374). Both layers must have the same shape."""
+        if (other.router.experts, other.router.top_k, other.D, other.I) != (self.router.experts, self.router.top_k,
+                                                                             self.D, self.I):
+            raise ValueError("layers that share scratch must have the same shape")
+        self.workspace, self.max_tokens = other.workspace, other.max_tokens
+
     def encode(self, x: torch.Tensor, out: torch.Tensor, rows: int, accumulate: bool = False,
                only: Optional[Iterable[str]] = None, stream: Optional[torch.cuda.Stream] = None):
         """out[rows, D] (+)= MoE(x[rows, D]) (MoELayer.encode MoE.swift:346-428; PrefillMoE.encodeAll
@@ -140,6 +148,31 @@ class MoELayer:
             "h": view(v.h, torch.float16, (rows * k, self.I)),
             "yd": view(v.yd, torch.float32, (rows * k, self.D)),
         }
+
+    # ---- expert-parallel pieces (no counterpart in the single-GPU reference) ---------------------------------------
+    def pack_rows(self, x: torch.Tensor, rows_f16: torch.Tensor, tokens: int, stream=None):
+        """rows_f16[pos[pair]] = fp16(x[pair // top_k]) for the routing the `group` piece left in the scratch."""
+        self.ctx.check(capi.lib().iq_moe_pack_rows(self._h, _stream_ptr(stream), x.data_ptr(), _dtype_id(x), x.stride(0),
+                                                   tokens, self.workspace.data_ptr(), self.workspace.numel(),
+                                                   rows_f16.data_ptr()))
+
+    def experts_workspace_bytes(self, max_rows: int, sources: int) -> int:
+        n = C.c_size_t()
+        self.ctx.check(capi.lib().iq_moe_experts_workspace_bytes(self._h, max_rows, sources, C.byref(n)))
+        return n.value
+
+    def experts(self, rows_f16: torch.Tensor, total_rows: int, counts: torch.Tensor, sources: int, yd: torch.Tensor,
+                workspace: torch.Tensor, stream=None):
+        """Gate/up/activation/down of this layer's own experts on received rows (source-major, expert order)."""
+        self.ctx.check(capi.lib().iq_moe_experts(self._h, _stream_ptr(stream), rows_f16.data_ptr(), total_rows,
+                                                 rows_f16.shape[0], counts.data_ptr(), sources, yd.data_ptr(),
+                                                 _dtype_id(yd), workspace.data_ptr(), workspace.numel()))
+
+    def combine_rows(self, yd_rows: torch.Tensor, out: torch.Tensor, tokens: int, accumulate: bool = False, stream=None):
+        self.ctx.check(capi.lib().iq_moe_combine_rows(self._h, _stream_ptr(stream), yd_rows.data_ptr(), _dtype_id(yd_rows),
+                                                      tokens, out.data_ptr(), _dtype_id(out), out.stride(0),
+                                                      capi.IQ_FLAG_ACCUMULATE if accumulate else 0,
+                                                      self.workspace.data_ptr(), self.workspace.numel()))
 
     def close(self):
         if self._h:
