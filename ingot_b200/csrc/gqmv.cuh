@@ -3,11 +3,12 @@
 //
 // One warp owns 16 consecutive output rows of W and a slice of K. Each lane streams 16-byte pieces ("chunks") of two
 // rows (r = lane/4 and r + 8): the four lanes of a row take four adjacent chunks, so every load instruction covers
-// 64 contiguous bytes of 8 (x2) rows. The codes become fp16 with one logic op and one half2 FMA per pair of weights
-// (the 0x6400 "1024 + q" trick followed by an exact fma(h, s, -1024 s) = round(s*q)), and the multiply-accumulate runs
-// on m16n8k16 tensor-core fragments with W as the A operand and up to 8 (or 16) activation rows as B, accumulating in
-// fp32. The affine bias term is applied exactly once per group through a second tiny MMA on per-group sums of x
-// (y += b[n,g] * sum_k x[m,k in g]). Activations are staged once per CTA into shared memory as fp16 in the
+// 64 contiguous bytes of 8 (x2) rows. The codes become fp16 weights with one logic op, one exact half2 subtraction
+// and one half2 FMA per pair (the 0x6400 "1024 + q" trick, then w = fma(q, s, b) rounded once: the fp16 rounding of
+// the exact s*q + b, which is the reference kernels' arithmetic), and the multiply-accumulate runs on m16n8k16
+// tensor-core fragments with W as the A operand and up to 8 (or 16) activation rows as B, accumulating in fp32.
+// (Rounding s*q alone and adding the bias separately was measured at 1.2e-3 on a small MoE layer: over the parity
+// bound; the single rounding of s*q + b measures ~0.) Activations are staged once per CTA into shared memory as fp16 in the
 // fragment order the B operand wants, so the inner loop has no shuffles. Partial sums of the K-slices are added in a
 // fixed warp order, which makes a row's bits independent of the other rows (the reference's row-invariance property,
 // Tests/IngotTests/KernelCaseTests.swift:68-86).
@@ -57,8 +58,6 @@ struct GqmvParams {
     // K tiling (host-chosen): K is walked in tiles of `kt` inputs, kt a multiple of 512
     int32_t kt;
     int32_t xs_bytes;    // bytes of the staged-x region (sized for the largest tile)
-    int32_t xsum_bytes;  // bytes of the two per-group-sum arrays (0 when the format has no bias)
-    int32_t gp;          // padded number of groups per K tile (multiple of 16)
 };
 
 template <int FMT>
@@ -66,7 +65,7 @@ struct FmtTraits;
 template <>
 struct FmtTraits<kFmtAffine4> {
     static constexpr int CK = 32, QU = 4, CPG = 2, GROUP = 64;
-    static constexpr bool PERM = true, BIAS = true;
+    static constexpr bool PERM = true, BIAS = true;  // BIAS: the format carries a per-group bias tensor
 };
 template <>
 struct FmtTraits<kFmtAffine8> {
@@ -97,28 +96,37 @@ __device__ __forceinline__ void cvt_e2m1x8(uint32_t w, uint32_t (&h)[4]) {
         : "r"(w));
 }
 
-// Per-chunk dequantisation constants of one weight row.
+// Per-chunk dequantisation constants of one weight row: scale, scale / 16 and bias as half2 pairs.
 struct DqConst {
-    uint32_t s2, c2, s16, c16;
+    uint32_t s2, s16, b2;
 };
 
+// raw_scale / raw_bias: bf16 bit patterns (affine) or the e8m0 byte (mxfp4, no bias).
 template <int FMT>
-__device__ __forceinline__ DqConst make_dq(uint32_t raw_scale) {
+__device__ __forceinline__ DqConst make_dq(uint32_t raw_scale, uint32_t raw_bias = 0) {
     DqConst d;
     if (FMT == kFmtMxfp4) {
         // e8m0: 2^(s - 127), 255 = NaN (Loader/Quant.swift:198-202 of the reference)
         float f = raw_scale == 255u ? __uint_as_float(0x7FC00000u)
                                     : (raw_scale == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(raw_scale << 23));
         d.s2 = pack_half2(f, f);
-        d.c2 = d.s16 = d.c16 = 0;
+        d.s16 = d.b2 = 0;
     } else {
-        float s = bf16_bits_to_f32(raw_scale);
+        const float s = bf16_bits_to_f32(raw_scale), b = bf16_bits_to_f32(raw_bias);
         d.s2 = pack_half2(s, s);
-        d.c2 = hmul2_u32(d.s2, 0xE400E400u);    // -1024 * s (exact)
-        d.s16 = hmul2_u32(d.s2, 0x2C002C00u);   // s / 16 (exact)
-        d.c16 = hmul2_u32(d.s2, 0xD400D400u);   // -64 * s = -1024 * (s / 16)
+        d.s16 = hmul2_u32(d.s2, 0x2C002C00u);  // s / 16 (exact)
+        d.b2 = pack_half2(b, b);
     }
     return d;
+}
+
+// (1024 + v, 1024 + v') -> fma(v, s, b) with one rounding: the subtraction is exact, so the weight is the fp16
+// rounding of the exact s * q + b — the reference kernels' own arithmetic (Shaders/qmm_nax.metal:77-95).
+__device__ __forceinline__ uint32_t dq_pair(uint32_t magic_plus_v, uint32_t s2, uint32_t b2) {
+    const uint32_t k1024 = 0x64006400u;
+    __half2 q = __hsub2(*reinterpret_cast<__half2*>(&magic_plus_v), *reinterpret_cast<const __half2*>(&k1024));
+    __half2 r = __hfma2(q, *reinterpret_cast<__half2*>(&s2), *reinterpret_cast<__half2*>(&b2));
+    return *reinterpret_cast<uint32_t*>(&r);
 }
 
 // Dequantises word `wd` of a chunk into the A-operand halves it feeds:
@@ -127,13 +135,13 @@ template <int FMT>
 __device__ __forceinline__ void dequant_word(uint32_t w, const DqConst& d, uint32_t (&p)[4]) {
     if (FMT == kFmtAffine4) {
         const uint32_t w8 = w >> 8;
-        p[0] = hfma2_u32((w & 0x000F000Fu) | 0x64006400u, d.s2, d.c2);     // (n0, n4)
-        p[1] = hfma2_u32((w & 0x00F000F0u) | 0x64006400u, d.s16, d.c16);   // (n1, n5)
-        p[2] = hfma2_u32((w8 & 0x000F000Fu) | 0x64006400u, d.s2, d.c2);    // (n2, n6)
-        p[3] = hfma2_u32((w8 & 0x00F000F0u) | 0x64006400u, d.s16, d.c16);  // (n3, n7)
+        p[0] = dq_pair((w & 0x000F000Fu) | 0x64006400u, d.s2, d.b2);    // (n0, n4)
+        p[1] = dq_pair((w & 0x00F000F0u) | 0x64006400u, d.s16, d.b2);   // (n1, n5): the codes sit 16x up
+        p[2] = dq_pair((w8 & 0x000F000Fu) | 0x64006400u, d.s2, d.b2);   // (n2, n6)
+        p[3] = dq_pair((w8 & 0x00F000F0u) | 0x64006400u, d.s16, d.b2);  // (n3, n7)
     } else if (FMT == kFmtAffine8) {
-        p[0] = hfma2_u32(__byte_perm(w, 0x64646464u, 0x4140), d.s2, d.c2);  // (c0, c1)
-        p[1] = hfma2_u32(__byte_perm(w, 0x64646464u, 0x4342), d.s2, d.c2);  // (c2, c3)
+        p[0] = dq_pair(__byte_perm(w, 0x64646464u, 0x4140), d.s2, d.b2);  // (c0, c1)
+        p[1] = dq_pair(__byte_perm(w, 0x64646464u, 0x4342), d.s2, d.b2);  // (c2, c3)
         p[2] = p[3] = 0;
     } else {
         uint32_t h[4];
@@ -147,6 +155,7 @@ template <int FMT, int NW>
 struct Batch {
     uint4 v[NW][2];       // codes of rows r and r + 8
     uint32_t sc[NW][2];   // raw scale of the chunk's group
+    uint32_t bi[NW][2];   // raw bias of the chunk's group (affine)
 };
 
 template <int FMT, int MH, int NW, int MODE, int RG, int WK>
@@ -174,9 +183,7 @@ __global__ void __launch_bounds__(RG* WK * 32) gqmv_kernel(const GqmvParams p) {
     const bool rows_ok = n0 < p.N;               // N is a multiple of 16
 
     uint4* xs = reinterpret_cast<uint4*>(smem);
-    __half* xsum_hi = reinterpret_cast<__half*>(smem + p.xs_bytes);
-    __half* xsum_lo = xsum_hi + MR * p.gp;
-    float* red = reinterpret_cast<float*>(smem + p.xs_bytes + p.xsum_bytes);
+    float* red = reinterpret_cast<float*>(smem + p.xs_bytes);
 
     const int row_words = p.K / 32 * (FMT == kFmtAffine8 ? 8 : 4);  // uint32 per weight row
     const int row_groups = p.K / F::GROUP;
@@ -184,6 +191,7 @@ __global__ void __launch_bounds__(RG* WK * 32) gqmv_kernel(const GqmvParams p) {
 
     const uint4* wrow[NW][2];
     const unsigned char* srow[NW][2];
+    const unsigned char* brow[NW][2];
 #pragma unroll
     for (int i = 0; i < NW; i++)
 #pragma unroll
@@ -192,6 +200,9 @@ __global__ void __launch_bounds__(RG* WK * 32) gqmv_kernel(const GqmvParams p) {
             wrow[i][h] = reinterpret_cast<const uint4*>(p.w[i] + tile.expert * p.w_estride + r * row_words);
             srow[i][h] = reinterpret_cast<const unsigned char*>(p.s[i]) +
                          (tile.expert * p.s_estride + r * row_groups) * (FMT == kFmtMxfp4 ? 1 : 2);
+            brow[i][h] = FMT == kFmtMxfp4 ? srow[i][h]
+                                          : reinterpret_cast<const unsigned char*>(p.b[i]) +
+                                                (tile.expert * p.s_estride + r * row_groups) * 2;
         }
 
     float acc[NW][MH][4];
@@ -216,9 +227,11 @@ __global__ void __launch_bounds__(RG* WK * 32) gqmv_kernel(const GqmvParams p) {
                         bt[u].v[i][h] = ldg_nc_u4(wrow[i][h] + c);
                         bt[u].sc[i][h] = FMT == kFmtMxfp4 ? ldg_nc_u8(srow[i][h] + c / F::CPG)
                                                          : ldg_nc_u16(srow[i][h] + 2 * (c / F::CPG));
+                        bt[u].bi[i][h] = FMT == kFmtMxfp4 ? 0u : ldg_nc_u16(brow[i][h] + 2 * (c / F::CPG));
                     } else {
                         bt[u].v[i][h] = make_uint4(0, 0, 0, 0);
                         bt[u].sc[i][h] = FMT == kFmtMxfp4 ? 127u : 0u;
+                        bt[u].bi[i][h] = 0u;
                     }
                 }
         }
@@ -232,7 +245,7 @@ __global__ void __launch_bounds__(RG* WK * 32) gqmv_kernel(const GqmvParams p) {
 #pragma unroll
             for (int i = 0; i < NW; i++)
 #pragma unroll
-                for (int h = 0; h < 2; h++) dq[i][h] = make_dq<FMT>(bt[u].sc[i][h]);
+                for (int h = 0; h < 2; h++) dq[i][h] = make_dq<FMT>(bt[u].sc[i][h], bt[u].bi[i][h]);
 #pragma unroll
             for (int q = 0; q < F::QU; q++) {
                 // x fragments of this 8-input unit for rows g (and g + 8)
@@ -312,35 +325,6 @@ __global__ void __launch_bounds__(RG* WK * 32) gqmv_kernel(const GqmvParams p) {
                     const int kl = ku * 8, cl = kl / F::CK, q = (kl % F::CK) / 8;
                     xs[(((cl >> 2) * F::QU + q) * MR + m) * 4 + (cl & 3)] = o;
                 }
-                if (F::BIAS) {
-                    // sum of the fp16-rounded values of this unit, then over the 8 units of a group of 64
-                    float sm = 0.f;
-                    {
-                        const __half2* hp = reinterpret_cast<const __half2*>(&o);
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            float2 f = __half22float2(hp[e]);
-                            sm += f.x + f.y;
-                        }
-                    }
-                    sm += __shfl_xor_sync(0xffffffffu, sm, 1);
-                    sm += __shfl_xor_sync(0xffffffffu, sm, 2);
-                    sm += __shfl_xor_sync(0xffffffffu, sm, 4);
-                    if ((lane & 7) == 0 && uidx < total) {
-                        const __half hi = __float2half_rn(sm);
-                        const __half lo = __float2half_rn(sm - __half2float(hi));
-                        xsum_hi[m * p.gp + ku / 8] = hi;
-                        xsum_lo[m * p.gp + ku / 8] = lo;
-                    }
-                }
-            }
-            if (F::BIAS) {
-                const int ng = klen / 64;
-                for (int i = tid; i < MR * (p.gp - ng); i += NT) {
-                    const int m = i / (p.gp - ng), gg = ng + i % (p.gp - ng);
-                    xsum_hi[m * p.gp + gg] = __float2half_rn(0.f);
-                    xsum_lo[m * p.gp + gg] = __float2half_rn(0.f);
-                }
             }
         }
         __syncthreads();
@@ -356,37 +340,6 @@ __global__ void __launch_bounds__(RG* WK * 32) gqmv_kernel(const GqmvParams p) {
             }
         }
 
-        // ---- affine bias term: acc += b[n, g] * xsum[m, g], 16 groups per MMA ------------------------------------
-        if (F::BIAS && rows_ok) {
-            const int ng = klen / 64, g_base = k0 / 64;
-            for (int gs = wk * 16; gs < ng; gs += WK * 16) {
-#pragma unroll
-                for (int i = 0; i < NW; i++) {
-                    uint32_t a[4];
-#pragma unroll
-                    for (int h = 0; h < 2; h++)
-#pragma unroll
-                        for (int half = 0; half < 2; half++) {
-                            const int gl = gs + 2 * t + 8 * half;
-                            const uint16_t* bp = reinterpret_cast<const uint16_t*>(p.b[i]) +
-                                                 tile.expert * p.s_estride + (int64_t)(n0 + g + 8 * h) * row_groups +
-                                                 g_base + gl;
-                            const float v0 = gl < ng ? bf16_bits_to_f32(ldg_nc_u16(bp)) : 0.f;
-                            const float v1 = gl + 1 < ng ? bf16_bits_to_f32(ldg_nc_u16(bp + 1)) : 0.f;
-                            a[h + 2 * half] = pack_half2(v0, v1);
-                        }
-#pragma unroll
-                    for (int h = 0; h < MH; h++) {
-                        const int m = g + 8 * h;
-                        const uint32_t* ph = reinterpret_cast<const uint32_t*>(xsum_hi + m * p.gp + gs + 2 * t);
-                        const uint32_t* pl = reinterpret_cast<const uint32_t*>(xsum_lo + m * p.gp + gs + 2 * t);
-                        const bool live = m < M;
-                        mma16816(acc[i][h], a[0], a[1], a[2], a[3], live ? ph[0] : 0u, live ? ph[4] : 0u);
-                        mma16816(acc[i][h], a[0], a[1], a[2], a[3], live ? pl[0] : 0u, live ? pl[4] : 0u);
-                    }
-                }
-            }
-        }
     }
 
     // ---- reduce the K slices in warp order -------------------------------------------------------------------------

@@ -101,10 +101,8 @@ int32_t launch_qmv_stream(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     const int stage_bytes = nw * mat_bytes;
     const int nsteps = (row_bytes / 16 + 3) / 4;
     const int xs_bytes = round_up(nsteps * qu * c.max_rows * 4 * 16, 128);
-    const int gp = round_up(c.K / 64, 16);
-    const int xsum_bytes = has_bias ? round_up(2 * c.max_rows * gp * 2, 128) : 0;
     const int red_bytes = 2 * 8 * nw * mh * 4 * 32 * 4;
-    const int fixed = xs_bytes + xsum_bytes + red_bytes + 256;  // + barriers, abort flag, zero block
+    const int fixed = xs_bytes + red_bytes + 256;  // + barriers, abort flag, zero block
     if (stage_bytes > 80 * 1024) return 1;
     // two CTAs per SM when the activations are small: twice the warps to hide dependency and barrier stalls
     int ctas_per_sm = 1;
@@ -137,7 +135,7 @@ int32_t launch_qmv_stream(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     p.R = R; p.NB = (c.N + R - 1) / R; p.rgs = rgs; p.wk = 8 / rgs;
     p.row_bytes = row_bytes; p.srow_bytes = srow_bytes; p.mat_bytes = mat_bytes; p.stage_bytes = stage_bytes;
     p.nstages = nstages;
-    p.xs_bytes = xs_bytes; p.xsum_bytes = xsum_bytes; p.gp = gp; p.red_bytes = red_bytes;
+    p.xs_bytes = xs_bytes; p.red_bytes = red_bytes;
     p.status = ctx->d_status;
 
     const int64_t items = (int64_t)p.NB * c.grid_tiles;
@@ -192,21 +190,19 @@ int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     const bool has_bias = c.fmt != kFmtMxfp4;
     // K tile: everything at once when the staged activations fit, else the largest multiple of 1024 that does
     int kt = c.K;
-    auto smem_for = [&](int ktile, int* xs_bytes, int* xsum_bytes, int* gp) {
+    auto smem_for = [&](int ktile, int* xs_bytes) {
         const int nsteps = (ktile / ck + 3) / 4;
         const int qu = ck == 32 ? 4 : 2;
         *xs_bytes = nsteps * qu * c.max_rows * 4 * 16;
-        *gp = round_up(ktile / 64, 16);
-        *xsum_bytes = has_bias ? 2 * c.max_rows * (*gp) * 2 : 0;
         const int red_bytes = 8 * nw * mh * 4 * 32 * 4;
-        return *xs_bytes + *xsum_bytes + red_bytes;
+        return *xs_bytes + red_bytes;
     };
-    int xs_bytes, xsum_bytes, gp;
-    while (smem_for(kt, &xs_bytes, &xsum_bytes, &gp) > kSmemBudget) {
+    int xs_bytes;
+    while (smem_for(kt, &xs_bytes) > kSmemBudget) {
         kt = kt > 1024 ? (kt - 1) / 1024 * 1024 : 0;
         if (kt == 0) return fail(ctx, kErrInvalidArg, "qmv: activations do not fit shared memory");
     }
-    const int smem = smem_for(kt, &xs_bytes, &xsum_bytes, &gp);
+    const int smem = smem_for(kt, &xs_bytes);
 
     // K slices per CTA: the fewest that still fill the GPU, keeping at least two steps per warp
     const int nsteps = (kt / ck + 3) / 4;
@@ -233,7 +229,7 @@ int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     p.tiles = c.tiles; p.ntiles = c.ntiles; p.M = c.rows;
     p.y = c.y; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
     p.limit = c.limit;
-    p.kt = kt; p.xs_bytes = xs_bytes; p.xsum_bytes = xsum_bytes; p.gp = gp;
+    p.kt = kt; p.xs_bytes = xs_bytes;
 
     dim3 grid((c.N / 16 + rg - 1) / rg, c.grid_tiles, 1);
     k<<<grid, 256, smem, st>>>(p);

@@ -55,7 +55,7 @@ struct QsParams {
     int32_t stage_bytes;
     int32_t nstages;
     // shared-memory layout
-    int32_t xs_bytes, xsum_bytes, gp, red_bytes;
+    int32_t xs_bytes, red_bytes;
     int32_t* status;
 };
 
@@ -76,9 +76,8 @@ __global__ void __launch_bounds__(kQsThreads, (MH == 1 && MODE != kModeGateUp) ?
     constexpr int NW = MODE == kModeGateUp ? 2 : 1;
     extern __shared__ __align__(128) unsigned char smem[];
     uint4* xs = reinterpret_cast<uint4*>(smem);
-    __half* xsum_hi = reinterpret_cast<__half*>(smem + p.xs_bytes);
-    float* red = reinterpret_cast<float*>(smem + p.xs_bytes + p.xsum_bytes);
-    unsigned char* stages = smem + p.xs_bytes + p.xsum_bytes + p.red_bytes;
+    float* red = reinterpret_cast<float*>(smem + p.xs_bytes);
+    unsigned char* stages = smem + p.xs_bytes + p.red_bytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(stages + (size_t)p.nstages * p.stage_bytes);
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * p.nstages;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * p.nstages);
@@ -197,28 +196,6 @@ __global__ void __launch_bounds__(kQsThreads, (MH == 1 && MODE != kModeGateUp) ?
                         const int kl = ku * 8, cl = kl / F::CK, q = (kl % F::CK) / 8;
                         xs[(((cl >> 2) * F::QU + q) * M + m) * 4 + (cl & 3)] = o;
                     }
-                    if (F::BIAS) {
-                        float sm = 0.f;
-                        const __half2* hp = reinterpret_cast<const __half2*>(&o);
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            float2 f = __half22float2(hp[e]);
-                            sm += f.x + f.y;
-                        }
-                        sm += __shfl_xor_sync(0xffffffffu, sm, 1);
-                        sm += __shfl_xor_sync(0xffffffffu, sm, 2);
-                        sm += __shfl_xor_sync(0xffffffffu, sm, 4);
-                        if ((lane & 7) == 0 && uidx < total_units) {
-                            const __half hi16 = __float2half_rn(sm);
-                            xsum_hi[m * p.gp + ku / 8] = hi16;
-                            xsum_hi[(M + m) * p.gp + ku / 8] = __float2half_rn(sm - __half2float(hi16));
-                        }
-                    }
-                }
-                if (F::BIAS) {
-                    const int ng = p.K / 64, pad = p.gp - ng;
-                    for (int i = tid; i < 2 * M * pad; i += kQsConsumers)
-                        xsum_hi[(i / pad) * p.gp + ng + i % pad] = __float2half_rn(0.f);
                 }
                 consumer_barrier();
             }
@@ -273,8 +250,9 @@ __global__ void __launch_bounds__(kQsThreads, (MH == 1 && MODE != kModeGateUp) ?
                         for (int h = 0; h < 2; h++) {
                             if (c_ok) {
                                 cv[i][h] = lds128(ca[i][h] + j * 64);
-                                dq[i][h] = make_dq<FMT>(FMT == kFmtMxfp4 ? lds_u8(sa[i][h] + j * SSTEP)
-                                                                         : lds_u16(sa[i][h] + j * SSTEP));
+                                dq[i][h] = FMT == kFmtMxfp4 ? make_dq<FMT>(lds_u8(sa[i][h] + j * SSTEP))
+                                                            : make_dq<FMT>(lds_u16(sa[i][h] + j * SSTEP),
+                                                                           lds_u16(sa[i][h] + sc_bytes + j * SSTEP));
                             } else {
                                 cv[i][h] = make_uint4(0, 0, 0, 0);
                                 dq[i][h] = make_dq<FMT>(FMT == kFmtMxfp4 ? 127u : 0u);
@@ -320,38 +298,6 @@ __global__ void __launch_bounds__(kQsThreads, (MH == 1 && MODE != kModeGateUp) ?
                 for (int h = 0; h < MH; h++)
 #pragma unroll
                     for (int e = 0; e < 4; e++) acc[i][h][e] = acc2[i][h][0][e] + acc2[i][h][1][e];
-            if (ok && rows_ok) {
-                // ---- affine bias term, 16 groups per MMA ---------------------------------------------------------------
-                if (F::BIAS) {
-                    const int ng = p.K / 64;
-                    for (int gs = wk * 16; gs < ng; gs += p.wk * 16) {
-#pragma unroll
-                        for (int i = 0; i < NW; i++) {
-                            const unsigned char* bb = st + i * p.mat_bytes + codes_bytes + sc_bytes;
-                            uint32_t a[4];
-#pragma unroll
-                            for (int h = 0; h < 2; h++)
-#pragma unroll
-                                for (int half = 0; half < 2; half++) {
-                                    const int gl = gs + 2 * t + 8 * half;
-                                    const uint16_t* bp = reinterpret_cast<const uint16_t*>(bb + (lr + 8 * h) * p.srow_bytes) + gl;
-                                    const float v0 = gl < ng ? bf16_bits_to_f32(bp[0]) : 0.f;
-                                    const float v1 = gl + 1 < ng ? bf16_bits_to_f32(bp[1]) : 0.f;
-                                    a[h + 2 * half] = pack_half2(v0, v1);
-                                }
-#pragma unroll
-                            for (int h = 0; h < MH; h++) {
-                                const int m = g + 8 * h;
-                                const bool live = m < M;
-                                const uint32_t* ph32 = reinterpret_cast<const uint32_t*>(xsum_hi + m * p.gp + gs + 2 * t);
-                                const uint32_t* pl32 = reinterpret_cast<const uint32_t*>(xsum_hi + (M + m) * p.gp + gs + 2 * t);
-                                mma16816(acc[i][h], a[0], a[1], a[2], a[3], live ? ph32[0] : 0u, live ? ph32[4] : 0u);
-                                mma16816(acc[i][h], a[0], a[1], a[2], a[3], live ? pl32[0] : 0u, live ? pl32[4] : 0u);
-                            }
-                        }
-                    }
-                }
-            }
             // the stage is free as soon as every warp has read its part
             __syncwarp();
             if (lane == 0 && ok) mbar_arrive(bar_empty + 8 * s);
