@@ -102,6 +102,21 @@ int32_t iq_qmm_workspace_bytes(iq_ctx* ctx, const iq_qlinear* m, int32_t rows, i
 int32_t iq_qmm(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx, const iq_qlinear* m, void* y,
                int32_t y_dtype, int64_t ldy, int32_t rows, uint32_t flags, void* workspace, size_t workspace_bytes);
 
+/* Prefill GEMM for callers that must not allocate device memory. No counterpart in the reference (its scratch is
+ * ordinary Metal buffers made at construction). Meant for hosts where cudaMalloc is off limits at the call site: a
+ * plugin inside an engine whose pool owns all device memory, a path that runs after the pool is sealed, a sandbox or
+ * real-time loop with a "no allocation" rule. Same operation and results as iq_qmm, but the fp16 copy of bf16/fp32
+ * activations goes to an 8 MiB array built into the library (held by every GPU that loads it until the process
+ * exits) instead of a caller workspace. Limits and rules:
+ *   - rows * k <= 4,194,304 (8 MiB of fp16); larger calls return IQ_ERR_WORKSPACE and should use iq_qmm;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress) with that device current;
+ *     make that first call outside any stream capture;
+ *   - the call itself allocates and frees nothing;
+ *   - all calls on a GPU share the one array: calls whose kernels may overlap on the GPU (different streams) race on
+ *     it — keep them on one stream or order them. Nothing in it has to be cleared between calls. */
+int32_t iq_qmm_noalloc(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx, const iq_qlinear* m,
+                       void* y, int32_t y_dtype, int64_t ldy, int32_t rows, uint32_t flags);
+
 /* ---- dense gated FFN ------------------------------------------------------------------------------------------------
  * out[rows, d] (+)= down( act(gate x) * up x ) with gate|up concatenated by rows as one [2*d_ff, d] matrix (gate rows
  * first). Replaces DenseMLP.encode / encodePrefill (Sources/Ingot/Layers/Dense.swift:56-96) and dswiglu*

@@ -189,3 +189,50 @@ extern "C" int32_t iq_qmm(iq_ctx* ctx, void* stream, const void* x, int32_t x_dt
     c.accumulate = (flags & IQ_FLAG_ACCUMULATE) ? 1 : 0;
     return launch_qmm(ctx, cs, c);
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Prefill GEMM for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc at all: a plugin loaded into an engine whose memory pool owns
+// every device byte and forbids side allocations, a call site that runs after the pool has been sealed, or code under
+// a "no allocation after start-up" rule (real-time serving paths, sandboxes that filter the allocator entry points).
+// iq_qmm needs a scratch buffer when the activations are bf16 or fp32 (they are converted to fp16 first) and expects the
+// caller to bring it. This variant brings its own: a fixed array that is part of the library image, so it exists on
+// every GPU that loads the library, from load until the process exits, and costs that GPU kNoAllocBytes of memory.
+constexpr size_t kNoAllocBytes = 8u << 20;  // 8 MiB: rows * k <= 4,194,304 activations (e.g. 1024 x 4096)
+static __device__ __align__(256) unsigned char g_qmm_noalloc_scratch[kNoAllocBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {nullptr};  // device address of the array, per device, resolved on first use
+}  // namespace
+
+extern "C" int32_t iq_qmm_noalloc(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx,
+                                  const iq_qlinear* m, void* y, int32_t y_dtype, int64_t ldy, int32_t rows,
+                                  uint32_t flags) {
+    if (ctx == nullptr) return kErrInvalidArg;
+    if (m == nullptr) return fail(ctx, kErrInvalidArg, "qmm_noalloc: null pointer");
+    if (rows < 1 || m->k < 1) return fail(ctx, kErrInvalidArg, "qmm_noalloc: rows = %d, k = %d", rows, m->k);
+    const size_t need = (size_t)rows * (size_t)m->k * 2;
+    if (need > kNoAllocBytes)
+        return fail(ctx, kErrWorkspace,
+                    "qmm_noalloc: rows * k = %zu activations exceed the built-in scratch (%zu); use iq_qmm with a "
+                    "caller-provided workspace", (size_t)rows * (size_t)m->k, kNoAllocBytes / 2);
+    const int dev = ctx->device;
+    if (dev < 0 || dev >= kMaxDevices) return fail(ctx, kErrInvalidArg, "qmm_noalloc: device %d", dev);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        // The array's name is only a host-side handle here; the kernels need its address on this device. Resolved once
+        // per device with that device current (it is: the context selected it, and the caller runs on it).
+        int cur = -1;
+        cudaError_t e = cudaGetDevice(&cur);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "cudaGetDevice");
+        if (cur != dev) return fail(ctx, kErrInvalidArg, "qmm_noalloc: device %d is current, the context is on %d", cur, dev);
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_qmm_noalloc_scratch);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "cudaGetSymbolAddress(scratch)");
+        g_noalloc_ptr[dev] = p;
+    }
+    // Every byte the GEMM reads from the scratch is written by this call's own conversion pass first, so nothing has
+    // to be cleared; what the previous call left behind is simply overwritten.
+    return iq_qmm(ctx, stream, x, x_dtype, ldx, m, y, y_dtype, ldy, rows, flags, g_noalloc_ptr[dev], kNoAllocBytes);
+}

@@ -97,6 +97,20 @@ class DenseQ:
                                     y.data_ptr(), _dtype_id(y), y.stride(0), rows,
                                     capi.IQ_FLAG_ACCUMULATE if accumulate else 0, ws_ptr, ws_bytes))
 
+    def encode_qmm_noalloc(self, x: torch.Tensor, y: torch.Tensor, rows: int, accumulate: bool = False,
+                           stream: Optional[torch.cuda.Stream] = None):
+        """The prefill GEMM for callers that may not allocate device memory (a plugin inside an engine that owns the
+        memory pool, a sealed pool, a no-allocation rule): same results as `encode_qmm_f32`, with the fp16 copy of
+        bf16/fp32 activations kept in an 8 MiB array built into the library. rows * K must not exceed 4,194,304; calls
+        that may overlap on the GPU share that array and must be ordered on one stream; make the first call on a device
+        outside any stream capture."""
+        _need_cuda(x, y)
+        ctx = capi.context(self.device_index)
+        ql = self.qlinear()
+        ctx.check(capi.lib().iq_qmm_noalloc(ctx.handle, _stream_ptr(stream), x.data_ptr(), _dtype_id(x), x.stride(0),
+                                            C.byref(ql), y.data_ptr(), _dtype_id(y), y.stride(0), rows,
+                                            capi.IQ_FLAG_ACCUMULATE if accumulate else 0))
+
 
 class VQMV:
     """Decode GEMV launcher (Linear.swift:287-444)."""
