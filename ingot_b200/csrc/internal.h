@@ -60,6 +60,32 @@ struct GqmvCall {
     float limit = 0.f;
 };
 int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c);
+
+// One launch of the tensor-core GEMM (csrc/qmm.cu). x16: fp16 activations [x_rows, ldx]; w[i]: stacked
+// [experts * N, K] codes (w[1]: the up matrix of the gate/up epilogue). tiles == nullptr: dense tiling over M x N.
+struct QmmCall {
+    int32_t fmt = 0;
+    int epi = 0;   // 0 store, 1 gate/up + activation
+    int bn = 256;  // token rows per tile (MMA N): 128 or 256
+    const void* x16 = nullptr;
+    int64_t ldx = 0;
+    int64_t x_rows = 0;
+    const void* w[2] = {nullptr, nullptr};
+    const void* s[2] = {nullptr, nullptr};
+    const void* b[2] = {nullptr, nullptr};
+    int32_t experts = 1;
+    int32_t expert_lo = 0;
+    int32_t N = 0, K = 0, M = 0;
+    const Tile* tiles = nullptr;
+    const uint32_t* ntiles = nullptr;
+    void* y = nullptr;
+    int32_t y_dtype = 0;
+    int64_t ldy = 0;
+    int32_t accumulate = 0;
+    const float* ebias[2] = {nullptr, nullptr};
+    float limit = 0.f;
+};
+int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c);
 int32_t gqmv_init(iq_ctx* ctx);
 int32_t qmm_init(iq_ctx* ctx);
 int32_t moe_init(iq_ctx* ctx);

@@ -30,6 +30,7 @@ struct MoeWs {
     Tile* tiles_b;
     __half* h;
     float* yd;
+    __half* xs;  // activations in expert order, fp16 [P, d_model] (tensor-core path)
     size_t bytes;
 };
 
@@ -39,6 +40,7 @@ int decode_tile_rows(const iq_moe* l, int tokens) {
     return pairs <= (int64_t)l->d.experts * 6 ? 8 : 16;
 }
 constexpr int kPrefillTileRows = 128;
+constexpr int kTensorPathRowsPerExpert = 24;
 constexpr int kRouterSmemMax = 200 * 1024;
 
 MoeWs carve(const iq_moe* l, void* base, int tokens) {
@@ -63,6 +65,7 @@ MoeWs carve(const iq_moe* l, void* base, int tokens) {
     w.tiles_b = static_cast<Tile*>(take((d.experts + P / kPrefillTileRows + 1) * sizeof(Tile)));
     w.h = static_cast<__half*>(take(P * d.d_ff * 2));
     w.yd = static_cast<float*>(take(P * d.d_model * 4));
+    w.xs = static_cast<__half*>(take(P * d.d_model * 2));
     w.bytes = off;
     return w;
 }
@@ -149,6 +152,43 @@ int32_t run_down(iq_moe* l, cudaStream_t cs, const __half* h, const Tile* tiles,
     c.y = yd; c.y_dtype = yd_dtype; c.ldy = d.d_model;
     if (d.down_bias) c.ebias[0] = d.down_bias - lo * d.d_model;
     return launch_gqmv(l->ctx, cs, c);
+}
+
+// The experts run on the tcgen05 grouped GEMM once they see enough rows each for 128-row MMA tiles to pay; below
+// that the layer is bandwidth-bound and the GEMV-style tile kernels read each touched expert once.
+bool use_tensor_path(int64_t rows, int64_t expert_slots) { return rows >= expert_slots * kTensorPathRowsPerExpert; }
+
+int32_t run_gateup_tc(iq_moe* l, cudaStream_t cs, const __half* rows16, int64_t n_rows, const Tile* tiles,
+                      const uint32_t* ntiles, __half* h) {
+    const iq_moe_desc& d = l->d;
+    QmmCall c;
+    c.fmt = l->fmt; c.epi = 1; c.bn = kPrefillTileRows;
+    c.x16 = rows16; c.ldx = d.d_model; c.x_rows = n_rows;
+    c.w[0] = d.gate.w; c.w[1] = d.up.w;
+    c.s[0] = d.gate.scales; c.s[1] = d.up.scales;
+    c.b[0] = d.gate.biases; c.b[1] = d.up.biases;
+    c.experts = d.expert_count; c.expert_lo = d.expert_lo;
+    c.N = d.d_ff; c.K = d.d_model; c.M = (int32_t)n_rows;
+    c.tiles = tiles; c.ntiles = ntiles;
+    c.y = h; c.y_dtype = kF16; c.ldy = d.d_ff;
+    c.ebias[0] = d.gate_bias; c.ebias[1] = d.up_bias;
+    c.limit = d.act == IQ_ACT_SWIGLU_OAI ? d.act_limit : 0.f;
+    return launch_qmm(l->ctx, cs, c);
+}
+
+int32_t run_down_tc(iq_moe* l, cudaStream_t cs, const __half* h, int64_t n_rows, const Tile* tiles, const uint32_t* ntiles,
+                    void* yd, int32_t yd_dtype) {
+    const iq_moe_desc& d = l->d;
+    QmmCall c;
+    c.fmt = l->fmt; c.epi = 0; c.bn = kPrefillTileRows;
+    c.x16 = h; c.ldx = d.d_ff; c.x_rows = n_rows;
+    c.w[0] = d.down.w; c.s[0] = d.down.scales; c.b[0] = d.down.biases;
+    c.experts = d.expert_count; c.expert_lo = d.expert_lo;
+    c.N = d.d_model; c.K = d.d_ff; c.M = (int32_t)n_rows;
+    c.tiles = tiles; c.ntiles = ntiles;
+    c.y = yd; c.y_dtype = yd_dtype; c.ldy = d.d_model;
+    c.ebias[0] = d.down_bias;
+    return launch_qmm(l->ctx, cs, c);
 }
 
 }  // namespace
@@ -389,13 +429,22 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
     }
     const int64_t max_tiles64 = (int64_t)d.expert_count + P / bm;
     const int max_tiles = (int)(max_tiles64 < P ? max_tiles64 : P);
-    if (max_tiles > 65535) return fail(ctx, kErrInvalidArg, "moe: %d tokens give too many tiles for one launch", tokens);
+    if (max_tiles > 65535 && !use_tensor_path(P, d.expert_count))
+        return fail(ctx, kErrInvalidArg, "moe: %d tokens give too many tiles for one launch", tokens);
+    const bool tc = use_tensor_path(P, d.expert_count);
     if (pieces & IQ_PIECE_GATEUP) {
-        st = run_gateup(l, cs, x, x_dtype, ldx, w.row_map, w.tiles_a, w.ntiles, max_tiles, bm, w.h);
+        if (tc) {
+            moe_pack_rows_kernel<<<P, 256, 0, cs>>>(x, x_dtype, ldx, w.pos, w.xs, P, d.d_model, d.top_k);
+            st = check_cuda(ctx, cudaGetLastError(), "moe_pack_rows launch");
+            if (st == kOk) st = run_gateup_tc(l, cs, w.xs, P, w.tiles_b, w.ntiles + 1, w.h);
+        } else {
+            st = run_gateup(l, cs, x, x_dtype, ldx, w.row_map, w.tiles_a, w.ntiles, max_tiles, bm, w.h);
+        }
         if (st != kOk) return st;
     }
     if (pieces & IQ_PIECE_DOWN) {
-        st = run_down(l, cs, w.h, w.tiles_a, w.ntiles, max_tiles, bm, w.yd, kF32);
+        st = tc ? run_down_tc(l, cs, w.h, P, w.tiles_b, w.ntiles + 1, w.yd, kF32)
+                : run_down(l, cs, w.h, w.tiles_a, w.ntiles, max_tiles, bm, w.yd, kF32);
         if (st != kOk) return st;
     }
     if (pieces & IQ_PIECE_COMBINE) {
@@ -477,6 +526,14 @@ extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16,
         return fail(ctx, kErrWorkspace, "moe_experts: workspace %zu < %zu", workspace_bytes, w.bytes);
     cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
     const int64_t slots = (int64_t)sources * d.expert_count;
+    if (use_tensor_path(total_rows, slots)) {
+        ep_tiles_kernel<<<1, 512, 0, cs>>>(counts, sources, d.experts, d.expert_lo, d.expert_count, kPrefillTileRows, w.tiles,
+                                           w.ntiles);
+        int32_t st2 = check_cuda(ctx, cudaGetLastError(), "ep_tiles launch");
+        if (st2 == kOk) st2 = run_gateup_tc(l, cs, static_cast<const __half*>(rows_f16), total_rows, w.tiles, w.ntiles, w.h);
+        if (st2 == kOk) st2 = run_down_tc(l, cs, w.h, total_rows, w.tiles, w.ntiles, yd, yd_dtype);
+        return st2;
+    }
     const int bm = total_rows <= slots * 6 ? 8 : 16;
     ep_tiles_kernel<<<1, 512, 0, cs>>>(counts, sources, d.experts, d.expert_lo, d.expert_count, bm, w.tiles, w.ntiles);
     int32_t st = check_cuda(ctx, cudaGetLastError(), "ep_tiles launch");

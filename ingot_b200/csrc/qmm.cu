@@ -76,29 +76,6 @@ int32_t make_map_2d(iq_ctx* ctx, CUtensorMap* map, const void* base, bool f16, u
     return kOk;
 }
 
-// One launch of the tensor-core GEMM. x16: fp16 activations [x_rows, ldx]; w[i]: stacked [experts * N, K] codes.
-struct QmmCall {
-    int32_t fmt = 0;
-    int epi = kEpiStore;
-    int bn = 256;
-    const void* x16 = nullptr;
-    int64_t ldx = 0;
-    int64_t x_rows = 0;
-    const void* w[2] = {nullptr, nullptr};
-    const void* s[2] = {nullptr, nullptr};
-    const void* b[2] = {nullptr, nullptr};
-    int32_t experts = 1;
-    int32_t N = 0, K = 0, M = 0;
-    const Tile* tiles = nullptr;
-    const uint32_t* ntiles = nullptr;
-    void* y = nullptr;
-    int32_t y_dtype = 0;
-    int64_t ldy = 0;
-    int32_t accumulate = 0;
-    const float* ebias[2] = {nullptr, nullptr};
-    float limit = 0.f;
-};
-
 int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
     const KernelEntry* ke = find(c.fmt, c.bn, c.epi);
     if (ke == nullptr) return fail(ctx, kErrNoKernel, "qmm: no kernel for format %d, tile %d, epilogue %d", c.fmt, c.bn, c.epi);
@@ -118,7 +95,7 @@ int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
         p.b[i] = c.b[i] ? c.b[i] : c.b[0];
         p.ebias[i] = c.ebias[i];
     }
-    p.s_estride = 0;
+    p.expert_lo = c.expert_lo;
     p.N = c.N; p.K = c.K; p.M = c.M;
     p.tiles = c.tiles; p.ntiles = c.ntiles;
     p.y = c.y; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;

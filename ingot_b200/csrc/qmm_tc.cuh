@@ -37,7 +37,7 @@ struct QmmParams {
     // scales / biases are read straight from global memory by the dequantisers
     const void* s[2];
     const void* b[2];
-    int64_t s_estride;       // scale elements between experts
+    int32_t expert_lo;       // first expert held here: tile.expert - expert_lo indexes the stacked tensors
     int32_t N, K;            // weight rows per expert, inputs
     int32_t M;               // token rows (dense) / total sorted rows (grouped)
     // work list: null = dense tiling over (N / 128) x (M / BN)
@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
     auto decode = [&](int wi, uint32_t& expert, int& row0, int& rows, int& n0) {
         if (p.tiles != nullptr) {
             const Tile t = p.tiles[wi / n_tiles_n];
-            expert = t.expert; row0 = (int)t.start; rows = (int)t.count;
+            expert = t.expert - (uint32_t)p.expert_lo; row0 = (int)t.start; rows = (int)t.count;  // local slot
             n0 = (wi % n_tiles_n) * kWRows;
         } else {
             const int tm = wi % m_tiles;
@@ -296,10 +296,10 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                     if (c0 + j >= rows) break;
                     float v = __uint_as_float(r0[j]) + bias0;
                     if (EPI == kEpiGateUp) {
-                        // the reference's prefill kernels round gate and up to half before the activation
-                        // (GU_HALF, Shaders/qmm_nax_moe.metal:491-505)
-                        const float g = __half2float(__float2half_rn(v));
-                        const float u = __half2float(__float2half_rn(__uint_as_float(r1[j]) + bias1));
+                        // gate and up stay fp32 up to the activation (the reference's prefill kernels round them to
+                        // half first, GU_HALF, Shaders/qmm_nax_moe.metal:491-505: a storage choice, not needed here)
+                        const float g = v;
+                        const float u = __uint_as_float(r1[j]) + bias1;
                         v = p.limit > 0.f ? glu<kActSwigluOai>(g, u, p.limit) : glu<kActSilu>(g, u, 0.f);
                     }
                     const size_t o = (size_t)(row0 + c0 + j) * p.ldy + n;
