@@ -326,45 +326,91 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
         const int sw = row & 7;
         uint32_t it = 0;
         bool ok = true;
-        for (int wi = blockIdx.x; wi < total_work && ok; wi += gridDim.x) {
+        // Scales and biases come straight from global memory (L2 after the first token tile). They are fetched two K
+        // steps ahead into three rotating register sets, across work items too, so that their latency never sits
+        // between a stage becoming ready and its dequantisation.
+        struct SB { uint32_t sc[NWT], bi[NWT]; };
+        auto row_base = [&](int wi, bool& r_ok) -> size_t {
+            if (wi >= total_work) { r_ok = false; return 0; }
             uint32_t expert; int row0, rows, n0;
             decode(wi, expert, row0, rows, n0);
-            const bool r_ok = n0 + row < p.N;
-            const size_t srow = ((size_t)expert * p.N + (r_ok ? n0 + row : 0)) * row_groups;
-            for (int ks = 0; ks < ksteps; ks++, it++) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1;
-                // scales first: their latency hides behind the barrier waits
-                uint32_t sc[NWT], bi[NWT];
+            r_ok = n0 + row < p.N;
+            return ((size_t)expert * p.N + (r_ok ? n0 + row : 0)) * row_groups;
+        };
+        bool r_ok = false, r_ok_nx = false;
+        size_t srow = row_base(blockIdx.x, r_ok), srow_nx = 0;
+        auto fetch = [&](int ks, SB& v) {
+            const bool cur = ks < ksteps;
+            const size_t base = cur ? srow : srow_nx;
+            const bool live = cur ? r_ok : r_ok_nx;
+            const int k2 = cur ? ks : ks - ksteps;
 #pragma unroll
-                for (int wt = 0; wt < NWT; wt++) {
-                    if (FMT == kFmtMxfp4) {
-                        sc[wt] = r_ok ? ldg_nc_u8(reinterpret_cast<const unsigned char*>(p.s[wt]) + srow + 2 * ks + half)
-                                      : 127u;
-                        bi[wt] = 0;
-                    } else {
-                        sc[wt] = r_ok ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.s[wt]) + srow + ks) : 0u;
-                        bi[wt] = r_ok ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.b[wt]) + srow + ks) : 0u;
-                    }
+            for (int wt = 0; wt < NWT; wt++) {
+                if (FMT == kFmtMxfp4) {
+                    v.sc[wt] = live ? ldg_nc_u8(reinterpret_cast<const unsigned char*>(p.s[wt]) + base + 2 * k2 + half) : 127u;
+                    v.bi[wt] = 0;
+                } else {
+                    v.sc[wt] = live ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.s[wt]) + base + k2) : 0u;
+                    v.bi[wt] = live ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.b[wt]) + base + k2) : 0u;
                 }
-                if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag))) break;     // packed codes landed
-                if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag))) break;  // fp16 tile no longer read
-                unsigned char* st = smem + s * S::STAGE_BYTES;
-#pragma unroll
-                for (int wt = 0; wt < NWT; wt++) {
-                    const unsigned char* pk = st + S::X_BYTES + NWT * S::WD_BYTES + wt * S::WP_BYTES +
-                                              row * S::PACK_ROW + half * (S::PACK_ROW / 2);
-                    uint4 o[4];
-                    dequant32<FMT>(pk, sc[wt], bi[wt], o);
-                    unsigned char* wd = st + S::X_BYTES + wt * S::WD_BYTES + (row >> 3) * 1024 + sw * 128;
-#pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        *reinterpret_cast<uint4*>(wd + (((half * 4 + j) ^ sw) << 4)) = o[j];
-                }
-                fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async-proxy reads
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_ready + 8 * s);
             }
+        };
+        auto process = [&](const SB& v) -> bool {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            if (!mbar_wait(bar_full + 8 * s, ph, abort_flag)) return false;       // packed codes landed
+            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag)) return false;  // fp16 tile no longer read
+            unsigned char* st = smem + s * S::STAGE_BYTES;
+#pragma unroll
+            for (int wt = 0; wt < NWT; wt++) {
+                const unsigned char* pk = st + S::X_BYTES + NWT * S::WD_BYTES + wt * S::WP_BYTES + row * S::PACK_ROW +
+                                          half * (S::PACK_ROW / 2);
+                uint4 o[4];
+                dequant32<FMT>(pk, v.sc[wt], v.bi[wt], o);
+                unsigned char* wd = st + S::X_BYTES + wt * S::WD_BYTES + (row >> 3) * 1024 + sw * 128;
+#pragma unroll
+                for (int j = 0; j < 4; j++) *reinterpret_cast<uint4*>(wd + (((half * 4 + j) ^ sw) << 4)) = o[j];
+            }
+            fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async-proxy reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_ready + 8 * s);
+            it++;
+            return true;
+        };
+        SB A, B, C;
+        if (ksteps < 3) {  // too short to pipeline: fetch in place
+            for (int wi = blockIdx.x; wi < total_work && ok; wi += gridDim.x) {
+                srow = row_base(wi, r_ok);
+                for (int ks = 0; ks < ksteps && ok; ks++) {
+                    fetch(ks, A);
+                    ok = process(A);
+                }
+            }
+            total_work = 0;  // nothing left for the pipelined loop below
+        } else {
+            fetch(0, A);
+            fetch(1, B);
+        }
+        for (int wi = blockIdx.x; wi < total_work && ok; wi += gridDim.x) {
+            srow_nx = row_base(wi + gridDim.x, r_ok_nx);
+            for (int ks = 0; ks < ksteps && ok; ks += 3) {
+                fetch(ks + 2, C);
+                ok = process(A);
+                if (ok && ks + 1 < ksteps) {
+                    fetch(ks + 3, A);
+                    ok = process(B);
+                }
+                if (ok && ks + 2 < ksteps) {
+                    fetch(ks + 4, B);
+                    ok = process(C);
+                }
+            }
+            // leave the next item's steps 0 and 1 in A and B
+            const int rem = ksteps % 3;
+            if (rem == 1) { A = B; B = C; }
+            else if (rem == 2) { const SB t = A; A = C; B = t; }
+            srow = srow_nx;
+            r_ok = r_ok_nx;
         }
     }
 
