@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_ready + 8 * s, 8);
+            mbar_init(bar_ready + 8 * s, 4);  // the four warps of the dequantiser group that owns the step
             mbar_init(bar_empty + 8 * s, 1);
         }
         for (int a = 0; a < 2; a++) {
@@ -320,97 +320,96 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
             if (lane == 0) mbar_arrive(bar_tempty + 8 * a);
         }
     } else {
-        // ================= dequantisers (256 threads) =================
+        // ================= dequantisers (256 threads, two groups of four warps) =================
+        // Group g takes the K steps with (global step index) % 2 == g: one thread per weight row, both halves of the
+        // step. While one group waits for its stage, converts and publishes it, the other is half a period ahead, so the
+        // fixed latencies (barrier wait, shared-memory round trip, proxy fence) overlap instead of adding up.
         const int dt = threadIdx.x - 6 * 32;      // 0..255
-        const int row = dt >> 1, half = dt & 1;   // weight row inside the tile, which 32 inputs of the K step
+        const int grp = dt >> 7;                  // which half of the steps
+        const int row = dt & 127;                 // weight row inside the tile
         const int sw = row & 7;
-        uint32_t it = 0;
         bool ok = true;
-        // Scales and biases come straight from global memory (L2 after the first token tile). They are fetched two K
-        // steps ahead into three rotating register sets, across work items too, so that their latency never sits
-        // between a stage becoming ready and its dequantisation.
-        struct SB { uint32_t sc[NWT], bi[NWT]; };
-        auto row_base = [&](int wi, bool& r_ok) -> size_t {
-            if (wi >= total_work) { r_ok = false; return 0; }
-            uint32_t expert; int row0, rows, n0;
-            decode(wi, expert, row0, rows, n0);
-            r_ok = n0 + row < p.N;
-            return ((size_t)expert * p.N + (r_ok ? n0 + row : 0)) * row_groups;
+        struct SB { uint32_t sc[NWT][2], bi[NWT]; };   // mxfp4: two scale bytes per step, affine: one scale and bias
+        struct Cursor { int wi, ks; uint32_t lin; size_t srow; bool live; };
+        auto locate = [&](Cursor& c) {  // srow / live of the item c.wi
+            c.live = false;
+            c.srow = 0;
+            if (c.wi < total_work) {
+                uint32_t expert; int row0, rows, n0;
+                decode(c.wi, expert, row0, rows, n0);
+                c.live = n0 + row < p.N;
+                c.srow = ((size_t)expert * p.N + (c.live ? n0 + row : 0)) * row_groups;
+            }
         };
-        bool r_ok = false, r_ok_nx = false;
-        size_t srow = row_base(blockIdx.x, r_ok), srow_nx = 0;
-        auto fetch = [&](int ks, SB& v) {
-            const bool cur = ks < ksteps;
-            const size_t base = cur ? srow : srow_nx;
-            const bool live = cur ? r_ok : r_ok_nx;
-            const int k2 = cur ? ks : ks - ksteps;
+        auto advance = [&](Cursor& c) {  // two global steps forward
+            c.ks += 2;
+            c.lin += 2;
+            bool moved = false;
+            while (c.ks >= ksteps && c.wi < total_work) { c.ks -= ksteps; c.wi += gridDim.x; moved = true; }
+            if (moved) locate(c);
+        };
+        auto fetch = [&](const Cursor& c, SB& v) {
+            const bool live = c.live && c.wi < total_work;
 #pragma unroll
             for (int wt = 0; wt < NWT; wt++) {
                 if (FMT == kFmtMxfp4) {
-                    v.sc[wt] = live ? ldg_nc_u8(reinterpret_cast<const unsigned char*>(p.s[wt]) + base + 2 * k2 + half) : 127u;
+                    const unsigned char* sp = reinterpret_cast<const unsigned char*>(p.s[wt]) + c.srow + 2 * c.ks;
+                    v.sc[wt][0] = live ? ldg_nc_u8(sp) : 127u;
+                    v.sc[wt][1] = live ? ldg_nc_u8(sp + 1) : 127u;
                     v.bi[wt] = 0;
                 } else {
-                    v.sc[wt] = live ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.s[wt]) + base + k2) : 0u;
-                    v.bi[wt] = live ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.b[wt]) + base + k2) : 0u;
+                    v.sc[wt][0] = v.sc[wt][1] = live ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.s[wt]) + c.srow + c.ks) : 0u;
+                    v.bi[wt] = live ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.b[wt]) + c.srow + c.ks) : 0u;
                 }
             }
         };
-        auto process = [&](const SB& v) -> bool {
-            const int s = it % STAGES;
-            const uint32_t ph = (it / STAGES) & 1;
+        auto process = [&](const Cursor& c, const SB& v) -> bool {
+            const int s = c.lin % STAGES;
+            const uint32_t ph = (c.lin / STAGES) & 1;
             if (!mbar_wait(bar_full + 8 * s, ph, abort_flag)) return false;       // packed codes landed
             if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag)) return false;  // fp16 tile no longer read
             unsigned char* st = smem + s * S::STAGE_BYTES;
 #pragma unroll
             for (int wt = 0; wt < NWT; wt++) {
-                const unsigned char* pk = st + S::X_BYTES + NWT * S::WD_BYTES + wt * S::WP_BYTES + row * S::PACK_ROW +
-                                          half * (S::PACK_ROW / 2);
-                uint4 o[4];
-                dequant32<FMT>(pk, v.sc[wt], v.bi[wt], o);
                 unsigned char* wd = st + S::X_BYTES + wt * S::WD_BYTES + (row >> 3) * 1024 + sw * 128;
 #pragma unroll
-                for (int j = 0; j < 4; j++) *reinterpret_cast<uint4*>(wd + (((half * 4 + j) ^ sw) << 4)) = o[j];
+                for (int half = 0; half < 2; half++) {
+                    const unsigned char* pk = st + S::X_BYTES + NWT * S::WD_BYTES + wt * S::WP_BYTES + row * S::PACK_ROW +
+                                              half * (S::PACK_ROW / 2);
+                    uint4 o[4];
+                    dequant32<FMT>(pk, v.sc[wt][half], v.bi[wt], o);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) *reinterpret_cast<uint4*>(wd + (((half * 4 + j) ^ sw) << 4)) = o[j];
+                }
             }
             fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async-proxy reads
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_ready + 8 * s);
-            it++;
             return true;
         };
-        SB A, B, C;
-        if (ksteps < 3) {  // too short to pipeline: fetch in place
-            for (int wi = blockIdx.x; wi < total_work && ok; wi += gridDim.x) {
-                srow = row_base(wi, r_ok);
-                for (int ks = 0; ks < ksteps && ok; ks++) {
-                    fetch(ks, A);
-                    ok = process(A);
-                }
-            }
-            total_work = 0;  // nothing left for the pipelined loop below
-        } else {
-            fetch(0, A);
-            fetch(1, B);
+        // cursor of the step being converted and of the step whose scales are being fetched (two of this group's steps
+        // ahead); three register sets rotate between them
+        Cursor cur;
+        cur.wi = blockIdx.x; cur.ks = grp; cur.lin = grp;
+        {
+            bool moved = false;
+            while (cur.ks >= ksteps && cur.wi < total_work) { cur.ks -= ksteps; cur.wi += gridDim.x; moved = true; }
+            (void)moved;
+            locate(cur);
         }
-        for (int wi = blockIdx.x; wi < total_work && ok; wi += gridDim.x) {
-            srow_nx = row_base(wi + gridDim.x, r_ok_nx);
-            for (int ks = 0; ks < ksteps && ok; ks += 3) {
-                fetch(ks + 2, C);
-                ok = process(A);
-                if (ok && ks + 1 < ksteps) {
-                    fetch(ks + 3, A);
-                    ok = process(B);
-                }
-                if (ok && ks + 2 < ksteps) {
-                    fetch(ks + 4, B);
-                    ok = process(C);
-                }
-            }
-            // leave the next item's steps 0 and 1 in A and B
-            const int rem = ksteps % 3;
-            if (rem == 1) { A = B; B = C; }
-            else if (rem == 2) { const SB t = A; A = C; B = t; }
-            srow = srow_nx;
-            r_ok = r_ok_nx;
+        Cursor pf = cur;
+        SB A, B, C;
+        fetch(pf, A); advance(pf);
+        fetch(pf, B); advance(pf);
+        while (ok && cur.wi < total_work) {
+            fetch(pf, C); advance(pf);
+            ok = process(cur, A); advance(cur);
+            if (!ok || cur.wi >= total_work) break;
+            fetch(pf, A); advance(pf);
+            ok = process(cur, B); advance(cur);
+            if (!ok || cur.wi >= total_work) break;
+            fetch(pf, B); advance(pf);
+            ok = process(cur, C); advance(cur);
         }
     }
 
