@@ -82,11 +82,13 @@ __device__ __forceinline__ void load_x8(const void* x, int32_t dtype, size_t i, 
 // Gated FFN activation on fp32 values.
 template <int ACT>
 __device__ __forceinline__ float glu(float g, float u, float limit) {
+    // __expf / __fdividef: a few ulp, far inside the fp16 rounding that follows; the IEEE division alone was a
+    // noticeable share of the grouped GEMM's epilogue
     if (ACT == kActSilu) {
-        return g / (1.0f + __expf(-g)) * u;
+        return __fdividef(g, 1.0f + __expf(-g)) * u;
     } else {
         const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
-        return gc / (1.0f + __expf(-1.702f * gc)) * (uc + 1.0f);
+        return __fdividef(gc, 1.0f + __expf(-1.702f * gc)) * (uc + 1.0f);
     }
 }
 
@@ -110,6 +112,19 @@ __device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
 __device__ __forceinline__ uint32_t ldg_nc_u16(const void* p) {
     unsigned short r;
     asm("ld.global.nc.u16 %0, [%1];" : "=h"(r) : "l"(p));
+    return r;
+}
+
+// Prefetching variants: volatile, so the compiler keeps them where they are written (ahead of a barrier wait) instead
+// of sinking them to the first use.
+__device__ __forceinline__ uint32_t ldg_nc_u16_early(const void* p) {
+    unsigned short r;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(r) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ uint32_t ldg_nc_u8_early(const void* p) {
+    uint32_t r;
+    asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(r) : "l"(p));
     return r;
 }
 

@@ -39,8 +39,10 @@ int decode_tile_rows(const iq_moe* l, int tokens) {
     const int64_t pairs = (int64_t)tokens * l->d.top_k;
     return pairs <= (int64_t)l->d.experts * 6 ? 8 : 16;
 }
-constexpr int kPrefillTileRows = 128;
+constexpr int kPrefillTileRows = 128;      // token rows per tensor-core tile while experts see few rows
+constexpr int kPrefillTileRowsBig = 256;   // ... and once they see many: every weight tile is dequantised half as often
 constexpr int kTensorPathRowsPerExpert = 24;
+constexpr int kBigTileRowsPerExpert = 96;
 constexpr int kRouterSmemMax = 200 * 1024;
 
 MoeWs carve(const iq_moe* l, void* base, int tokens) {
@@ -157,12 +159,15 @@ int32_t run_down(iq_moe* l, cudaStream_t cs, const __half* h, const Tile* tiles,
 // The experts run on the tcgen05 grouped GEMM once they see enough rows each for 128-row MMA tiles to pay; below
 // that the layer is bandwidth-bound and the GEMV-style tile kernels read each touched expert once.
 bool use_tensor_path(int64_t rows, int64_t expert_slots) { return rows >= expert_slots * kTensorPathRowsPerExpert; }
+int tensor_tile_rows(int64_t rows, int64_t expert_slots) {
+    return rows >= expert_slots * kBigTileRowsPerExpert ? kPrefillTileRowsBig : kPrefillTileRows;
+}
 
 int32_t run_gateup_tc(iq_moe* l, cudaStream_t cs, const __half* rows16, int64_t n_rows, const Tile* tiles,
-                      const uint32_t* ntiles, __half* h) {
+                      const uint32_t* ntiles, __half* h, int bn) {
     const iq_moe_desc& d = l->d;
     QmmCall c;
-    c.fmt = l->fmt; c.epi = 1; c.bn = kPrefillTileRows;
+    c.fmt = l->fmt; c.epi = 1; c.bn = bn;
     c.x16 = rows16; c.ldx = d.d_model; c.x_rows = n_rows;
     c.w[0] = d.gate.w; c.w[1] = d.up.w;
     c.s[0] = d.gate.scales; c.s[1] = d.up.scales;
@@ -177,10 +182,10 @@ int32_t run_gateup_tc(iq_moe* l, cudaStream_t cs, const __half* rows16, int64_t 
 }
 
 int32_t run_down_tc(iq_moe* l, cudaStream_t cs, const __half* h, int64_t n_rows, const Tile* tiles, const uint32_t* ntiles,
-                    void* yd, int32_t yd_dtype) {
+                    void* yd, int32_t yd_dtype, int bn) {
     const iq_moe_desc& d = l->d;
     QmmCall c;
-    c.fmt = l->fmt; c.epi = 0; c.bn = kPrefillTileRows;
+    c.fmt = l->fmt; c.epi = 0; c.bn = bn;
     c.x16 = h; c.ldx = d.d_ff; c.x_rows = n_rows;
     c.w[0] = d.down.w; c.s[0] = d.down.scales; c.b[0] = d.down.biases;
     c.experts = d.expert_count; c.expert_lo = d.expert_lo;
@@ -420,7 +425,7 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
         GroupParams gp;
         gp.inds = inds; gp.counts = w.counts; gp.offsets = w.offsets; gp.row_map = w.row_map; gp.pos = w.pos;
         gp.tiles_a = w.tiles_a; gp.tiles_b = w.tiles_b; gp.ntiles = w.ntiles;
-        gp.P = P; gp.E = d.experts; gp.bm_a = bm; gp.bm_b = kPrefillTileRows;
+        gp.P = P; gp.E = d.experts; gp.bm_a = bm; gp.bm_b = tensor_tile_rows(P, d.expert_count);
         gp.e_lo = d.expert_lo; gp.e_hi = d.expert_lo + d.expert_count;
         moe_count_kernel<<<d.experts, 256, 0, cs>>>(gp);
         moe_scatter_kernel<<<d.experts, 256, 0, cs>>>(gp);
@@ -436,14 +441,14 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
         if (tc) {
             moe_pack_rows_kernel<<<P, 256, 0, cs>>>(x, x_dtype, ldx, w.pos, w.xs, P, d.d_model, d.top_k);
             st = check_cuda(ctx, cudaGetLastError(), "moe_pack_rows launch");
-            if (st == kOk) st = run_gateup_tc(l, cs, w.xs, P, w.tiles_b, w.ntiles + 1, w.h);
+            if (st == kOk) st = run_gateup_tc(l, cs, w.xs, P, w.tiles_b, w.ntiles + 1, w.h, tensor_tile_rows(P, d.expert_count));
         } else {
             st = run_gateup(l, cs, x, x_dtype, ldx, w.row_map, w.tiles_a, w.ntiles, max_tiles, bm, w.h);
         }
         if (st != kOk) return st;
     }
     if (pieces & IQ_PIECE_DOWN) {
-        st = tc ? run_down_tc(l, cs, w.h, P, w.tiles_b, w.ntiles + 1, w.yd, kF32)
+        st = tc ? run_down_tc(l, cs, w.h, P, w.tiles_b, w.ntiles + 1, w.yd, kF32, tensor_tile_rows(P, d.expert_count))
                 : run_down(l, cs, w.h, w.tiles_a, w.ntiles, max_tiles, bm, w.yd, kF32);
         if (st != kOk) return st;
     }
@@ -527,11 +532,11 @@ extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16,
     cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
     const int64_t slots = (int64_t)sources * d.expert_count;
     if (use_tensor_path(total_rows, slots)) {
-        ep_tiles_kernel<<<1, 512, 0, cs>>>(counts, sources, d.experts, d.expert_lo, d.expert_count, kPrefillTileRows, w.tiles,
-                                           w.ntiles);
+        const int bn = tensor_tile_rows(total_rows, slots);
+        ep_tiles_kernel<<<1, 512, 0, cs>>>(counts, sources, d.experts, d.expert_lo, d.expert_count, bn, w.tiles, w.ntiles);
         int32_t st2 = check_cuda(ctx, cudaGetLastError(), "ep_tiles launch");
-        if (st2 == kOk) st2 = run_gateup_tc(l, cs, static_cast<const __half*>(rows_f16), total_rows, w.tiles, w.ntiles, w.h);
-        if (st2 == kOk) st2 = run_down_tc(l, cs, w.h, total_rows, w.tiles, w.ntiles, yd, yd_dtype);
+        if (st2 == kOk) st2 = run_gateup_tc(l, cs, static_cast<const __half*>(rows_f16), total_rows, w.tiles, w.ntiles, w.h, bn);
+        if (st2 == kOk) st2 = run_down_tc(l, cs, w.h, total_rows, w.tiles, w.ntiles, yd, yd_dtype, bn);
         return st2;
     }
     const int bm = total_rows <= slots * 6 ? 8 : 16;

@@ -1,4 +1,6 @@
 // Host side of the tcgen05 GEMM: tensor maps, kernel selection, the iq_qmm entry point.
+#include <stdlib.h>
+
 #include "internal.h"
 #include "qmm_tc.cuh"
 
@@ -31,6 +33,7 @@ const KernelEntry* table(int* n) {
         entry<kFmtAffine8, 256, kEpiStore>(), entry<kFmtAffine8, 128, kEpiStore>(),
         entry<kFmtMxfp4, 256, kEpiStore>(),   entry<kFmtMxfp4, 128, kEpiStore>(),
         entry<kFmtAffine4, 128, kEpiGateUp>(), entry<kFmtMxfp4, 128, kEpiGateUp>(),
+        entry<kFmtAffine4, 256, kEpiGateUp>(), entry<kFmtMxfp4, 256, kEpiGateUp>(),
     };
     *n = (int)(sizeof(t) / sizeof(t[0]));
     return t;
@@ -101,6 +104,10 @@ int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
     p.y = c.y; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
     p.limit = c.limit;
     p.status = ctx->d_status;
+    {
+        const char* dbg = getenv("INGOT_QMM_DEBUG");
+        p.debug = dbg ? atoi(dbg) : 0;
+    }
     int grid = ctx->sms;
     if (c.tiles == nullptr) {
         const int work = ((c.M + c.bn - 1) / c.bn) * ((c.N + kWRows - 1) / kWRows);

@@ -12,7 +12,7 @@
 //               weight-row dimension, which is the fast dimension of Y)
 //   warps 6-13  dequantisers: packed codes (shared memory) -> fp16 w = fma(q, s, b) -> swizzled K-major tile
 // Stages are recycled by tcgen05.commit on an mbarrier; two accumulators in tensor memory let the epilogue of one
-// tile overlap the main loop of the next. Every wait is bounded: on a timeout the kernel writes a status word, all
+// tile overlap the main loop of the next (one accumulator when a tile needs all 512 columns: gate+up on 256 tokens). Every wait is bounded: on a timeout the kernel writes a status word, all
 // roles drain and tensor memory is released.
 //
 // Replaces qmm_t_nax3* (Shaders/qmm_nax_v3.metal:107-256) and, with a tile list, moe_gateup_swiglu2* / moe_down2*
@@ -51,6 +51,7 @@ struct QmmParams {
     const float* ebias[2];   // fp32 [E, N] or null
     float limit;
     int32_t* status;         // device status word (0 = ok)
+    int32_t debug;           // experiments: 1 = dequantisers publish without converting, 2 = producer loads no X tile
 };
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes
@@ -71,10 +72,11 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
 
 // ---- dequantisation of 32 consecutive inputs of one weight row into four 16-byte chunks --------------------------
 template <int FMT>
-__device__ __forceinline__ void dequant32(const unsigned char* packed_row_half, uint32_t sc_raw, uint32_t bi_raw,
-                                          uint4 (&out)[4]) {
+__device__ __forceinline__ void dequant32(uint32_t packed_row_half, uint32_t sc_raw, uint32_t bi_raw, uint4 (&out)[4]) {
+    // packed_row_half: shared-memory address (explicit shared-space loads: a generic load here costs the long latency
+    // path and showed up as the dequantisers' main stall)
     if (FMT == kFmtAffine4) {
-        const uint4 v = *reinterpret_cast<const uint4*>(packed_row_half);
+        const uint4 v = lds128(packed_row_half);
         const float s = bf16_bits_to_f32(sc_raw), b = bf16_bits_to_f32(bi_raw);
         const uint32_t s2 = pack_half2(s, s * 0.0625f), b2 = pack_half2(b, b);
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -92,8 +94,8 @@ __device__ __forceinline__ void dequant32(const unsigned char* packed_row_half, 
             out[i] = make_uint4(o[0], o[1], o[2], o[3]);
         }
     } else if (FMT == kFmtAffine8) {
-        const uint4 v0 = *reinterpret_cast<const uint4*>(packed_row_half);
-        const uint4 v1 = *reinterpret_cast<const uint4*>(packed_row_half + 16);
+        const uint4 v0 = lds128(packed_row_half);
+        const uint4 v1 = lds128(packed_row_half + 16);
         const float s = bf16_bits_to_f32(sc_raw), b = bf16_bits_to_f32(bi_raw);
         const uint32_t s2 = pack_half2(s, s), b2 = pack_half2(b, b);
         const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
@@ -110,7 +112,7 @@ __device__ __forceinline__ void dequant32(const unsigned char* packed_row_half, 
             out[i] = make_uint4(o[0], o[1], o[2], o[3]);
         }
     } else {
-        const uint4 v = *reinterpret_cast<const uint4*>(packed_row_half);
+        const uint4 v = lds128(packed_row_half);
         const DqConst d = make_dq<kFmtMxfp4>(sc_raw);
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -135,7 +137,8 @@ struct QmmSmem {
     static constexpr int STAGES = kMaxDyn / STAGE_BYTES > 6 ? 6 : kMaxDyn / STAGE_BYTES;
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
     static constexpr int ACC_COLS = NWT * BN;                             // tensor-memory columns per accumulator
-    static_assert(2 * ACC_COLS <= 512, "two accumulators must fit tensor memory");
+    static constexpr int NACC = 2 * ACC_COLS <= 512 ? 2 : 1;              // accumulators in tensor memory (512 columns)
+    static_assert(ACC_COLS <= 512, "the accumulator must fit tensor memory");
     static_assert(STAGES >= 2, "need at least two stages");
 };
 
@@ -219,10 +222,10 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                 for (int ks = 0; ks < ksteps; ks++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag))) break;
+                    if (!(ok = mbar_wait_relaxed(bar_empty + 8 * s, ph ^ 1, abort_flag))) break;
                     unsigned char* st = smem + s * S::STAGE_BYTES;
-                    mbar_arrive_expect_tx(bar_full + 8 * s, S::X_BYTES + NWT * S::WP_BYTES);
-                    tma_load_2d(smem_u32(st), &map_x, bar_full + 8 * s, ks * kBK, row0);
+                    mbar_arrive_expect_tx(bar_full + 8 * s, (p.debug == 2 ? 0 : S::X_BYTES) + NWT * S::WP_BYTES);
+                    if (p.debug != 2) tma_load_2d(smem_u32(st), &map_x, bar_full + 8 * s, ks * kBK, row0);
                     const int wrow = (int)expert * p.N + n0;
                     tma_load_2d(smem_u32(st + S::X_BYTES + NWT * S::WD_BYTES), &map_w0, bar_full + 8 * s,
                                 ks * S::PACK_ROW, wrow);
@@ -242,8 +245,8 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                 decode(wi, expert, row0, rows, n0);
                 const int nmma = min(BN, (rows + 15) & ~15);
                 const uint32_t idesc = make_idesc(nmma);
-                const int a = tcount & 1;
-                const uint32_t aph = (tcount >> 1) & 1;
+                const int a = tcount % S::NACC;
+                const uint32_t aph = (tcount / S::NACC) & 1;
                 if (!(ok = mbar_wait(bar_tempty + 8 * a, aph ^ 1, abort_flag))) break;
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + a * S::ACC_COLS;
@@ -275,9 +278,9 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
         for (int wi = blockIdx.x; wi < total_work && ok; wi += gridDim.x, tcount++) {
             uint32_t expert; int row0, rows, n0;
             decode(wi, expert, row0, rows, n0);
-            const int a = tcount & 1;
-            const uint32_t aph = (tcount >> 1) & 1;
-            if (!(ok = mbar_wait(bar_tfull + 8 * a, aph, abort_flag))) break;
+            const int a = tcount % S::NACC;
+            const uint32_t aph = (tcount / S::NACC) & 1;
+            if (!(ok = mbar_wait_relaxed(bar_tfull + 8 * a, aph, abort_flag))) break;
             tc_fence_after();
             const int n = n0 + 32 * q + lane;  // weight row = output feature of this thread
             const bool n_ok = n < p.N;
@@ -354,12 +357,12 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
             for (int wt = 0; wt < NWT; wt++) {
                 if (FMT == kFmtMxfp4) {
                     const unsigned char* sp = reinterpret_cast<const unsigned char*>(p.s[wt]) + c.srow + 2 * c.ks;
-                    v.sc[wt][0] = live ? ldg_nc_u8(sp) : 127u;
-                    v.sc[wt][1] = live ? ldg_nc_u8(sp + 1) : 127u;
+                    v.sc[wt][0] = live ? ldg_nc_u8_early(sp) : 127u;
+                    v.sc[wt][1] = live ? ldg_nc_u8_early(sp + 1) : 127u;
                     v.bi[wt] = 0;
                 } else {
-                    v.sc[wt][0] = v.sc[wt][1] = live ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.s[wt]) + c.srow + c.ks) : 0u;
-                    v.bi[wt] = live ? ldg_nc_u16(reinterpret_cast<const uint16_t*>(p.b[wt]) + c.srow + c.ks) : 0u;
+                    v.sc[wt][0] = v.sc[wt][1] = live ? ldg_nc_u16_early(reinterpret_cast<const uint16_t*>(p.s[wt]) + c.srow + c.ks) : 0u;
+                    v.bi[wt] = live ? ldg_nc_u16_early(reinterpret_cast<const uint16_t*>(p.b[wt]) + c.srow + c.ks) : 0u;
                 }
             }
         };
@@ -368,18 +371,19 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
             const uint32_t ph = (c.lin / STAGES) & 1;
             if (!mbar_wait(bar_full + 8 * s, ph, abort_flag)) return false;       // packed codes landed
             if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag)) return false;  // fp16 tile no longer read
-            unsigned char* st = smem + s * S::STAGE_BYTES;
+            const uint32_t st = smem_u32(smem + s * S::STAGE_BYTES);
 #pragma unroll
             for (int wt = 0; wt < NWT; wt++) {
-                unsigned char* wd = st + S::X_BYTES + wt * S::WD_BYTES + (row >> 3) * 1024 + sw * 128;
+                if (p.debug == 1) break;
+                const uint32_t wd = st + S::X_BYTES + wt * S::WD_BYTES + (row >> 3) * 1024 + sw * 128;
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
-                    const unsigned char* pk = st + S::X_BYTES + NWT * S::WD_BYTES + wt * S::WP_BYTES + row * S::PACK_ROW +
-                                              half * (S::PACK_ROW / 2);
+                    const uint32_t pk = st + S::X_BYTES + NWT * S::WD_BYTES + wt * S::WP_BYTES + row * S::PACK_ROW +
+                                        half * (S::PACK_ROW / 2);
                     uint4 o[4];
                     dequant32<FMT>(pk, v.sc[wt][half], v.bi[wt], o);
 #pragma unroll
-                    for (int j = 0; j < 4; j++) *reinterpret_cast<uint4*>(wd + (((half * 4 + j) ^ sw) << 4)) = o[j];
+                    for (int j = 0; j < 4; j++) sts128(wd + (((half * 4 + j) ^ sw) << 4), o[j]);
                 }
             }
             fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async-proxy reads
