@@ -177,6 +177,23 @@ def graph_time_us(torch, fn, n_in_graph: int, reps: int = 20) -> float:
     return e0.elapsed_time(e1) / (reps * n_in_graph) * 1e3
 
 
+def capture(torch, fn):
+    """Captures fn() (kernel launches only, no host synchronisation) into a CUDA graph and returns its replay: the step
+    then costs one launch on the host, which is what a serving loop does with a fixed-shape step."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            fn()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    return g.replay
+
+
 def bench_qmv(torch, dev, peaks):
     """Decode GEMV: x bf16 [1, 4096], W [14336, 4096] 4-bit g64; eight distinct weight copies (264 MB > L2) in rotation."""
     from ingot_b200 import synth
@@ -264,6 +281,21 @@ def run_ours(args):
         out_pinned.copy_(r, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
+    graphed = world == 1  # the expert-parallel exchange reads split sizes on the host: not capturable
+    if graphed:
+        step_graph = capture(torch, step)
+        fwd_graph = capture(torch, lambda: stack.forward(r, t_n))
+        step_eager = step
+
+        def step():
+            step_graph()
+
+        def step_e2e():  # noqa: F811
+            r.copy_(r0_pinned, non_blocking=True)
+            fwd_graph()
+            out_pinned.copy_(r, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -282,6 +314,8 @@ def run_ours(args):
             rd.copy_(rd0)
             stack.forward(rd, d_n)
 
+        if graphed:
+            step_dec = capture(torch, step_dec)
         ms_dec = time_steps(torch, dist, world, step_dec, max(args.steps, 3), args.warmup)
         dec = {"tokens": DECODE_TOKENS, "ms_per_step": round(ms_dec, 3), "tokens_per_s": round(DECODE_TOKENS / ms_dec * 1e3, 1)}
 
@@ -295,7 +329,7 @@ def run_ours(args):
             for l in stack.layers:
                 l.layer.encode(xn, r, t_n, only="gateup")
 
-        step()
+        step_eager()
         ms_gu = time_steps(torch, dist, 1, gateup_all, max(2, args.steps // 2), 1) / len(stack.layers)
         flops = 2.0 * t_n * TOPK * (2 * I) * D
         tf = flops / (ms_gu * 1e-3) / 1e12
@@ -318,7 +352,8 @@ def run_ours(args):
             "config": {"workload": f"{args.layers}-layer MoE FFN stack, prefill {T} tokens: 128 experts top-8 d_model 2048 "
                                    "d_ff 768 4-bit g64, r += MoE(RMSNorm(r))",
                        "parallelism": f"ep{world}" if world > 1 else "single", "tokens": T, "layers": args.layers,
-                       "l2": "per-step working set (weights of all layers) is far larger than L2"},
+                       "l2": "per-step working set (weights of all layers) is far larger than L2",
+                       "launch": "one CUDA graph per step" if graphed else "eager launches (host-planned exchange)"},
             "e2e": {"value": round(T / ms_e2e * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 3),
                     "h2d_bytes_per_step": int(t_n * D * 4), "d2h_bytes_per_step": int(t_n * D * 4)},
             "gpu_launches": launches_per_layer * args.layers * args.steps,

@@ -402,17 +402,21 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
     int32_t st;
 
     if ((pieces & IQ_PIECE_ROUTER) && l->ext_inds == nullptr) {
-        const int ee = d.experts < 256 ? d.experts : 256;
-        const size_t smem = (size_t)kRouterTT * d.d_model * 8 + (size_t)(256 / ee) * kRouterTT * ee * 8;
+        // experts per block: small ranges for few tokens (more blocks, shorter dot products per thread)
+        int eb = d.experts < 256 ? d.experts : 256;
+        if (tokens <= 16) eb = 8;
+        else if (tokens <= 256 && eb > 32) eb = 32;
+        while (d.experts % eb != 0) eb /= 2;
+        const size_t smem = (size_t)kRouterTT * d.d_model * 8 + (size_t)256 * kRouterTT * 8;
         if (smem > (size_t)kRouterSmemMax) return fail(ctx, kErrUnsupported, "moe: d_model = %d is too wide for the router kernel", d.d_model);
-        const int grid = (tokens + kRouterTT - 1) / kRouterTT;
+        const dim3 grid((tokens + kRouterTT - 1) / kRouterTT, d.experts / eb);
         if (d.router_kind == IQ_ROUTER_BF16)
             router_logits_kernel<0><<<grid, 256, smem, cs>>>(x, x_dtype, ldx, d.router_w, nullptr, nullptr, w.logits,
-                                                              tokens, d.experts, d.d_model, l->ld);
+                                                              tokens, d.experts, d.d_model, l->ld, eb);
         else
             router_logits_kernel<1><<<grid, 256, smem, cs>>>(x, x_dtype, ldx, d.router_w, d.router_scales,
                                                               d.router_biases, w.logits, tokens, d.experts, d.d_model,
-                                                              l->ld);
+                                                              l->ld, eb);
         st = check_cuda(ctx, cudaGetLastError(), "router_logits launch");
         if (st != kOk) return st;
     }

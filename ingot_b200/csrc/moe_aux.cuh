@@ -27,14 +27,16 @@ template <int WFMT>  // 0: bf16 dense router; 1: 8-bit affine g64 router
 __global__ void __launch_bounds__(256) router_logits_kernel(const void* __restrict__ x, int32_t x_dtype, int64_t ldx,
                                                             const void* __restrict__ wr, const void* __restrict__ ws,
                                                             const void* __restrict__ wb, float* __restrict__ logits,
-                                                            int T, int E, int D, int ld) {
+                                                            int T, int E, int D, int ld, int eb) {
+    // eb: experts per block (a power of two, at most 256); blockIdx.y picks the expert range. Few tokens take small
+    // ranges so that the dot products spread over many blocks and K slices.
     extern __shared__ __align__(16) unsigned char smem[];
     double* xs = reinterpret_cast<double*>(smem);                      // [TT][D]
     double* part = xs + (size_t)kRouterTT * D;                         // [slices][TT][ee]
     const int tid = threadIdx.x;
     const int t0 = blockIdx.x * kRouterTT;
     const int nt = min(kRouterTT, T - t0);
-    const int ee = min(E, 256);                 // experts handled per pass
+    const int ee = eb;                          // experts handled by this block
     const int slices = 256 / ee;                // k-slices per expert
     for (int i = tid; i < kRouterTT * D / 8; i += 256) {
         const int tt = i / (D / 8), ku = i % (D / 8);
@@ -51,8 +53,8 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const void* __restri
     const int el = tid % ee, sl = tid / ee;
     const int units = D / 8;                                  // 8-input units per row
     const int upw = (units + slices - 1) / slices;            // units per slice
-    for (int e0 = 0; e0 < E; e0 += ee) {
-        const int e = e0 + el;
+    {
+        const int e = blockIdx.y * ee + el;
         double acc[kRouterTT];
 #pragma unroll
         for (int tt = 0; tt < kRouterTT; tt++) acc[tt] = 0.0;
@@ -83,6 +85,7 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const void* __restri
                 }
 #pragma unroll
                 for (int tt = 0; tt < kRouterTT; tt++) {
+                    if (tt >= nt) break;
                     const double2* xp = reinterpret_cast<const double2*>(xs + (size_t)tt * D + u * 8);
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
@@ -113,9 +116,11 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const void* __restri
                 if (tt < nt) logits[(size_t)(t0 + tt) * ld + e] = (float)acc[tt];
         }
     }
-    for (int i = tid; i < kRouterTT * (ld - E); i += 256) {
-        const int tt = i / (ld - E), c = E + i % (ld - E);
-        if (tt < nt) logits[(size_t)(t0 + tt) * ld + c] = 0.f;
+    if (blockIdx.y == 0) {
+        for (int i = tid; i < kRouterTT * (ld - E); i += 256) {
+            const int tt = i / (ld - E), c = E + i % (ld - E);
+            if (tt < nt) logits[(size_t)(t0 + tt) * ld + c] = 0.f;
+        }
     }
 }
 
