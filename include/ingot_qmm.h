@@ -217,7 +217,9 @@ int32_t iq_moe_get_views(const iq_moe* layer, void* workspace, int32_t tokens, i
 int32_t iq_moe_pack_rows(iq_moe* layer, void* stream, const void* x, int32_t x_dtype, int64_t ldx, int32_t tokens,
                          void* workspace, size_t workspace_bytes, void* rows_f16);
 int32_t iq_moe_experts_workspace_bytes(const iq_moe* layer, int32_t max_rows, int32_t sources, size_t* bytes);
-/* Gate/up/activation/down of the layer's own experts on received rows. rows_f16: fp16 [total_rows, d_model];
+/* Gate/up/activation/down of the layer's own experts on received rows. rows_f16: fp16 [max_rows, d_model] of which
+ * the first sum(counts) rows are live; total_rows is the caller's (expected or exact) row count and only picks the
+ * kernels, every bound comes from max_rows and the device-side counts;
  * counts: device uint32 [sources, experts], counts[s*experts + e] = rows source s sent for expert e (rows are ordered
  * by source, then expert); yd: fp16 or fp32 [total_rows, d_model]. */
 int32_t iq_moe_experts(iq_moe* layer, void* stream, const void* rows_f16, int32_t total_rows, int32_t max_rows,
@@ -226,6 +228,31 @@ int32_t iq_moe_experts(iq_moe* layer, void* stream, const void* rows_f16, int32_
 /* out[t, :] (+)= sum_k wts[t, k] * yd_rows[pos[t*top_k + k], :] with the routing in `workspace`. */
 int32_t iq_moe_combine_rows(iq_moe* layer, void* stream, const void* yd_rows, int32_t yd_dtype, int32_t tokens, void* out,
                             int32_t out_dtype, int64_t ldo, uint32_t flags, void* workspace, size_t workspace_bytes);
+
+/* Device-side exchange: the same layer with no host involvement, so that a multi-layer step can live in one CUDA
+ * graph. The host allocates, once, four buffers per rank in memory every peer can address (cudaIpc / cuMem / torch
+ * symmetric memory) and passes the peers' addresses: recv (fp16 [max_rows, d_model] rows this rank computes), back
+ * (expert outputs returning, [tokens*top_k, d_model] of yd_dtype), flags (uint32 [world], zeroed) and counts (uint32
+ * [world, experts]). Per layer, on every rank, in stream order:
+ *   iq_moe_forward(ROUTER|ROUTE|GROUP); iq_ep_share_counts(offsets); iq_ep_barrier; iq_ep_plan; iq_ep_pack_push;
+ *   iq_ep_barrier; iq_moe_experts(recv, counts = own counts matrix); iq_ep_return_push; iq_ep_barrier;
+ *   iq_moe_combine_rows(back).
+ * Rows move with plain 16-byte peer stores (no TMA, no multicast). Every rank must run the same sequence; the barrier's
+ * wait is bounded (IQ_ERR_TIMEOUT in iq_ctx_status when a peer never arrives). At most 8 ranks. */
+typedef struct iq_ep iq_ep;
+int32_t iq_ep_create(iq_ctx* ctx, int32_t rank, int32_t world, int32_t experts, void* const* peer_recv,
+                     void* const* peer_back, void* const* peer_flags, void* const* peer_counts, iq_ep** out);
+void iq_ep_destroy(iq_ep* ep);
+/* Writes this rank's per-expert row counts (offsets[e+1] - offsets[e]) into row `rank` of every peer's counts matrix. */
+int32_t iq_ep_share_counts(iq_ep* ep, void* stream, const uint32_t* offsets);
+int32_t iq_ep_barrier(iq_ep* ep, void* stream);
+/* Derives the layer's send / receive offsets from this rank's counts matrix (after the barrier that follows sharing). */
+int32_t iq_ep_plan(iq_ep* ep, void* stream);
+/* fp16 rows of this rank's tokens, in expert order, stored straight into the owners' receive buffers. */
+int32_t iq_ep_pack_push(iq_ep* ep, void* stream, const void* x, int32_t x_dtype, int64_t ldx, int32_t tokens,
+                        int32_t top_k, int32_t d_model, const uint32_t* inds, const uint32_t* pos, const uint32_t* offsets);
+/* Expert outputs of the received rows stored back into each source's return buffer at the source's sorted positions. */
+int32_t iq_ep_return_push(iq_ep* ep, void* stream, const void* yd, int32_t yd_dtype, int32_t max_rows, int32_t d_model);
 
 /* ---- layer-stack helper ----------------------------------------------------------------------------------------------
  * out = x / sqrt(mean(x^2) + eps) per row, unit weight: the input normalisation between the fp32 residual and an FFN

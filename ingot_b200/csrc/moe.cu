@@ -539,16 +539,17 @@ extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16,
         const int bn = tensor_tile_rows(total_rows, slots);
         ep_tiles_kernel<<<1, 512, 0, cs>>>(counts, sources, d.experts, d.expert_lo, d.expert_count, bn, w.tiles, w.ntiles);
         int32_t st2 = check_cuda(ctx, cudaGetLastError(), "ep_tiles launch");
-        if (st2 == kOk) st2 = run_gateup_tc(l, cs, static_cast<const __half*>(rows_f16), total_rows, w.tiles, w.ntiles, w.h, bn);
-        if (st2 == kOk) st2 = run_down_tc(l, cs, w.h, total_rows, w.tiles, w.ntiles, yd, yd_dtype, bn);
+        // the row count is only known on the device: bounds come from the capacity, total_rows picks the kernels
+        if (st2 == kOk) st2 = run_gateup_tc(l, cs, static_cast<const __half*>(rows_f16), max_rows, w.tiles, w.ntiles, w.h, bn);
+        if (st2 == kOk) st2 = run_down_tc(l, cs, w.h, max_rows, w.tiles, w.ntiles, yd, yd_dtype, bn);
         return st2;
     }
     const int bm = total_rows <= slots * 6 ? 8 : 16;
     ep_tiles_kernel<<<1, 512, 0, cs>>>(counts, sources, d.experts, d.expert_lo, d.expert_count, bm, w.tiles, w.ntiles);
     int32_t st = check_cuda(ctx, cudaGetLastError(), "ep_tiles launch");
     if (st != kOk) return st;
-    const int64_t mt = total_rows / bm + slots;
-    const int max_tiles = (int)(mt < total_rows ? mt : total_rows);
+    const int64_t mt = max_rows / bm + slots;
+    const int max_tiles = (int)(mt < max_rows ? mt : max_rows);
     if (max_tiles > 65535) return fail(ctx, kErrInvalidArg, "moe_experts: too many tiles for one launch");
     st = run_gateup(l, cs, rows_f16, kF16, d.d_model, nullptr, w.tiles, w.ntiles, max_tiles, bm, w.h);
     if (st != kOk) return st;

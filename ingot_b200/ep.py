@@ -78,9 +78,33 @@ class ExpertParallelMoE:
                 "ws": torch.empty(layer.experts_workspace_bytes(max_rows, self.world), dtype=torch.uint8, device=dev),
             }
 
+    def use_device_exchange(self, dx: "DeviceExchange"):
+        """Switches the layer to the device-side exchange (`dx` is shared by the layers of a stack). The kernels are
+        picked for the rows this rank expects to receive (as many as it sends: rows * top_k); capacity stays max_rows."""
+        self.dx = dx
+        if "yd_dx" not in self.buf:
+            self.buf["yd_dx"] = torch.empty(self.max_rows, self.layer.D, dtype=dx.yd_dtype, device=self.layer.device)
+
+    def _encode_device(self, x, out, rows, accumulate):
+        L, b, dx = self.layer, self.buf, self.dx
+        L.encode(x, out, rows, only=("router", "route", "group"))
+        v = L.views(rows)
+        dx.share_counts(v["offsets"])
+        dx.barrier()
+        dx.plan()
+        dx.pack_push(x, rows, L.router.top_k, v["inds"], v["pos"], v["offsets"])
+        dx.barrier()
+        L.experts(dx.recv, min(rows * L.router.top_k, self.max_rows), dx.counts, self.world, b["yd_dx"], b["ws"])
+        dx.return_push(b["yd_dx"])
+        dx.barrier()
+        L.combine_rows(dx.back, out, rows, accumulate=accumulate)
+
     def encode(self, x: torch.Tensor, out: torch.Tensor, rows: int, accumulate: bool = False):
         if self.world == 1:
             self.layer.encode(x, out, rows, accumulate=accumulate)
+            return
+        if getattr(self, "dx", None) is not None:
+            self._encode_device(x, out, rows, accumulate)
             return
         L, b = self.layer, self.buf
         k = L.router.top_k
@@ -98,6 +122,71 @@ class ExpertParallelMoE:
         L.experts(b["recv"], R, b["counts_all"], self.world, b["yd"], b["ws"])
         dist.all_to_all_single(b["back"][:P], b["yd"][:R], send, recv, group=self.group)
         L.combine_rows(b["back"], out, rows, accumulate=accumulate)
+
+
+class DeviceExchange:
+    """The expert-parallel exchange done by this library's own kernels over NVLink peer memory: rows are stored straight
+    into the owners' buffers, sizes are exchanged and read on the device, ranks meet at a flag barrier in peer memory.
+    No host synchronisation and no library collective inside a layer, so a whole multi-layer step can be captured in one
+    CUDA graph. Peer-addressable buffers come from torch's symmetric memory (plain peer pointers; multicast is not used).
+    """
+
+    def __init__(self, experts: int, top_k: int, d_model: int, max_local_tokens: int, max_rows: int,
+                 yd_dtype: torch.dtype, device: torch.device, group=None):
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.max_rows, self.yd_dtype, self.d_model = max_rows, yd_dtype, d_model
+        esz = torch.empty((), dtype=yd_dtype).element_size()
+        P = max_local_tokens * top_k
+        sizes = [max_rows * d_model * 2, P * d_model * esz, 256, self.world * experts * 4]
+        self._bufs, self._hdls, ptrs = [], [], []
+        for n in sizes:
+            t = symm_mem.empty((n + 255) // 256 * 256, dtype=torch.uint8, device=device)
+            t.zero_()
+            h = symm_mem.rendezvous(t, group)
+            self._bufs.append(t)
+            self._hdls.append(h)
+            ptrs.append([int(p) for p in h.buffer_ptrs])
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        self.recv = self._bufs[0].view(torch.float16)[: max_rows * d_model].view(max_rows, d_model)
+        self.back = self._bufs[1].view(yd_dtype)[: P * d_model].view(P, d_model)
+        self.counts = self._bufs[3].view(torch.int32)[: self.world * experts].view(self.world, experts)
+        self.ctx = capi.context(device.index or 0)
+        arr = lambda v: (C.c_void_p * self.world)(*v)
+        self._h = C.c_void_p()
+        self.ctx.check(capi.lib().iq_ep_create(self.ctx.handle, self.rank, self.world, experts, arr(ptrs[0]), arr(ptrs[1]),
+                                               arr(ptrs[2]), arr(ptrs[3]), C.byref(self._h)))
+
+    def share_counts(self, offsets: torch.Tensor, stream=None):
+        self.ctx.check(capi.lib().iq_ep_share_counts(self._h, _stream_ptr(stream), offsets.data_ptr()))
+
+    def barrier(self, stream=None):
+        self.ctx.check(capi.lib().iq_ep_barrier(self._h, _stream_ptr(stream)))
+
+    def plan(self, stream=None):
+        self.ctx.check(capi.lib().iq_ep_plan(self._h, _stream_ptr(stream)))
+
+    def pack_push(self, x: torch.Tensor, tokens: int, top_k: int, inds: torch.Tensor, pos: torch.Tensor,
+                  offsets: torch.Tensor, stream=None):
+        dt = {torch.float32: capi.IQ_F32, torch.float16: capi.IQ_F16, torch.bfloat16: capi.IQ_BF16}[x.dtype]
+        self.ctx.check(capi.lib().iq_ep_pack_push(self._h, _stream_ptr(stream), x.data_ptr(), dt, x.stride(0), tokens, top_k,
+                                                  self.d_model, inds.data_ptr(), pos.data_ptr(), offsets.data_ptr()))
+
+    def return_push(self, yd: torch.Tensor, stream=None):
+        dt = capi.IQ_F32 if yd.dtype == torch.float32 else capi.IQ_F16
+        self.ctx.check(capi.lib().iq_ep_return_push(self._h, _stream_ptr(stream), yd.data_ptr(), dt, self.max_rows,
+                                                    self.d_model))
+
+    def close(self):
+        if self._h:
+            capi.lib().iq_ep_destroy(self._h)
+            self._h = C.c_void_p()
 
 
 def rmsnorm(x: torch.Tensor, out: torch.Tensor, rows: int, eps: float = 1e-6, stream=None):
