@@ -97,6 +97,12 @@ class ClockSampler:
 # GPU arm
 
 
+def RETURN_DTYPE(torch):
+    """Element type of the expert outputs on the way back to the tokens' ranks (N > 1). fp16 is what the reference
+    stores between its down projection and its combine for affine experts (yd, MoEPrefill.swift:159-160)."""
+    return torch.float16
+
+
 def build_stack(torch, dev, rank: int, world: int, max_local_tokens: int, layers: int):
     """The stack's weights, seeded per layer and identical whatever the number of ranks: every rank draws the full
     expert tensors of a layer on its device and keeps its own contiguous slice."""
@@ -126,7 +132,7 @@ def build_stack(torch, dev, rank: int, world: int, max_local_tokens: int, layers
         if first_ep is None:
             first_ep = epl
             if world > 1:  # rows move by the library's own peer stores; nothing in a layer touches the host
-                dx = ep.DeviceExchange(E, TOPK, D, max_local_tokens, PREFILL_TOKENS * TOPK, torch.float32, dev)
+                dx = ep.DeviceExchange(E, TOPK, D, max_local_tokens, RETURN_DTYPE(torch), dev)
         if world > 1:
             epl.use_device_exchange(dx)
         out.append(epl)
@@ -260,7 +266,7 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl")
+        dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
     T = args.tokens
     t_lo, t_n = ep.token_slice(rank, world, T)
@@ -375,7 +381,7 @@ def run_ours(args):
         dist.barrier()
         dist.destroy_process_group()
     if line is not None:
-        print(json.dumps(line), flush=True)
+        emit(line)
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -442,7 +448,28 @@ def run_reference(args):
         "note": "ingot has no CPU or CUDA implementation to install (Swift + Metal only); this arm runs the C restatement "
                 "of its fp32 semantics kept under oracle/",
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_RESULT_FD = None
+
+
+def claim_stdout():
+    """The one line on stdout is the result: everything else a library prints there (NCCL's version banner, for one)
+    goes to stderr. File descriptor 1 is pointed at stderr and the original kept for emit()."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line: dict):
+    data = (json.dumps(line) + "\n").encode()
+    sys.stdout.flush()
+    if _RESULT_FD is None:
+        os.write(1, data)
+    else:
+        os.write(_RESULT_FD, data)
 
 
 def main():
@@ -455,6 +482,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--cpu-tokens", type=int, default=1024, help="tokens of the bounded CPU sample")
     args = ap.parse_args()
+    claim_stdout()
     if args.impl == "reference":
         run_reference(args)
     else:

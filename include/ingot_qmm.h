@@ -221,38 +221,59 @@ int32_t iq_moe_experts_workspace_bytes(const iq_moe* layer, int32_t max_rows, in
  * the first sum(counts) rows are live; total_rows is the caller's (expected or exact) row count and only picks the
  * kernels, every bound comes from max_rows and the device-side counts;
  * counts: device uint32 [sources, experts], counts[s*experts + e] = rows source s sent for expert e (rows are ordered
- * by source, then expert); yd: fp16 or fp32 [total_rows, d_model]. */
+ * by source, then expert: packed one source after the other when region_rows == 0, or source s starting at row
+ * s*region_rows); yd: fp16 or fp32, same row positions. yd_rows (device array of max_rows addresses, or null): when
+ * given, the output of row r goes to yd_rows[r] (d_model elements of yd_dtype, 16-byte aligned, any memory this GPU can
+ * store to, a peer's included; 0 = row unused) and yd is scratch. */
 int32_t iq_moe_experts(iq_moe* layer, void* stream, const void* rows_f16, int32_t total_rows, int32_t max_rows,
-                       const uint32_t* counts, int32_t sources, void* yd, int32_t yd_dtype, void* workspace,
-                       size_t workspace_bytes);
+                       const uint32_t* counts, int32_t sources, int32_t region_rows, void* yd, int32_t yd_dtype,
+                       void* const* yd_rows, void* workspace, size_t workspace_bytes);
 /* out[t, :] (+)= sum_k wts[t, k] * yd_rows[pos[t*top_k + k], :] with the routing in `workspace`. */
 int32_t iq_moe_combine_rows(iq_moe* layer, void* stream, const void* yd_rows, int32_t yd_dtype, int32_t tokens, void* out,
                             int32_t out_dtype, int64_t ldo, uint32_t flags, void* workspace, size_t workspace_bytes);
 
 /* Device-side exchange: the same layer with no host involvement, so that a multi-layer step can live in one CUDA
  * graph. The host allocates, once, four buffers per rank in memory every peer can address (cudaIpc / cuMem / torch
- * symmetric memory) and passes the peers' addresses: recv (fp16 [max_rows, d_model] rows this rank computes), back
- * (expert outputs returning, [tokens*top_k, d_model] of yd_dtype), flags (uint32 [world], zeroed) and counts (uint32
+ * symmetric memory) and passes the peers' addresses: recv (fp16 [world * region_rows, d_model]: region s holds the rows
+ * source rank s sends, in local-expert order, so region_rows >= the largest tokens*top_k of any rank), back (expert
+ * outputs returning, [tokens*top_k, d_model] of yd_dtype), flags (uint32 [world], zeroed) and counts (uint32
  * [world, experts]). Per layer, on every rank, in stream order:
- *   iq_moe_forward(ROUTER|ROUTE|GROUP); iq_ep_share_counts(offsets); iq_ep_barrier; iq_ep_plan; iq_ep_pack_push;
- *   iq_ep_barrier; iq_moe_experts(recv, counts = own counts matrix); iq_ep_return_push; iq_ep_barrier;
+ *   iq_moe_forward(ROUTER|ROUTE|GROUP); iq_ep_pack_push; iq_ep_barrier(then_plan = 1);
+ *   iq_moe_experts(recv, counts = own counts matrix, region_rows); iq_ep_return_push; iq_ep_barrier(0);
+ *   (or, faster: iq_ep_compact, then iq_moe_experts(compacted rows, merged counts, 1 source, yd_rows = table), and no
+ *   iq_ep_return_push: the down projection stores its rows straight into the sources' return buffers)
  *   iq_moe_combine_rows(back).
  * Rows move with plain 16-byte peer stores (no TMA, no multicast). Every rank must run the same sequence; the barrier's
  * wait is bounded (IQ_ERR_TIMEOUT in iq_ctx_status when a peer never arrives). At most 8 ranks. */
 typedef struct iq_ep iq_ep;
-int32_t iq_ep_create(iq_ctx* ctx, int32_t rank, int32_t world, int32_t experts, void* const* peer_recv,
-                     void* const* peer_back, void* const* peer_flags, void* const* peer_counts, iq_ep** out);
+int32_t iq_ep_create(iq_ctx* ctx, int32_t rank, int32_t world, int32_t experts, int32_t region_rows,
+                     void* const* peer_recv, void* const* peer_back, void* const* peer_flags, void* const* peer_counts,
+                     iq_ep** out);
 void iq_ep_destroy(iq_ep* ep);
-/* Writes this rank's per-expert row counts (offsets[e+1] - offsets[e]) into row `rank` of every peer's counts matrix. */
+/* Writes this rank's per-expert row counts (offsets[e+1] - offsets[e]) into row `rank` of every peer's counts matrix
+ * (iq_ep_pack_push does the same; this entry point serves hosts that move the rows themselves). */
 int32_t iq_ep_share_counts(iq_ep* ep, void* stream, const uint32_t* offsets);
-int32_t iq_ep_barrier(iq_ep* ep, void* stream);
-/* Derives the layer's send / receive offsets from this rank's counts matrix (after the barrier that follows sharing). */
+/* All ranks meet; with then_plan != 0 the kernel then derives the return-path plan from the completed counts matrix. */
+int32_t iq_ep_barrier(iq_ep* ep, void* stream, int32_t then_plan);
+/* The plan alone (after a barrier that followed the sharing of the counts). */
 int32_t iq_ep_plan(iq_ep* ep, void* stream);
-/* fp16 rows of this rank's tokens, in expert order, stored straight into the owners' receive buffers. */
+/* fp16 rows of this rank's tokens, in expert order, stored straight into region `rank` of the owners' receive buffers,
+ * together with this rank's counts; needs nothing from the peers. tokens*top_k <= region_rows. */
 int32_t iq_ep_pack_push(iq_ep* ep, void* stream, const void* x, int32_t x_dtype, int64_t ldx, int32_t tokens,
                         int32_t top_k, int32_t d_model, const uint32_t* inds, const uint32_t* pos, const uint32_t* offsets);
-/* Expert outputs of the received rows stored back into each source's return buffer at the source's sorted positions. */
-int32_t iq_ep_return_push(iq_ep* ep, void* stream, const void* yd, int32_t yd_dtype, int32_t max_rows, int32_t d_model);
+/* Expert outputs of the received rows ([world * region_rows, d_model], the layout of recv) stored back into each
+ * source's return buffer at the source's sorted positions. */
+int32_t iq_ep_return_push(iq_ep* ep, void* stream, const void* yd, int32_t yd_dtype, int32_t d_model);
+/* The same mapping as a table for iq_moe_experts' yd_rows (device array of world * region_rows addresses): the down
+ * projection then stores each output row straight into its source rank's return buffer and no copy kernel runs. */
+int32_t iq_ep_return_rows(iq_ep* ep, void* stream, int32_t yd_dtype, int32_t d_model, void** table);
+/* Received rows gathered out of their regions into expert-major order (rows_out, fp16 [world * region_rows, d_model]):
+ * all sources' rows of one expert end up next to each other, so the grouped GEMM dequantises each weight tile once per
+ * expert rather than once per (source, expert). table gets the return address of every compacted row (for yd_rows);
+ * *merged_counts is a device array [experts] of this rank's per-expert row totals: pass it to iq_moe_experts as counts
+ * with sources = 1, region_rows = 0. After iq_ep_barrier(then_plan = 1). */
+int32_t iq_ep_compact(iq_ep* ep, void* stream, const void* recv_rows, int32_t d_model, int32_t yd_dtype, void* rows_out,
+                      void** table, const uint32_t** merged_counts);
 
 /* ---- layer-stack helper ----------------------------------------------------------------------------------------------
  * out = x / sqrt(mean(x^2) + eps) per row, unit weight: the input normalisation between the fp32 residual and an FFN

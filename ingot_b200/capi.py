@@ -22,7 +22,7 @@ SYMBOLS = [
     "iq_moe_destroy", "iq_moe_workspace_bytes", "iq_moe_forward", "iq_moe_route", "iq_moe_set_external_routing",
     "iq_moe_get_views", "iq_moe_pack_rows", "iq_moe_experts_workspace_bytes", "iq_moe_experts", "iq_moe_combine_rows",
     "iq_rmsnorm", "iq_qmm_noalloc", "iq_ep_create", "iq_ep_destroy", "iq_ep_share_counts", "iq_ep_barrier", "iq_ep_plan",
-    "iq_ep_pack_push", "iq_ep_return_push",
+    "iq_ep_pack_push", "iq_ep_return_push", "iq_ep_return_rows", "iq_ep_compact",
 ]
 
 
@@ -91,20 +91,22 @@ def lib() -> C.CDLL:
         l.iq_moe_get_views.argtypes = [vp, vp, i32, C.POINTER(MoeViews)]
         l.iq_qmm_noalloc.argtypes = [vp, vp, vp, i32, i64, C.POINTER(QLinear), vp, i32, i64, i32, u32]
         l.iq_qmm_noalloc.restype = i32
-        l.iq_ep_create.argtypes = [vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]
+        l.iq_ep_create.argtypes = [vp, i32, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]
         l.iq_ep_destroy.argtypes = [vp]
         l.iq_ep_destroy.restype = None
         l.iq_ep_share_counts.argtypes = [vp, vp, vp]
-        l.iq_ep_barrier.argtypes = [vp, vp]
+        l.iq_ep_barrier.argtypes = [vp, vp, i32]
         l.iq_ep_plan.argtypes = [vp, vp]
         l.iq_ep_pack_push.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, vp, vp, vp]
-        l.iq_ep_return_push.argtypes = [vp, vp, vp, i32, i32, i32]
+        l.iq_ep_return_push.argtypes = [vp, vp, vp, i32, i32]
+        l.iq_ep_return_rows.argtypes = [vp, vp, i32, i32, vp]
+        l.iq_ep_compact.argtypes = [vp, vp, vp, i32, i32, vp, vp, C.POINTER(vp)]
         for name in ("iq_ep_create", "iq_ep_share_counts", "iq_ep_barrier", "iq_ep_plan", "iq_ep_pack_push",
-                     "iq_ep_return_push"):
+                     "iq_ep_return_push", "iq_ep_return_rows", "iq_ep_compact"):
             getattr(l, name).restype = i32
         l.iq_moe_pack_rows.argtypes = [vp, vp, vp, i32, i64, i32, vp, sz, vp]
         l.iq_moe_experts_workspace_bytes.argtypes = [vp, i32, i32, C.POINTER(sz)]
-        l.iq_moe_experts.argtypes = [vp, vp, vp, i32, i32, vp, i32, vp, i32, vp, sz]
+        l.iq_moe_experts.argtypes = [vp, vp, vp, i32, i32, vp, i32, i32, vp, i32, vp, vp, sz]
         l.iq_moe_combine_rows.argtypes = [vp, vp, vp, i32, i32, vp, i32, i64, u32, vp, sz]
         l.iq_rmsnorm.argtypes = [vp, vp, vp, i64, vp, i32, i64, i32, i32, C.c_float]
         for name in ("iq_moe_pack_rows", "iq_moe_experts_workspace_bytes", "iq_moe_experts", "iq_moe_combine_rows",

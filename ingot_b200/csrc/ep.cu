@@ -19,49 +19,30 @@ namespace {
 constexpr int kMaxRanks = 8;
 constexpr int kMaxSegs = kMaxRanks * 512;
 
-// Per-layer plan derived from counts[s * E + e] (rows rank s routes to expert e), for rank `rank`:
-//   send_off[d]   first row of this rank's segment inside rank d's receive buffer
-//   recv_off[s]   first row of source s's segment inside this rank's receive buffer; recv_off[world] = total
-//   seg_recv[s * El + j] / seg_src[s * El + j]: where the rows of (source s, local expert j) start in this rank's
-//   receive buffer and in source s's expert-sorted list
+// Receive-buffer layout: every source rank owns a fixed region of region_rows rows in each peer's receive buffer, so a
+// rank can push its rows without knowing what the other sources send. Inside region s the rows are in local-expert
+// order. Per-layer plan of rank `rank`, derived from counts[s * E + e] (rows rank s routes to expert e):
+//   from[s]                 rows received from source s
+//   seg_recv[s * El + j]    first row of (source s, local expert j) in this rank's receive buffer
+//   seg_src[s * El + j]     position of that segment in source s's expert-sorted list
+//   seg_dst[s * El + j]     where that segment goes when the rows are compacted expert-major (all sources' rows of one
+//                           expert next to each other, so that the grouped GEMM sees one run of rows per expert)
+//   merged[e]               rows of expert e over all sources (global expert index; zero outside this rank's range)
 struct EpPlan {
-    uint32_t send_off[kMaxRanks];
-    uint32_t recv_off[kMaxRanks + 1];
-    uint32_t seg_recv[kMaxSegs + 1];
+    uint32_t from[kMaxRanks];
+    uint32_t seg_recv[kMaxSegs];
     uint32_t seg_src[kMaxSegs];
+    uint32_t seg_dst[kMaxSegs];
+    uint32_t merged[kMaxSegs];
 };
 
-__global__ void __launch_bounds__(256) ep_plan_kernel(const uint32_t* __restrict__ counts, int rank, int world, int E,
-                                                      EpPlan* __restrict__ plan) {
+// One block of any size.
+__device__ __forceinline__ void ep_plan_body(const uint32_t* __restrict__ counts, int rank, int world, int E,
+                                             uint32_t region_rows, EpPlan* __restrict__ plan) {
     const int El = E / world;
-    __shared__ uint32_t tot[kMaxRanks][kMaxRanks];  // tot[s][d] = rows s -> d
-    for (int i = threadIdx.x; i < world * world; i += 256) {
-        const int s = i / world, d = i % world;
-        uint32_t t = 0;
-        for (int e = d * El; e < (d + 1) * El; e++) t += counts[s * E + e];
-        tot[s][d] = t;
-    }
-    __syncthreads();
-    if (threadIdx.x < world) {
-        const int d = threadIdx.x;
-        uint32_t o = 0;
-        for (int s = 0; s < rank; s++) o += tot[s][d];
-        plan->send_off[d] = o;
-    }
-    if (threadIdx.x == 0) {
-        uint32_t o = 0;
-        for (int s = 0; s < world; s++) {
-            plan->recv_off[s] = o;
-            o += tot[s][rank];
-        }
-        plan->recv_off[world] = o;
-    }
-    // segments (source, local expert): one thread per source walks its local experts
-    if (threadIdx.x < world) {
+    if ((int)threadIdx.x < world) {
         const int s = threadIdx.x;
-        uint32_t r = 0;
-        for (int s2 = 0; s2 < s; s2++) r += tot[s2][rank];
-        uint32_t src = 0;
+        uint32_t r = s * region_rows, src = 0;
         for (int e = 0; e < rank * El; e++) src += counts[s * E + e];
         for (int j = 0; j < El; j++) {
             plan->seg_recv[s * El + j] = r;
@@ -70,24 +51,52 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(const uint32_t* __restrict
             r += c;
             src += c;
         }
-        if (s == world - 1) plan->seg_recv[world * El] = r;
+        plan->from[s] = r - s * region_rows;
     }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        uint32_t m = 0;
+        if (e / El == rank)
+            for (int s = 0; s < world; s++) m += counts[s * E + e];
+        plan->merged[e] = m;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < El; j += blockDim.x) {
+        uint32_t o = 0;
+        for (int j2 = 0; j2 < j; j2++) o += plan->merged[rank * El + j2];
+        for (int s = 0; s < world; s++) {
+            plan->seg_dst[s * El + j] = o;
+            o += counts[s * E + rank * El + j];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(32) ep_plan_kernel(const uint32_t* __restrict__ counts, int rank, int world, int E,
+                                                     uint32_t region_rows, EpPlan* __restrict__ plan) {
+    ep_plan_body(counts, rank, world, E, region_rows, plan);
 }
 
 struct PeerPtrs {
     void* p[kMaxRanks];
 };
 
-// rows of this rank, packed as fp16 in expert order, written straight into the owners' receive buffers
+// Rows of this rank, packed as fp16 in expert order, written straight into region `rank` of the owners' receive
+// buffers; the first `world` blocks also write this rank's per-expert counts into row `rank` of every peer's count
+// matrix. Nothing here depends on what the peers do in the same layer.
 __global__ void __launch_bounds__(256) ep_pack_push_kernel(const void* __restrict__ x, int32_t x_dtype, int64_t ldx,
                                                           const uint32_t* __restrict__ inds, const uint32_t* __restrict__ pos,
-                                                          const uint32_t* __restrict__ offsets, const EpPlan* __restrict__ plan,
-                                                          PeerPtrs recv, int P, int D, int topk, int El) {
+                                                          const uint32_t* __restrict__ offsets, PeerPtrs recv, PeerPtrs counts,
+                                                          int rank, int world, int E, uint32_t region_rows, int P, int D,
+                                                          int topk) {
+    const int El = E / world;
+    if ((int)blockIdx.x < world) {
+        uint32_t* c = static_cast<uint32_t*>(counts.p[blockIdx.x]) + rank * E;
+        for (int e = threadIdx.x; e < E; e += 256) c[e] = offsets[e + 1] - offsets[e];
+    }
     const int pair = blockIdx.x;
     if (pair >= P) return;
     const uint32_t e = inds[pair];
     const int d = e / El;
-    const uint32_t row = plan->send_off[d] + (pos[pair] - offsets[d * El]);
+    const uint32_t row = rank * region_rows + (pos[pair] - offsets[d * El]);
     __half* dst = static_cast<__half*>(recv.p[d]) + (size_t)row * D;
     const size_t src = (size_t)(pair / topk) * ldx;
     for (int u = threadIdx.x; u < D / 8; u += 256) {
@@ -99,29 +108,89 @@ __global__ void __launch_bounds__(256) ep_pack_push_kernel(const void* __restric
     }
 }
 
-// expert outputs of the rows this rank computed, written back into each source's return buffer at the source's own
-// expert-sorted positions
+// Expert outputs of the rows this rank computed, written back into each source's return buffer at the source's own
+// expert-sorted positions. Four rows per block, 64 threads per row, four 16-byte loads in flight per thread.
 __global__ void __launch_bounds__(256) ep_return_push_kernel(const void* __restrict__ yd, int elem_bytes,
                                                             const EpPlan* __restrict__ plan, PeerPtrs back, int D, int world,
-                                                            int El) {
-    __shared__ uint32_t s_dst, s_src;
-    const uint32_t j = blockIdx.x;
-    if (j >= plan->recv_off[world]) return;
-    if (threadIdx.x == 0) {
-        // the segment that holds row j: binary search over the segment starts
-        int lo = 0, hi = world * El;  // seg_recv[lo] <= j < seg_recv[hi]
+                                                            int El, uint32_t region_rows) {
+    const uint32_t j = blockIdx.x * 4 + (threadIdx.x >> 6);
+    const int t = threadIdx.x & 63;
+    const uint32_t s = j / region_rows;
+    if ((int)s >= world) return;
+    if (j - s * region_rows >= plan->from[s]) return;
+    // the segment of source s that holds row j: binary search over that source's segment starts
+    int lo = s * El, hi = (s + 1) * El;  // seg_recv[lo] <= j, seg_recv[hi] > j (hi may be one past the source's last)
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (plan->seg_recv[mid] <= j) lo = mid; else hi = mid;
+    }
+    const uint32_t drow = plan->seg_src[lo] + (j - plan->seg_recv[lo]);
+    const size_t row_bytes = (size_t)D * elem_bytes;
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(yd) + (size_t)j * row_bytes);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(back.p[s]) + (size_t)drow * row_bytes);
+    const int n16 = (int)(row_bytes / 16);
+    int u = t;
+    for (; u + 192 < n16; u += 256) {
+        const uint4 a = ldg_nc_u4(src + u), b = ldg_nc_u4(src + u + 64), c = ldg_nc_u4(src + u + 128), d = ldg_nc_u4(src + u + 192);
+        dst[u] = a; dst[u + 64] = b; dst[u + 128] = c; dst[u + 192] = d;
+    }
+    for (; u < n16; u += 64) dst[u] = ldg_nc_u4(src + u);
+}
+
+// Received rows gathered from their per-source regions into expert-major order (xc), with the table of return addresses
+// in the same order: table[i] = where the output of compacted row i goes in its source rank's return buffer (0 past the
+// rows received). Four rows per block, 64 threads per row.
+__global__ void __launch_bounds__(256) ep_compact_kernel(const __half* __restrict__ recv, const EpPlan* __restrict__ plan,
+                                                        PeerPtrs back, int D, int row_bytes_back, int world, int El,
+                                                        uint32_t region_rows, __half* __restrict__ xc,
+                                                        uint64_t* __restrict__ table) {
+    const uint32_t j = blockIdx.x * 4 + (threadIdx.x >> 6);
+    const int t = threadIdx.x & 63;
+    const uint32_t s = j / region_rows;
+    if ((int)s >= world) return;
+    // rows past the total keep a zero in the table (j runs over the capacity; the total is small next to it)
+    uint32_t total = 0;
+    for (int q = 0; q < world; q++) total += plan->from[q];
+    if (j >= total && t == 0) table[j] = 0;
+    if (j - s * region_rows >= plan->from[s]) return;
+    int lo = s * El, hi = (s + 1) * El;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (plan->seg_recv[mid] <= j) lo = mid; else hi = mid;
+    }
+    const uint32_t idx = j - plan->seg_recv[lo];
+    const uint32_t dst = plan->seg_dst[lo] + idx;
+    if (t == 0)
+        table[dst] = reinterpret_cast<uint64_t>(static_cast<char*>(back.p[s]) + (size_t)(plan->seg_src[lo] + idx) * row_bytes_back);
+    const uint4* src = reinterpret_cast<const uint4*>(recv + (size_t)j * D);
+    uint4* out = reinterpret_cast<uint4*>(xc + (size_t)dst * D);
+    const int n16 = D / 8;
+    int u = t;
+    for (; u + 192 < n16; u += 256) {
+        const uint4 a = ldg_nc_u4(src + u), b = ldg_nc_u4(src + u + 64), c = ldg_nc_u4(src + u + 128), d = ldg_nc_u4(src + u + 192);
+        out[u] = a; out[u + 64] = b; out[u + 128] = c; out[u + 192] = d;
+    }
+    for (; u < n16; u += 64) out[u] = ldg_nc_u4(src + u);
+}
+
+// The same mapping as a table: table[j] = address, in the source rank's return buffer, of the output of received row j
+// (0 for rows nobody sent). A GEMM epilogue that stores through this table returns the rows without a copy kernel.
+__global__ void __launch_bounds__(256) ep_return_rows_kernel(const EpPlan* __restrict__ plan, PeerPtrs back, int row_bytes, int world,
+                                                            int El, uint32_t region_rows, uint64_t* __restrict__ table) {
+    const uint32_t j = blockIdx.x * 256 + threadIdx.x;
+    const uint32_t s = j / region_rows;
+    if ((int)s >= world) return;
+    uint64_t out = 0;
+    if (j - s * region_rows < plan->from[s]) {
+        int lo = s * El, hi = (s + 1) * El;
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
             if (plan->seg_recv[mid] <= j) lo = mid; else hi = mid;
         }
-        s_src = lo / El;
-        s_dst = plan->seg_src[lo] + (j - plan->seg_recv[lo]);
+        const uint32_t drow = plan->seg_src[lo] + (j - plan->seg_recv[lo]);
+        out = reinterpret_cast<uint64_t>(static_cast<char*>(back.p[s]) + (size_t)drow * row_bytes);
     }
-    __syncthreads();
-    const size_t row_bytes = (size_t)D * elem_bytes;
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(yd) + (size_t)j * row_bytes);
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(back.p[s_src]) + (size_t)s_dst * row_bytes);
-    for (int u = threadIdx.x; u < (int)(row_bytes / 16); u += 256) dst[u] = src[u];
+    table[j] = out;
 }
 
 // this rank's per-expert row counts (from its expert offsets) written into row `rank` of every peer's count matrix
@@ -135,7 +204,9 @@ __global__ void ep_share_counts_kernel(const uint32_t* __restrict__ offsets, Pee
 // Barrier over the ranks of the box. Each rank bumps its own epoch, publishes it into slot `rank` of every peer's flag
 // array and waits until every slot of its own array has reached the epoch. Counters only grow, so the kernel can be
 // replayed from a CUDA graph. The wait is bounded: on a timeout the status word is set and the kernel returns.
-__global__ void ep_barrier_kernel(PeerPtrs flags, uint32_t* epoch, int rank, int world, int32_t* status) {
+// With plan != nullptr the kernel goes on to derive this rank's plan from the count matrix the peers have just completed.
+__global__ void ep_barrier_kernel(PeerPtrs flags, uint32_t* epoch, int rank, int world, int32_t* status,
+                                  const uint32_t* counts, int E, uint32_t region_rows, EpPlan* plan) {
     __shared__ uint32_t e;
     if (threadIdx.x == 0) {
         e = *epoch + 1;
@@ -159,6 +230,7 @@ __global__ void ep_barrier_kernel(PeerPtrs flags, uint32_t* epoch, int rank, int
     }
     __syncthreads();
     __threadfence_system();
+    if (plan != nullptr) ep_plan_body(counts, rank, world, E, region_rows, plan);
 }
 
 }  // namespace
@@ -169,22 +241,22 @@ using namespace iq;
 // Opaque per-rank state of the exchange: the peers' buffers and a small device block (plan, epoch).
 struct iq_ep {
     iq_ctx* ctx = nullptr;
-    int32_t rank = 0, world = 1, experts = 0;
+    int32_t rank = 0, world = 1, experts = 0, region_rows = 0;
     PeerPtrs recv, back, flags, counts;
     EpPlan* plan = nullptr;   // device
     uint32_t* epoch = nullptr;  // device
 };
 
-extern "C" int32_t iq_ep_create(iq_ctx* ctx, int32_t rank, int32_t world, int32_t experts, void* const* peer_recv,
+extern "C" int32_t iq_ep_create(iq_ctx* ctx, int32_t rank, int32_t world, int32_t experts, int32_t region_rows, void* const* peer_recv,
                                 void* const* peer_back, void* const* peer_flags, void* const* peer_counts, iq_ep** out) {
     if (ctx == nullptr || out == nullptr) return kErrInvalidArg;
     *out = nullptr;
-    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || experts < world || experts % world != 0 ||
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || experts < world || experts % world != 0 || region_rows < 1 ||
         world * (experts / world) > kMaxSegs || peer_recv == nullptr || peer_back == nullptr || peer_flags == nullptr || peer_counts == nullptr)
         return fail(ctx, kErrInvalidArg, "ep_create: rank %d of %d, %d experts", rank, world, experts);
     iq_ep* ep = new (std::nothrow) iq_ep();
     if (ep == nullptr) return kErrCuda;
-    ep->ctx = ctx; ep->rank = rank; ep->world = world; ep->experts = experts;
+    ep->ctx = ctx; ep->rank = rank; ep->world = world; ep->experts = experts; ep->region_rows = region_rows;
     for (int i = 0; i < world; i++) {
         if (!peer_recv[i] || !peer_back[i] || !peer_flags[i] || !peer_counts[i]) {
             delete ep;
@@ -223,14 +295,16 @@ extern "C" int32_t iq_ep_share_counts(iq_ep* ep, void* stream, const uint32_t* o
 extern "C" int32_t iq_ep_plan(iq_ep* ep, void* stream) {
     if (ep == nullptr) return kErrInvalidArg;
     const uint32_t* counts_all = static_cast<const uint32_t*>(ep->counts.p[ep->rank]);
-    ep_plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(counts_all, ep->rank, ep->world, ep->experts, ep->plan);
+    ep_plan_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(counts_all, ep->rank, ep->world, ep->experts,
+                                                                         (uint32_t)ep->region_rows, ep->plan);
     return check_cuda(ep->ctx, cudaGetLastError(), "ep_plan launch");
 }
 
-extern "C" int32_t iq_ep_barrier(iq_ep* ep, void* stream) {
+extern "C" int32_t iq_ep_barrier(iq_ep* ep, void* stream, int32_t then_plan) {
     if (ep == nullptr) return kErrInvalidArg;
-    ep_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ep->flags, ep->epoch, ep->rank, ep->world,
-                                                                           ep->ctx->d_status);
+    ep_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        ep->flags, ep->epoch, ep->rank, ep->world, ep->ctx->d_status, static_cast<const uint32_t*>(ep->counts.p[ep->rank]),
+        ep->experts, (uint32_t)ep->region_rows, then_plan ? ep->plan : nullptr);
     return check_cuda(ep->ctx, cudaGetLastError(), "ep_barrier launch");
 }
 
@@ -242,18 +316,46 @@ extern "C" int32_t iq_ep_pack_push(iq_ep* ep, void* stream, const void* x, int32
         ldx < d_model || ldx % 8 != 0 || x_dtype < 0 || x_dtype > 2)
         return fail(ep->ctx, kErrInvalidArg, "ep_pack_push: arguments");
     const int P = tokens * top_k;
-    ep_pack_push_kernel<<<P, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x, x_dtype, ldx, inds, pos, offsets, ep->plan,
-                                                                             ep->recv, P, d_model, top_k,
-                                                                             ep->experts / ep->world);
+    if (P > ep->region_rows)
+        return fail(ep->ctx, kErrInvalidArg, "ep_pack_push: %d rows exceed the region of %d rows", P, ep->region_rows);
+    const int grid = P > ep->world ? P : ep->world;
+    ep_pack_push_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        x, x_dtype, ldx, inds, pos, offsets, ep->recv, ep->counts, ep->rank, ep->world, ep->experts, (uint32_t)ep->region_rows, P,
+        d_model, top_k);
     return check_cuda(ep->ctx, cudaGetLastError(), "ep_pack_push launch");
 }
 
-extern "C" int32_t iq_ep_return_push(iq_ep* ep, void* stream, const void* yd, int32_t yd_dtype, int32_t max_rows,
-                                     int32_t d_model) {
+extern "C" int32_t iq_ep_return_push(iq_ep* ep, void* stream, const void* yd, int32_t yd_dtype, int32_t d_model) {
     if (ep == nullptr) return kErrInvalidArg;
-    if (yd == nullptr || max_rows < 1 || (yd_dtype != kF32 && yd_dtype != kF16) || d_model % 8 != 0)
+    if (yd == nullptr || (yd_dtype != kF32 && yd_dtype != kF16) || d_model % 8 != 0)
         return fail(ep->ctx, kErrInvalidArg, "ep_return_push: arguments");
-    ep_return_push_kernel<<<max_rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        yd, yd_dtype == kF32 ? 4 : 2, ep->plan, ep->back, d_model, ep->world, ep->experts / ep->world);
+    const int64_t rows = (int64_t)ep->world * ep->region_rows;
+    ep_return_push_kernel<<<(unsigned)((rows + 3) / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        yd, yd_dtype == kF32 ? 4 : 2, ep->plan, ep->back, d_model, ep->world, ep->experts / ep->world, (uint32_t)ep->region_rows);
     return check_cuda(ep->ctx, cudaGetLastError(), "ep_return_push launch");
+}
+
+extern "C" int32_t iq_ep_return_rows(iq_ep* ep, void* stream, int32_t yd_dtype, int32_t d_model, void** table) {
+    if (ep == nullptr) return kErrInvalidArg;
+    if (table == nullptr || (yd_dtype != kF32 && yd_dtype != kF16) || d_model % 8 != 0)
+        return fail(ep->ctx, kErrInvalidArg, "ep_return_rows: arguments");
+    const int64_t rows = (int64_t)ep->world * ep->region_rows;
+    ep_return_rows_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        ep->plan, ep->back, d_model * (yd_dtype == kF32 ? 4 : 2), ep->world, ep->experts / ep->world, (uint32_t)ep->region_rows,
+        reinterpret_cast<uint64_t*>(table));
+    return check_cuda(ep->ctx, cudaGetLastError(), "ep_return_rows launch");
+}
+
+extern "C" int32_t iq_ep_compact(iq_ep* ep, void* stream, const void* recv_rows, int32_t d_model, int32_t yd_dtype,
+                                 void* rows_out, void** table, const uint32_t** merged_counts) {
+    if (ep == nullptr) return kErrInvalidArg;
+    if (recv_rows == nullptr || rows_out == nullptr || table == nullptr || (yd_dtype != kF32 && yd_dtype != kF16) ||
+        d_model % 8 != 0)
+        return fail(ep->ctx, kErrInvalidArg, "ep_compact: arguments");
+    const int64_t rows = (int64_t)ep->world * ep->region_rows;
+    ep_compact_kernel<<<(unsigned)((rows + 3) / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(recv_rows), ep->plan, ep->back, d_model, d_model * (yd_dtype == kF32 ? 4 : 2), ep->world,
+        ep->experts / ep->world, (uint32_t)ep->region_rows, static_cast<__half*>(rows_out), reinterpret_cast<uint64_t*>(table));
+    if (merged_counts != nullptr) *merged_counts = ep->plan->merged;
+    return check_cuda(ep->ctx, cudaGetLastError(), "ep_compact launch");
 }

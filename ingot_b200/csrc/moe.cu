@@ -44,6 +44,7 @@ constexpr int kPrefillTileRowsBig = 256;   // ... and once they see many: every 
 constexpr int kTensorPathRowsPerExpert = 24;
 constexpr int kBigTileRowsPerExpert = 96;
 constexpr int kRouterSmemMax = 200 * 1024;
+constexpr int kRouterTiledMinTokens = 64;  // above this the router runs as a tiled float64 GEMM
 
 MoeWs carve(const iq_moe* l, void* base, int tokens) {
     const iq_moe_desc& d = l->d;
@@ -182,7 +183,7 @@ int32_t run_gateup_tc(iq_moe* l, cudaStream_t cs, const __half* rows16, int64_t 
 }
 
 int32_t run_down_tc(iq_moe* l, cudaStream_t cs, const __half* h, int64_t n_rows, const Tile* tiles, const uint32_t* ntiles,
-                    void* yd, int32_t yd_dtype, int bn) {
+                    void* yd, int32_t yd_dtype, int bn, const uint64_t* yd_rows = nullptr) {
     const iq_moe_desc& d = l->d;
     QmmCall c;
     c.fmt = l->fmt; c.epi = 0; c.bn = bn;
@@ -191,7 +192,7 @@ int32_t run_down_tc(iq_moe* l, cudaStream_t cs, const __half* h, int64_t n_rows,
     c.experts = d.expert_count; c.expert_lo = d.expert_lo;
     c.N = d.d_model; c.K = d.d_ff; c.M = (int32_t)n_rows;
     c.tiles = tiles; c.ntiles = ntiles;
-    c.y = yd; c.y_dtype = yd_dtype; c.ldy = d.d_model;
+    c.y = yd; c.y_row_ptr = yd_rows; c.y_dtype = yd_dtype; c.ldy = d.d_model;
     c.ebias[0] = d.down_bias;
     return launch_qmm(l->ctx, cs, c);
 }
@@ -199,6 +200,10 @@ int32_t run_down_tc(iq_moe* l, cudaStream_t cs, const __half* h, int64_t n_rows,
 }  // namespace
 
 int32_t moe_init(iq_ctx* ctx) {
+    cudaFuncSetAttribute(reinterpret_cast<const void*>(router_logits_tiled_kernel<0, 64>),
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)router_tiled_smem(64));
+    cudaFuncSetAttribute(reinterpret_cast<const void*>(router_logits_tiled_kernel<1, 64>),
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)router_tiled_smem(64));
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(router_logits_kernel<0>),
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kRouterSmemMax);
     if (e == cudaSuccess)
@@ -402,6 +407,35 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
     int32_t st;
 
     if ((pieces & IQ_PIECE_ROUTER) && l->ext_inds == nullptr) {
+        if (tokens > kRouterTiledMinTokens && d.d_model % 64 == 0) {
+            // register-tiled float64 GEMM; the K range is split over a cluster until the grid fills the GPU several
+            // times over (the blocks of one SM share its float64 pipe, so balance comes from many small blocks)
+            const int bm = tokens >= 1024 ? 64 : 32;
+            const int tiles = ((tokens + bm - 1) / bm) * ((d.experts + kRtBN - 1) / kRtBN);
+            const int nchunks = d.d_model / kRtBK;
+            int S = 1;
+            while (tiles * S < 4 * 148 && S < 8 && nchunks / (2 * S) >= 2) S *= 2;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((tokens + bm - 1) / bm, (d.experts + kRtBN - 1) / kRtBN, S);
+            cfg.blockDim = dim3(128);
+            cfg.dynamicSmemBytes = router_tiled_smem(bm);
+            cfg.stream = cs;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = S;
+            cfg.attrs = at; cfg.numAttrs = 1;
+            const int cps = (nchunks + S - 1) / S;
+            const bool q8 = d.router_kind != IQ_ROUTER_BF16;
+            const void* rw = d.router_w;
+            const void* rs = q8 ? d.router_scales : nullptr;
+            const void* rb = q8 ? d.router_biases : nullptr;
+            auto kern = bm == 64 ? (q8 ? router_logits_tiled_kernel<1, 64> : router_logits_tiled_kernel<0, 64>)
+                                 : (q8 ? router_logits_tiled_kernel<1, 32> : router_logits_tiled_kernel<0, 32>);
+            st = check_cuda(ctx, cudaLaunchKernelEx(&cfg, kern, x, x_dtype, ldx, rw, rs, rb, w.logits, tokens, d.experts,
+                                                    d.d_model, l->ld, cps),
+                            "router_logits_tiled launch");
+            if (st != kOk) return st;
+        } else {
         // experts per block: small ranges for few tokens (more blocks, shorter dot products per thread)
         int eb = d.experts < 256 ? d.experts : 256;
         if (tokens <= 16) eb = 8;
@@ -417,6 +451,7 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
             router_logits_kernel<1><<<grid, 256, smem, cs>>>(x, x_dtype, ldx, d.router_w, d.router_scales,
                                                               d.router_biases, w.logits, tokens, d.experts, d.d_model,
                                                               l->ld, eb);
+        }
         st = check_cuda(ctx, cudaGetLastError(), "router_logits launch");
         if (st != kOk) return st;
     }
@@ -520,13 +555,14 @@ extern "C" int32_t iq_moe_experts_workspace_bytes(const iq_moe* l, int32_t max_r
 }
 
 extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16, int32_t total_rows, int32_t max_rows,
-                                  const uint32_t* counts, int32_t sources, void* yd, int32_t yd_dtype, void* workspace,
-                                  size_t workspace_bytes) {
+                                  const uint32_t* counts, int32_t sources, int32_t region_rows, void* yd, int32_t yd_dtype,
+                                  void* const* yd_rows, void* workspace, size_t workspace_bytes) {
     if (l == nullptr) return kErrInvalidArg;
     iq_ctx* ctx = l->ctx;
     const iq_moe_desc& d = l->d;
     if (rows_f16 == nullptr || counts == nullptr || yd == nullptr || sources < 1 || sources * d.expert_count > 4096 ||
-        total_rows < 0 || total_rows > max_rows || (yd_dtype != kF32 && yd_dtype != kF16) ||
+        total_rows < 0 || total_rows > max_rows || (yd_dtype != kF32 && yd_dtype != kF16) || region_rows < 0 ||
+        (int64_t)region_rows * sources > max_rows ||
         (reinterpret_cast<uintptr_t>(rows_f16) & 15) != 0)
         return fail(ctx, kErrInvalidArg, "moe_experts: arguments");
     if (total_rows == 0) return kOk;
@@ -537,15 +573,18 @@ extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16,
     const int64_t slots = (int64_t)sources * d.expert_count;
     if (use_tensor_path(total_rows, slots)) {
         const int bn = tensor_tile_rows(total_rows, slots);
-        ep_tiles_kernel<<<1, 512, 0, cs>>>(counts, sources, d.experts, d.expert_lo, d.expert_count, bn, w.tiles, w.ntiles);
+        ep_tiles_kernel<<<1, 512, 0, cs>>>(counts, sources, d.experts, d.expert_lo, d.expert_count, bn, (uint32_t)region_rows, w.tiles,
+                                           w.ntiles);
         int32_t st2 = check_cuda(ctx, cudaGetLastError(), "ep_tiles launch");
         // the row count is only known on the device: bounds come from the capacity, total_rows picks the kernels
         if (st2 == kOk) st2 = run_gateup_tc(l, cs, static_cast<const __half*>(rows_f16), max_rows, w.tiles, w.ntiles, w.h, bn);
-        if (st2 == kOk) st2 = run_down_tc(l, cs, w.h, max_rows, w.tiles, w.ntiles, yd, yd_dtype, bn);
+        if (st2 == kOk)
+            st2 = run_down_tc(l, cs, w.h, max_rows, w.tiles, w.ntiles, yd, yd_dtype, bn, reinterpret_cast<const uint64_t*>(yd_rows));
         return st2;
     }
     const int bm = total_rows <= slots * 6 ? 8 : 16;
-    ep_tiles_kernel<<<1, 512, 0, cs>>>(counts, sources, d.experts, d.expert_lo, d.expert_count, bm, w.tiles, w.ntiles);
+    ep_tiles_kernel<<<1, 512, 0, cs>>>(counts, sources, d.experts, d.expert_lo, d.expert_count, bm, (uint32_t)region_rows, w.tiles,
+                                       w.ntiles);
     int32_t st = check_cuda(ctx, cudaGetLastError(), "ep_tiles launch");
     if (st != kOk) return st;
     const int64_t mt = max_rows / bm + slots;
@@ -553,7 +592,12 @@ extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16,
     if (max_tiles > 65535) return fail(ctx, kErrInvalidArg, "moe_experts: too many tiles for one launch");
     st = run_gateup(l, cs, rows_f16, kF16, d.d_model, nullptr, w.tiles, w.ntiles, max_tiles, bm, w.h);
     if (st != kOk) return st;
-    return run_down(l, cs, w.h, w.tiles, w.ntiles, max_tiles, bm, yd, yd_dtype);
+    st = run_down(l, cs, w.h, w.tiles, w.ntiles, max_tiles, bm, yd, yd_dtype);
+    if (st != kOk || yd_rows == nullptr) return st;
+    // few rows per expert: the tile kernels wrote yd; the rows then go where the caller's table points
+    const int row_bytes = d.d_model * (yd_dtype == kF32 ? 4 : 2);
+    moe_scatter_rows_kernel<<<(max_rows + 3) / 4, 256, 0, cs>>>(yd, reinterpret_cast<const uint64_t*>(yd_rows), max_rows, row_bytes);
+    return check_cuda(ctx, cudaGetLastError(), "moe_scatter_rows launch");
 }
 
 extern "C" int32_t iq_moe_combine_rows(iq_moe* l, void* stream, const void* yd_rows, int32_t yd_dtype, int32_t tokens,

@@ -9,6 +9,7 @@
 
 #include "common.cuh"
 #include "gqmv.cuh"
+#include "ptx.cuh"
 
 namespace iq {
 
@@ -120,6 +121,161 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const void* __restri
         for (int i = tid; i < kRouterTT * (ld - E); i += 256) {
             const int tt = i / (ld - E), c = E + i % (ld - E);
             if (tt < nt) logits[(size_t)(t0 + tt) * ld + c] = 0.f;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The same logits for many tokens: a register-tiled float64 GEMM. Block = BM tokens x 64 experts, 128 threads, each
+// thread a (BM/8) x 4 tile of accumulators (32 DFMA per six 16-byte shared loads at BM = 64), operands converted to
+// float64 on their way into shared memory ([k][row] layout, double-buffered, next chunk's global loads in flight during
+// the math). The K range is split over the gridDim.z blocks of a thread-block cluster; their partial tiles are summed
+// through distributed shared memory in rank order, so the result does not depend on timing.
+constexpr int kRtBN = 64, kRtBK = 32;
+constexpr size_t router_tiled_smem(int BM) { return (size_t)2 * kRtBK * (BM + kRtBN) * 8; }
+
+template <int WFMT>
+__device__ __forceinline__ void router_w8(const void* __restrict__ wr, const void* __restrict__ ws,
+                                          const void* __restrict__ wb, int e, int k, int D, float (&w)[8]) {
+    if (WFMT == 0) {
+        const uint4 r = ldg_nc_u4(reinterpret_cast<const uint16_t*>(wr) + (size_t)e * D + k);
+        const uint32_t q[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            w[2 * j] = __uint_as_float(q[j] << 16);
+            w[2 * j + 1] = __uint_as_float(q[j] & 0xFFFF0000u);
+        }
+    } else {
+        const uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint32_t*>(wr) + (size_t)e * (D / 4) + k / 4);
+        const int gi = e * (D / 64) + k / 64;
+        // the weight value is the fp32 s*q + b of the reference's CPU dequantisation
+        const float sc = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(ws)[gi]);
+        const float bi = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(wb)[gi]);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            w[j] = __fadd_rn(__fmul_rn(sc, (float)((r.x >> (8 * j)) & 0xFFu)), bi);
+            w[4 + j] = __fadd_rn(__fmul_rn(sc, (float)((r.y >> (8 * j)) & 0xFFu)), bi);
+        }
+    }
+}
+
+template <int WFMT, int BM>
+__global__ void __launch_bounds__(128) router_logits_tiled_kernel(const void* __restrict__ x, int32_t x_dtype, int64_t ldx,
+                                                                  const void* __restrict__ wr, const void* __restrict__ ws,
+                                                                  const void* __restrict__ wb, float* __restrict__ logits,
+                                                                  int T, int E, int D, int ld, int chunks_per_split) {
+    constexpr int TM = BM / 8;   // tokens per thread: TM/2 pairs, 16 rows apart
+    constexpr int XU = BM / 32;  // 8-value units of x per thread and chunk
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    double (*xs)[kRtBK][BM] = reinterpret_cast<double (*)[kRtBK][BM]>(smem_raw);
+    double (*wsm)[kRtBK][kRtBN] = reinterpret_cast<double (*)[kRtBK][kRtBN]>(smem_raw + (size_t)2 * kRtBK * BM * 8);
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int t0 = blockIdx.x * BM, e0 = blockIdx.y * kRtBN;
+    const int nchunks = D / kRtBK;
+    const int c_lo = blockIdx.z * chunks_per_split, c_hi = min(nchunks, c_lo + chunks_per_split);
+    // fill roles: consecutive lanes take consecutive rows, so the transposed float64 stores are free of bank conflicts
+    const int xrow = tid & (BM - 1), xku = tid / BM;   // BM = 32: four k-units by tid; BM = 64: two, twice
+    const int wrow = tid & 63, wku = tid >> 6;
+    float xv[XU][8], wv[2][8];
+    auto fetch = [&](int c) {
+        const int k0 = c * kRtBK;
+#pragma unroll
+        for (int i = 0; i < XU; i++) {
+            if (t0 + xrow < T) load_x8(x, x_dtype, (size_t)(t0 + xrow) * ldx + k0 + (xku + (128 / BM) * i) * 8, xv[i]);
+            else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) xv[i][j] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (e0 + wrow < E) router_w8<WFMT>(wr, ws, wb, e0 + wrow, k0 + (wku + 2 * i) * 8, D, wv[i]);
+            else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) wv[i][j] = 0.f;
+            }
+        }
+    };
+    auto stash = [&](int b) {
+#pragma unroll
+        for (int i = 0; i < XU; i++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) xs[b][(xku + (128 / BM) * i) * 8 + j][xrow] = (double)xv[i][j];
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) wsm[b][(wku + 2 * i) * 8 + j][wrow] = (double)wv[i][j];
+    };
+    // thread tile: tokens {16p + 2ty, 16p + 2ty + 1 : p < TM/2} x experts {2tx, 2tx+1, 32+2tx, 33+2tx}
+    double acc[TM][4];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0;
+    int b = 0;
+    if (c_lo < c_hi) {
+        fetch(c_lo);
+        stash(0);
+    }
+    __syncthreads();
+    for (int c = c_lo; c < c_hi; c++) {
+        const bool more = c + 1 < c_hi;
+        if (more) fetch(c + 1);
+#pragma unroll 4
+        for (int k = 0; k < kRtBK; k++) {
+            double xr[TM];
+#pragma unroll
+            for (int p = 0; p < TM / 2; p++) {
+                const double2 v = *reinterpret_cast<const double2*>(&xs[b][k][16 * p + 2 * ty]);
+                xr[2 * p] = v.x;
+                xr[2 * p + 1] = v.y;
+            }
+            const double2 wa = *reinterpret_cast<const double2*>(&wsm[b][k][2 * tx]);
+            const double2 wc = *reinterpret_cast<const double2*>(&wsm[b][k][32 + 2 * tx]);
+            const double wq[4] = {wa.x, wa.y, wc.x, wc.y};
+#pragma unroll
+            for (int i = 0; i < TM; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fma(xr[i], wq[j], acc[i][j]);
+        }
+        if (more) stash(b ^ 1);
+        __syncthreads();
+        b ^= 1;
+    }
+    const int ecol[4] = {2 * tx, 2 * tx + 1, 32 + 2 * tx, 33 + 2 * tx};
+    if (gridDim.z == 1) {
+#pragma unroll
+        for (int i = 0; i < TM; i++) {
+            const int tr = 16 * (i >> 1) + 2 * ty + (i & 1);
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (t0 + tr < T && e0 + ecol[j] < E) logits[(size_t)(t0 + tr) * ld + e0 + ecol[j]] = (float)acc[i][j];
+        }
+    } else {
+        // partial tiles meet in the cluster: every block parks its tile in its own shared memory, then sums a slice of
+        // the rows over all blocks, in rank order
+        double* red = reinterpret_cast<double*>(smem_raw);  // [BM][kRtBN], free after the last barrier of the loop
+#pragma unroll
+        for (int i = 0; i < TM; i++) {
+            const int tr = 16 * (i >> 1) + 2 * ty + (i & 1);
+#pragma unroll
+            for (int j = 0; j < 4; j++) red[tr * kRtBN + ecol[j]] = acc[i][j];
+        }
+        cluster_sync_all();
+        const int S = gridDim.z, z = blockIdx.z;
+        const int rows = BM / S;  // S is a power of two, at most 8
+        for (int i = tid; i < rows * kRtBN; i += 128) {
+            const int r = z * rows + i / kRtBN, cidx = i % kRtBN;
+            double sum = 0.0;
+            for (int q = 0; q < S; q++) sum += ld_dsmem_f64(red + r * kRtBN + cidx, q);
+            if (t0 + r < T && e0 + cidx < E) logits[(size_t)(t0 + r) * ld + e0 + cidx] = (float)sum;
+        }
+        cluster_sync_all();  // no block leaves while its shared memory may still be read
+    }
+    if (blockIdx.y == 0 && blockIdx.z == 0) {
+        for (int i = tid; i < BM * (ld - E); i += 128) {
+            const int tt = i / (ld - E), cidx = E + i % (ld - E);
+            if (t0 + tt < T) logits[(size_t)(t0 + tt) * ld + cidx] = 0.f;
         }
     }
 }
@@ -384,33 +540,64 @@ __global__ void __launch_bounds__(256) moe_pack_rows_kernel(const void* __restri
     }
 }
 
-// Tile list of the rows a rank received: source-major, then by local expert; counts[s * E + e] rows from source s
-// for expert e. One block; entries = sources * local experts (at most 8 per thread with 512 threads).
+// Tile list of the rows a rank received, by source then by local expert; counts[s * E + e] rows from source s for
+// expert e. region_rows == 0: the sources' rows follow each other (packed); region_rows > 0: the rows of source s start
+// at s * region_rows (every source owns a fixed region of the receive buffer). One block; at most 4096 entries.
 __global__ void __launch_bounds__(512) ep_tiles_kernel(const uint32_t* __restrict__ counts, int sources, int E, int e_lo,
-                                                       int e_cnt, int bm, Tile* __restrict__ tiles,
+                                                       int e_cnt, int bm, uint32_t region_rows, Tile* __restrict__ tiles,
                                                        uint32_t* __restrict__ ntiles) {
-    __shared__ uint32_t srows[512], stiles[512];
+    __shared__ uint32_t rstart[4096];
+    __shared__ uint32_t stot[16];
+    __shared__ uint32_t stiles[512];
     const int n = sources * e_cnt;
+    if ((int)threadIdx.x < sources) {
+        uint32_t t = 0;
+        for (int j = 0; j < e_cnt; j++) t += counts[threadIdx.x * E + e_lo + j];
+        stot[threadIdx.x] = t;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < sources) {
+        const int s = threadIdx.x;
+        uint32_t r = 0;
+        if (region_rows > 0) r = s * region_rows;
+        else for (int s2 = 0; s2 < s; s2++) r += stot[s2];
+        for (int j = 0; j < e_cnt; j++) {
+            rstart[s * e_cnt + j] = r;
+            r += counts[s * E + e_lo + j];
+        }
+    }
+    __syncthreads();
     const int per = (n + 511) / 512;
     const int b = threadIdx.x * per, e_end = min(n, b + per);
-    uint32_t rows = 0, tl = 0;
+    uint32_t tl = 0;
     for (int i = b; i < e_end; i++) {
         const uint32_t c = counts[(i / e_cnt) * E + e_lo + i % e_cnt];
-        rows += c;
         tl += (c + bm - 1) / bm;
     }
-    srows[threadIdx.x] = rows;
     stiles[threadIdx.x] = tl;
     __syncthreads();
-    uint32_t r0 = 0, t0 = 0;
-    for (int i = 0; i < (int)threadIdx.x; i++) { r0 += srows[i]; t0 += stiles[i]; }
+    uint32_t t0 = 0;
+    for (int i = 0; i < (int)threadIdx.x; i++) t0 += stiles[i];
     for (int i = b; i < e_end; i++) {
         const uint32_t e = e_lo + i % e_cnt;
         const uint32_t c = counts[(i / e_cnt) * E + e];
+        const uint32_t r0 = rstart[i];
         for (uint32_t j = 0; j * bm < c; j++) tiles[t0++] = Tile{e, r0 + j * bm, min((uint32_t)bm, c - j * bm), 0};
-        r0 += c;
     }
     if (threadIdx.x == 511) ntiles[0] = t0;
+}
+
+// Row r of src (row_bytes each, a multiple of 16) copied to the address row_ptr[r]; rows whose address is 0 stay.
+// Four rows per block, 64 threads per row.
+__global__ void __launch_bounds__(256) moe_scatter_rows_kernel(const void* __restrict__ src, const uint64_t* __restrict__ row_ptr,
+                                                              int rows, int row_bytes) {
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 6);
+    if (r >= rows) return;
+    const uint64_t dptr = row_ptr[r];
+    if (dptr == 0) return;
+    const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(src) + (size_t)r * row_bytes);
+    uint4* d = reinterpret_cast<uint4*>(dptr);
+    for (int u = threadIdx.x & 63; u < row_bytes / 16; u += 64) d[u] = ldg_nc_u4(s + u);
 }
 
 // Unit-weight RMSNorm of fp32 rows (the layer-stack skeleton's input normalisation; Shaders/verify.metal:503-523 of

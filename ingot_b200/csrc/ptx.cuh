@@ -127,4 +127,19 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// ---- thread-block clusters ------------------------------------------------------------------------------------------
+// barrier over all threads of the cluster, with release/acquire ordering of shared-memory writes
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// float64 at the same shared-memory offset as `p` in the block with rank `cta` of this cluster
+__device__ __forceinline__ double ld_dsmem_f64(const double* p, uint32_t cta) {
+    const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    uint32_t remote;
+    double v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(cta));
+    asm volatile("ld.shared::cluster.f64 %0, [%1];" : "=d"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 }  // namespace iq

@@ -101,7 +101,7 @@ int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
     p.expert_lo = c.expert_lo;
     p.N = c.N; p.K = c.K; p.M = c.M;
     p.tiles = c.tiles; p.ntiles = c.ntiles;
-    p.y = c.y; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
+    p.y = c.y; p.y_row_ptr = c.y_row_ptr; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
     p.limit = c.limit;
     p.status = ctx->d_status;
     {

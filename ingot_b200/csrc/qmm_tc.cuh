@@ -45,6 +45,7 @@ struct QmmParams {
     const uint32_t* ntiles;
     // output
     void* y;
+    const uint64_t* y_row_ptr;  // grouped mode, optional: address of every output row (peers' memory included); y unused
     int32_t y_dtype;
     int64_t ldy;
     int32_t accumulate;
@@ -305,15 +306,22 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                         const float u = __uint_as_float(r1[j]) + bias1;
                         v = p.limit > 0.f ? glu<kActSwigluOai>(g, u, p.limit) : glu<kActSilu>(g, u, 0.f);
                     }
-                    const size_t o = (size_t)(row0 + c0 + j) * p.ldy + n;
+                    // a row either sits in y or, when the caller gave one address per row, wherever that points:
+                    // the expert outputs of an expert-parallel layer go straight into their source rank's memory
+                    size_t o = (size_t)(row0 + c0 + j) * p.ldy + n;
+                    void* ybase = p.y;
+                    if (p.y_row_ptr != nullptr) {
+                        ybase = reinterpret_cast<void*>(p.y_row_ptr[row0 + c0 + j]);
+                        o = n;
+                    }
                     if (p.y_dtype == kF32) {
-                        float* yp = reinterpret_cast<float*>(p.y) + o;
+                        float* yp = reinterpret_cast<float*>(ybase) + o;
                         *yp = p.accumulate ? *yp + v : v;
                     } else if (p.y_dtype == kF16) {
-                        __half* yp = reinterpret_cast<__half*>(p.y) + o;
+                        __half* yp = reinterpret_cast<__half*>(ybase) + o;
                         *yp = __float2half_rn(p.accumulate ? __half2float(*yp) + v : v);
                     } else {
-                        uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + o;
+                        uint16_t* yp = reinterpret_cast<uint16_t*>(ybase) + o;
                         *yp = (uint16_t)f32_to_bf16_bits(p.accumulate ? bf16_bits_to_f32(*yp) + v : v);
                     }
                 }

@@ -79,23 +79,34 @@ class ExpertParallelMoE:
             }
 
     def use_device_exchange(self, dx: "DeviceExchange"):
-        """Switches the layer to the device-side exchange (`dx` is shared by the layers of a stack). The kernels are
-        picked for the rows this rank expects to receive (as many as it sends: rows * top_k); capacity stays max_rows."""
+        """Switches the layer to the device-side exchange (`dx` is shared by the layers of a stack). Every source rank
+        owns a region of dx.region_rows rows in each receive buffer, so the expert scratch covers world * region_rows."""
         self.dx = dx
         if "yd_dx" not in self.buf:
-            self.buf["yd_dx"] = torch.empty(self.max_rows, self.layer.D, dtype=dx.yd_dtype, device=self.layer.device)
+            dev = self.layer.device
+            self.buf["yd_dx"] = torch.empty(dx.max_rows, self.layer.D, dtype=dx.yd_dtype, device=dev)
+            self.buf["rows_dx"] = torch.zeros(dx.max_rows, dtype=torch.int64, device=dev)
+            self.buf["xc_dx"] = torch.zeros(dx.max_rows, self.layer.D, dtype=torch.float16, device=dev)
+            self.buf["ws_dx"] = torch.empty(self.layer.experts_workspace_bytes(dx.max_rows, self.world), dtype=torch.uint8,
+                                            device=dev)
 
     def _encode_device(self, x, out, rows, accumulate):
         L, b, dx = self.layer, self.buf, self.dx
+        k = L.router.top_k
         L.encode(x, out, rows, only=("router", "route", "group"))
         v = L.views(rows)
-        dx.share_counts(v["offsets"])
-        dx.barrier()
-        dx.plan()
-        dx.pack_push(x, rows, L.router.top_k, v["inds"], v["pos"], v["offsets"])
-        dx.barrier()
-        L.experts(dx.recv, min(rows * L.router.top_k, self.max_rows), dx.counts, self.world, b["yd_dx"], b["ws"])
-        dx.return_push(b["yd_dx"])
+        dx.pack_push(x, rows, k, v["inds"], v["pos"], v["offsets"])  # rows and counts go out; no peer input needed
+        dx.barrier(then_plan=True)
+        # the kernels are picked for the rows this rank expects to receive (about as many as it sends)
+        if dx.fused_return:
+            # rows gathered expert-major (one run of rows per expert, whatever their source); the down projection then
+            # stores its output rows straight into the sources' return buffers
+            merged = dx.compact(b["xc_dx"], b["rows_dx"])
+            L.experts(b["xc_dx"], min(rows * k, dx.max_rows), merged, 1, b["yd_dx"], b["ws_dx"], yd_rows=b["rows_dx"])
+        else:
+            L.experts(dx.recv, min(rows * k, dx.max_rows), dx.counts, self.world, b["yd_dx"], b["ws_dx"],
+                      region_rows=dx.region_rows)
+            dx.return_push(b["yd_dx"])
         dx.barrier()
         L.combine_rows(dx.back, out, rows, accumulate=accumulate)
 
@@ -131,8 +142,9 @@ class DeviceExchange:
     CUDA graph. Peer-addressable buffers come from torch's symmetric memory (plain peer pointers; multicast is not used).
     """
 
-    def __init__(self, experts: int, top_k: int, d_model: int, max_local_tokens: int, max_rows: int,
-                 yd_dtype: torch.dtype, device: torch.device, group=None):
+    def __init__(self, experts: int, top_k: int, d_model: int, max_local_tokens: int, yd_dtype: torch.dtype,
+                 device: torch.device, group=None, fused_return: bool = True):
+        """max_local_tokens: the largest token count any rank handles per call (the same value on every rank)."""
         import os
 
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -140,9 +152,12 @@ class DeviceExchange:
 
         group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        P = max_local_tokens * top_k
+        # region s of a receive buffer takes whatever source s sends, at most all of its P rows
+        self.fused_return = fused_return
+        self.region_rows, max_rows = P, self.world * P
         self.max_rows, self.yd_dtype, self.d_model = max_rows, yd_dtype, d_model
         esz = torch.empty((), dtype=yd_dtype).element_size()
-        P = max_local_tokens * top_k
         sizes = [max_rows * d_model * 2, P * d_model * esz, 256, self.world * experts * 4]
         self._bufs, self._hdls, ptrs = [], [], []
         for n in sizes:
@@ -160,14 +175,14 @@ class DeviceExchange:
         self.ctx = capi.context(device.index or 0)
         arr = lambda v: (C.c_void_p * self.world)(*v)
         self._h = C.c_void_p()
-        self.ctx.check(capi.lib().iq_ep_create(self.ctx.handle, self.rank, self.world, experts, arr(ptrs[0]), arr(ptrs[1]),
-                                               arr(ptrs[2]), arr(ptrs[3]), C.byref(self._h)))
+        self.ctx.check(capi.lib().iq_ep_create(self.ctx.handle, self.rank, self.world, experts, self.region_rows,
+                                               arr(ptrs[0]), arr(ptrs[1]), arr(ptrs[2]), arr(ptrs[3]), C.byref(self._h)))
 
     def share_counts(self, offsets: torch.Tensor, stream=None):
         self.ctx.check(capi.lib().iq_ep_share_counts(self._h, _stream_ptr(stream), offsets.data_ptr()))
 
-    def barrier(self, stream=None):
-        self.ctx.check(capi.lib().iq_ep_barrier(self._h, _stream_ptr(stream)))
+    def barrier(self, then_plan: bool = False, stream=None):
+        self.ctx.check(capi.lib().iq_ep_barrier(self._h, _stream_ptr(stream), 1 if then_plan else 0))
 
     def plan(self, stream=None):
         self.ctx.check(capi.lib().iq_ep_plan(self._h, _stream_ptr(stream)))
@@ -180,8 +195,20 @@ class DeviceExchange:
 
     def return_push(self, yd: torch.Tensor, stream=None):
         dt = capi.IQ_F32 if yd.dtype == torch.float32 else capi.IQ_F16
-        self.ctx.check(capi.lib().iq_ep_return_push(self._h, _stream_ptr(stream), yd.data_ptr(), dt, self.max_rows,
-                                                    self.d_model))
+        self.ctx.check(capi.lib().iq_ep_return_push(self._h, _stream_ptr(stream), yd.data_ptr(), dt, self.d_model))
+
+    def compact(self, rows_out: torch.Tensor, table: torch.Tensor, stream=None) -> int:
+        """Gathers the received rows expert-major into rows_out and fills `table` with their return addresses; returns
+        the device address of this rank's per-expert row totals ([experts] uint32)."""
+        dt = capi.IQ_F32 if self.yd_dtype == torch.float32 else capi.IQ_F16
+        merged = C.c_void_p()
+        self.ctx.check(capi.lib().iq_ep_compact(self._h, _stream_ptr(stream), self.recv.data_ptr(), self.d_model, dt,
+                                                rows_out.data_ptr(), table.data_ptr(), C.byref(merged)))
+        return merged.value
+
+    def return_rows(self, table: torch.Tensor, stream=None):
+        dt = capi.IQ_F32 if self.yd_dtype == torch.float32 else capi.IQ_F16
+        self.ctx.check(capi.lib().iq_ep_return_rows(self._h, _stream_ptr(stream), dt, self.d_model, table.data_ptr()))
 
     def close(self):
         if self._h:

@@ -162,11 +162,15 @@ class MoELayer:
         return n.value
 
     def experts(self, rows_f16: torch.Tensor, total_rows: int, counts: torch.Tensor, sources: int, yd: torch.Tensor,
-                workspace: torch.Tensor, stream=None):
-        """Gate/up/activation/down of this layer's own experts on received rows (source-major, expert order)."""
+                workspace: torch.Tensor, region_rows: int = 0, yd_rows: Optional[torch.Tensor] = None, stream=None):
+        """Gate/up/activation/down of this layer's own experts on received rows (source-major, expert order). yd_rows:
+        int64 device tensor of one address per row; the outputs go there instead of into yd. counts: an int32 device
+        tensor [sources, experts] or the device address of one."""
         self.ctx.check(capi.lib().iq_moe_experts(self._h, _stream_ptr(stream), rows_f16.data_ptr(), total_rows,
-                                                 rows_f16.shape[0], counts.data_ptr(), sources, yd.data_ptr(),
-                                                 _dtype_id(yd), workspace.data_ptr(), workspace.numel()))
+                                                 rows_f16.shape[0], counts.data_ptr() if hasattr(counts, "data_ptr") else int(counts),
+                                                 sources, region_rows, yd.data_ptr(),
+                                                 _dtype_id(yd), 0 if yd_rows is None else yd_rows.data_ptr(),
+                                                 workspace.data_ptr(), workspace.numel()))
 
     def combine_rows(self, yd_rows: torch.Tensor, out: torch.Tensor, tokens: int, accumulate: bool = False, stream=None):
         self.ctx.check(capi.lib().iq_moe_combine_rows(self._h, _stream_ptr(stream), yd_rows.data_ptr(), _dtype_id(yd_rows),

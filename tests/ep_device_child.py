@@ -22,7 +22,7 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl")
     rng = np.random.default_rng(11)
-    E, K, D, I, T = 32, 4, 256, 128, 90
+    E, K, D, I, T = 32, 4, 256, 128, 391  # enough rows per expert for the tensor-core kernels
     g, u, d = synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, D, I, 4, E)
     wr = synth.router_np(rng, E, D)
     x = synth.activations_np(rng, T, D)
@@ -30,8 +30,10 @@ def main():
     mk = lambda t: synth.dense_q_affine(t[0][lo:lo + per], t[1][lo:lo + per], t[2][lo:lo + per], 4, dev)
     tl, tn = ep.token_slice(rank, world, T)
     layer = MoELayer(RouterSpec(E, K), synth.bf16_values_tensor(wr, dev), mk(g), mk(u), mk(d), expert_lo=lo, max_tokens=tn)
+    tmax = -(-T // world)  # the region size must be the same on every rank
+    yd_dtype = torch.float16 if "f16" in sys.argv[1:] else torch.float32
     epl = ep.ExpertParallelMoE(layer, None, tn, T * K)
-    dx = ep.DeviceExchange(E, K, D, tn, T * K, torch.float32, dev)
+    dx = ep.DeviceExchange(E, K, D, tmax, yd_dtype, dev, fused_return="copy" not in sys.argv[1:])
     epl.use_device_exchange(dx)
     xt = torch.from_numpy(x[tl:tl + tn]).to(dev).to(torch.bfloat16)
     out = torch.zeros(tn, D, dtype=torch.float32, device=dev)

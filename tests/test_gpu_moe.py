@@ -171,6 +171,31 @@ def test_route_kernel_ties_e512_k10_and_edge_rows(cuda_device):
     assert qref.max_rel(wts.cpu().numpy()[ok], rw[ok]) <= 1e-5
 
 
+@pytest.mark.parametrize("T", [3, 200])
+def test_router_8bit_affine(cuda_device, T):
+    """A router stored as 8-bit affine codes (MoE.swift:258-273 keeps the router quantized when the checkpoint does): the
+    logits are the float64 dot products with the fp32 weights s*q + b, bit for bit, through both router kernels."""
+    rng = np.random.default_rng(70 + T)
+    E, K, D, I = 64, 4, 256, 128
+    g, u, d = synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, D, I, 4, E)
+    mk = lambda t: synth.dense_q_affine(t[0], t[1], t[2], 4, cuda_device)
+    rw, rs, rb = synth.affine_np(rng, E, D, 8)
+    dev_t = lambda a, dt: torch.from_numpy(a[0].view(dt).copy()).to(cuda_device)
+    layer = MoELayer(RouterSpec(E, K), dev_t(rw, np.int32), mk(g), mk(u), mk(d), max_tokens=T,
+                     router_scales=dev_t(rs, np.int16).view(torch.bfloat16), router_biases=dev_t(rb, np.int16).view(torch.bfloat16))
+    x = synth.activations_np(rng, T, D)
+    xt = x_tensor(x, cuda_device)
+    out = torch.zeros(T, D, dtype=torch.float32, device=cuda_device)
+    layer.encode(xt, out, T, only=("router", "route"))
+    torch.cuda.synchronize()
+    v = layer.views(T)
+    wr = qref.dequant_affine(rw[0], rs[0], rb[0], 8)
+    logits = qref.router_logits(x, wr)
+    assert np.array_equal(v["logits"][:, :E].cpu().numpy(), logits)
+    inds, _ = qref.route(logits, K)
+    assert np.array_equal(v["inds"].cpu().numpy().astype(np.uint32), inds)
+
+
 def test_moe_load_guards(cuda_device):
     """Shapes the reference refuses at load (MoE.swift:186-219) come back as named errors."""
     rng = np.random.default_rng(3)
