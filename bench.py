@@ -318,7 +318,7 @@ def run_ours(args):
 
     # decode batch of 64 through the same stack
     dec = None
-    if d_n > 0:
+    if d_n > 0 and args.only is None:
         rd0 = r0_dev[:d_n].clone() if t_n >= d_n else torch.randn(d_n, D, device=dev)
         rd = torch.empty_like(rd0)
 
@@ -333,7 +333,9 @@ def run_ours(args):
 
     # the dominant kernel of the prefill stack: the experts' gate+up GEMM; timed alone over the layers (rank 0's share)
     roof = None
-    launches_per_layer = 9 if world == 1 else 16
+    # kernels per layer: norm, router, top-k, count, scatter, pack, gate/up, down, combine; expert-parallel: norm, router,
+    # top-k, count, scatter, pack+push, barrier(+plan), compact, tile list, gate/up, down(+return), barrier, combine
+    launches_per_layer = 9 if world == 1 else 13
     if world == 1:
         xn = stack.xn
 
@@ -352,8 +354,8 @@ def run_ours(args):
 
     line = None
     if rank == 0:
-        qmv = bench_qmv(torch, dev, peaks)
-        qmm = bench_qmm(torch, dev, peaks)
+        qmv = bench_qmv(torch, dev, peaks) if args.only is None else None
+        qmm = bench_qmm(torch, dev, peaks) if args.only is None else None
         from ingot_b200 import capi
         status = capi.context(local).device_status()
         line = {
@@ -375,7 +377,7 @@ def run_ours(args):
                                                         "note": "per-kernel timing is taken at N=1"},
             "decode": dec, "qmv": qmv, "qmm": qmm,
         }
-        if world == 1:
+        if world == 1 and args.only is None:
             line["cpu_baseline"] = cpu_baseline(sample_tokens=args.cpu_tokens, reps=1)
     if world > 1:
         dist.barrier()
@@ -481,8 +483,18 @@ def main():
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS)
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--cpu-tokens", type=int, default=1024, help="tokens of the bounded CPU sample")
+    ap.add_argument("--only", choices=["stack", "qmv", "qmm"], default=None,
+                    help="run one part alone (small profiling runs): the MoE stack without its side results, or the "
+                         "GEMV / GEMM micro-benchmarks")
     args = ap.parse_args()
     claim_stdout()
+    if args.only in ("qmv", "qmm"):
+        import torch
+
+        torch.cuda.set_device(0)
+        fn = bench_qmv if args.only == "qmv" else bench_qmm
+        emit(fn(torch, torch.device("cuda", 0), measured_peaks()))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

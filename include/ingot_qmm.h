@@ -224,7 +224,7 @@ int32_t iq_moe_experts_workspace_bytes(const iq_moe* layer, int32_t max_rows, in
  * by source, then expert: packed one source after the other when region_rows == 0, or source s starting at row
  * s*region_rows); yd: fp16 or fp32, same row positions. yd_rows (device array of max_rows addresses, or null): when
  * given, the output of row r goes to yd_rows[r] (d_model elements of yd_dtype, 16-byte aligned, any memory this GPU can
- * store to, a peer's included; 0 = row unused) and yd is scratch. */
+ * store to, a peer's included; 0 = row unused) by a copy kernel that follows the experts, and yd is scratch. */
 int32_t iq_moe_experts(iq_moe* layer, void* stream, const void* rows_f16, int32_t total_rows, int32_t max_rows,
                        const uint32_t* counts, int32_t sources, int32_t region_rows, void* yd, int32_t yd_dtype,
                        void* const* yd_rows, void* workspace, size_t workspace_bytes);
@@ -241,7 +241,7 @@ int32_t iq_moe_combine_rows(iq_moe* layer, void* stream, const void* yd_rows, in
  *   iq_moe_forward(ROUTER|ROUTE|GROUP); iq_ep_pack_push; iq_ep_barrier(then_plan = 1);
  *   iq_moe_experts(recv, counts = own counts matrix, region_rows); iq_ep_return_push; iq_ep_barrier(0);
  *   (or, faster: iq_ep_compact, then iq_moe_experts(compacted rows, merged counts, 1 source, yd_rows = table), and no
- *   iq_ep_return_push: the down projection stores its rows straight into the sources' return buffers)
+ *   iq_ep_return_push: the rows go from yd straight into the sources' return buffers through the table)
  *   iq_moe_combine_rows(back).
  * Rows move with plain 16-byte peer stores (no TMA, no multicast). Every rank must run the same sequence; the barrier's
  * wait is bounded (IQ_ERR_TIMEOUT in iq_ctx_status when a peer never arrives). At most 8 ranks. */
@@ -264,8 +264,7 @@ int32_t iq_ep_pack_push(iq_ep* ep, void* stream, const void* x, int32_t x_dtype,
 /* Expert outputs of the received rows ([world * region_rows, d_model], the layout of recv) stored back into each
  * source's return buffer at the source's sorted positions. */
 int32_t iq_ep_return_push(iq_ep* ep, void* stream, const void* yd, int32_t yd_dtype, int32_t d_model);
-/* The same mapping as a table for iq_moe_experts' yd_rows (device array of world * region_rows addresses): the down
- * projection then stores each output row straight into its source rank's return buffer and no copy kernel runs. */
+/* The same mapping as a table for iq_moe_experts' yd_rows (device array of world * region_rows addresses). */
 int32_t iq_ep_return_rows(iq_ep* ep, void* stream, int32_t yd_dtype, int32_t d_model, void** table);
 /* Received rows gathered out of their regions into expert-major order (rows_out, fp16 [world * region_rows, d_model]):
  * all sources' rows of one expert end up next to each other, so the grouped GEMM dequantises each weight tile once per

@@ -53,7 +53,6 @@ struct GqmvCall {
     int32_t rows = 1;
     int32_t max_rows = 1;
     void* y = nullptr;
-    const uint64_t* y_row_ptr = nullptr;  // grouped mode: one address per output row instead of y
     int32_t y_dtype = 0;
     int64_t ldy = 0;
     int32_t accumulate = 0;
@@ -80,7 +79,6 @@ struct QmmCall {
     const Tile* tiles = nullptr;
     const uint32_t* ntiles = nullptr;
     void* y = nullptr;
-    const uint64_t* y_row_ptr = nullptr;  // grouped mode: one address per output row instead of y
     int32_t y_dtype = 0;
     int64_t ldy = 0;
     int32_t accumulate = 0;

@@ -183,7 +183,7 @@ int32_t run_gateup_tc(iq_moe* l, cudaStream_t cs, const __half* rows16, int64_t 
 }
 
 int32_t run_down_tc(iq_moe* l, cudaStream_t cs, const __half* h, int64_t n_rows, const Tile* tiles, const uint32_t* ntiles,
-                    void* yd, int32_t yd_dtype, int bn, const uint64_t* yd_rows = nullptr) {
+                    void* yd, int32_t yd_dtype, int bn) {
     const iq_moe_desc& d = l->d;
     QmmCall c;
     c.fmt = l->fmt; c.epi = 0; c.bn = bn;
@@ -192,9 +192,17 @@ int32_t run_down_tc(iq_moe* l, cudaStream_t cs, const __half* h, int64_t n_rows,
     c.experts = d.expert_count; c.expert_lo = d.expert_lo;
     c.N = d.d_model; c.K = d.d_ff; c.M = (int32_t)n_rows;
     c.tiles = tiles; c.ntiles = ntiles;
-    c.y = yd; c.y_row_ptr = yd_rows; c.y_dtype = yd_dtype; c.ldy = d.d_model;
+    c.y = yd; c.y_dtype = yd_dtype; c.ldy = d.d_model;
     c.ebias[0] = d.down_bias;
     return launch_qmm(l->ctx, cs, c);
+}
+
+// The experts' kernels wrote yd; the rows then go where the caller's table points (peer memory included).
+int32_t scatter_rows(iq_ctx* ctx, cudaStream_t cs, const void* yd, void* const* yd_rows, int max_rows, int d_model,
+                     int32_t yd_dtype) {
+    const int row_bytes = d_model * (yd_dtype == kF32 ? 4 : 2);
+    moe_scatter_rows_kernel<<<(max_rows + 3) / 4, 256, 0, cs>>>(yd, reinterpret_cast<const uint64_t*>(yd_rows), max_rows, row_bytes);
+    return check_cuda(ctx, cudaGetLastError(), "moe_scatter_rows launch");
 }
 
 }  // namespace
@@ -578,8 +586,8 @@ extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16,
         int32_t st2 = check_cuda(ctx, cudaGetLastError(), "ep_tiles launch");
         // the row count is only known on the device: bounds come from the capacity, total_rows picks the kernels
         if (st2 == kOk) st2 = run_gateup_tc(l, cs, static_cast<const __half*>(rows_f16), max_rows, w.tiles, w.ntiles, w.h, bn);
-        if (st2 == kOk)
-            st2 = run_down_tc(l, cs, w.h, max_rows, w.tiles, w.ntiles, yd, yd_dtype, bn, reinterpret_cast<const uint64_t*>(yd_rows));
+        if (st2 == kOk) st2 = run_down_tc(l, cs, w.h, max_rows, w.tiles, w.ntiles, yd, yd_dtype, bn);
+        if (st2 == kOk && yd_rows != nullptr) st2 = scatter_rows(ctx, cs, yd, yd_rows, max_rows, d.d_model, yd_dtype);
         return st2;
     }
     const int bm = total_rows <= slots * 6 ? 8 : 16;
@@ -594,10 +602,7 @@ extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16,
     if (st != kOk) return st;
     st = run_down(l, cs, w.h, w.tiles, w.ntiles, max_tiles, bm, yd, yd_dtype);
     if (st != kOk || yd_rows == nullptr) return st;
-    // few rows per expert: the tile kernels wrote yd; the rows then go where the caller's table points
-    const int row_bytes = d.d_model * (yd_dtype == kF32 ? 4 : 2);
-    moe_scatter_rows_kernel<<<(max_rows + 3) / 4, 256, 0, cs>>>(yd, reinterpret_cast<const uint64_t*>(yd_rows), max_rows, row_bytes);
-    return check_cuda(ctx, cudaGetLastError(), "moe_scatter_rows launch");
+    return scatter_rows(ctx, cs, yd, yd_rows, max_rows, d.d_model, yd_dtype);
 }
 
 extern "C" int32_t iq_moe_combine_rows(iq_moe* l, void* stream, const void* yd_rows, int32_t yd_dtype, int32_t tokens,

@@ -1,6 +1,4 @@
 // Host side of the tcgen05 GEMM: tensor maps, kernel selection, the iq_qmm entry point.
-#include <stdlib.h>
-
 #include "internal.h"
 #include "qmm_tc.cuh"
 
@@ -101,13 +99,10 @@ int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
     p.expert_lo = c.expert_lo;
     p.N = c.N; p.K = c.K; p.M = c.M;
     p.tiles = c.tiles; p.ntiles = c.ntiles;
-    p.y = c.y; p.y_row_ptr = c.y_row_ptr; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
+    p.y = c.y; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
     p.limit = c.limit;
     p.status = ctx->d_status;
-    {
-        const char* dbg = getenv("INGOT_QMM_DEBUG");
-        p.debug = dbg ? atoi(dbg) : 0;
-    }
+    p.reserved = 0;
     int grid = ctx->sms;
     if (c.tiles == nullptr) {
         const int work = ((c.M + c.bn - 1) / c.bn) * ((c.N + kWRows - 1) / kWRows);

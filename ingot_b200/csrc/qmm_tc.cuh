@@ -45,14 +45,14 @@ struct QmmParams {
     const uint32_t* ntiles;
     // output
     void* y;
-    const uint64_t* y_row_ptr;  // grouped mode, optional: address of every output row (peers' memory included); y unused
     int32_t y_dtype;
     int64_t ldy;
     int32_t accumulate;
     const float* ebias[2];   // fp32 [E, N] or null
     float limit;
     int32_t* status;         // device status word (0 = ok)
-    int32_t debug;           // experiments: 1 = dequantisers publish without converting, 2 = producer loads no X tile
+    int32_t reserved;        // keeps the parameter block off an exact 512 bytes: at that size the fused gate/up kernel
+                             // measured a quarter slower (487 against 386 us on the 4096-token layer), same code otherwise
 };
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes
@@ -225,8 +225,8 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!(ok = mbar_wait_relaxed(bar_empty + 8 * s, ph ^ 1, abort_flag))) break;
                     unsigned char* st = smem + s * S::STAGE_BYTES;
-                    mbar_arrive_expect_tx(bar_full + 8 * s, (p.debug == 2 ? 0 : S::X_BYTES) + NWT * S::WP_BYTES);
-                    if (p.debug != 2) tma_load_2d(smem_u32(st), &map_x, bar_full + 8 * s, ks * kBK, row0);
+                    mbar_arrive_expect_tx(bar_full + 8 * s, S::X_BYTES + NWT * S::WP_BYTES);
+                    tma_load_2d(smem_u32(st), &map_x, bar_full + 8 * s, ks * kBK, row0);
                     const int wrow = (int)expert * p.N + n0;
                     tma_load_2d(smem_u32(st + S::X_BYTES + NWT * S::WD_BYTES), &map_w0, bar_full + 8 * s,
                                 ks * S::PACK_ROW, wrow);
@@ -306,22 +306,15 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                         const float u = __uint_as_float(r1[j]) + bias1;
                         v = p.limit > 0.f ? glu<kActSwigluOai>(g, u, p.limit) : glu<kActSilu>(g, u, 0.f);
                     }
-                    // a row either sits in y or, when the caller gave one address per row, wherever that points:
-                    // the expert outputs of an expert-parallel layer go straight into their source rank's memory
-                    size_t o = (size_t)(row0 + c0 + j) * p.ldy + n;
-                    void* ybase = p.y;
-                    if (p.y_row_ptr != nullptr) {
-                        ybase = reinterpret_cast<void*>(p.y_row_ptr[row0 + c0 + j]);
-                        o = n;
-                    }
+                    const size_t o = (size_t)(row0 + c0 + j) * p.ldy + n;
                     if (p.y_dtype == kF32) {
-                        float* yp = reinterpret_cast<float*>(ybase) + o;
+                        float* yp = reinterpret_cast<float*>(p.y) + o;
                         *yp = p.accumulate ? *yp + v : v;
                     } else if (p.y_dtype == kF16) {
-                        __half* yp = reinterpret_cast<__half*>(ybase) + o;
+                        __half* yp = reinterpret_cast<__half*>(p.y) + o;
                         *yp = __float2half_rn(p.accumulate ? __half2float(*yp) + v : v);
                     } else {
-                        uint16_t* yp = reinterpret_cast<uint16_t*>(ybase) + o;
+                        uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + o;
                         *yp = (uint16_t)f32_to_bf16_bits(p.accumulate ? bf16_bits_to_f32(*yp) + v : v);
                     }
                 }
@@ -382,7 +375,6 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
             const uint32_t st = smem_u32(smem + s * S::STAGE_BYTES);
 #pragma unroll
             for (int wt = 0; wt < NWT; wt++) {
-                if (p.debug == 1) break;
                 const uint32_t wd = st + S::X_BYTES + wt * S::WD_BYTES + (row >> 3) * 1024 + sw * 128;
 #pragma unroll
                 for (int half = 0; half < 2; half++) {

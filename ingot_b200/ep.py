@@ -99,8 +99,8 @@ class ExpertParallelMoE:
         dx.barrier(then_plan=True)
         # the kernels are picked for the rows this rank expects to receive (about as many as it sends)
         if dx.fused_return:
-            # rows gathered expert-major (one run of rows per expert, whatever their source); the down projection then
-            # stores its output rows straight into the sources' return buffers
+            # rows gathered expert-major (one run of rows per expert, whatever their source); the expert outputs then
+            # go through the table of return addresses straight into the sources' buffers
             merged = dx.compact(b["xc_dx"], b["rows_dx"])
             L.experts(b["xc_dx"], min(rows * k, dx.max_rows), merged, 1, b["yd_dx"], b["ws_dx"], yd_rows=b["rows_dx"])
         else:
