@@ -7,6 +7,7 @@
 
 #include "gqmv.cuh"
 #include "internal.h"
+#include "qmv_imma.cuh"
 #include "qmv_stream.cuh"
 
 namespace iq {
@@ -155,9 +156,78 @@ int32_t launch_qmv_stream(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     return check_cuda(ctx, cudaLaunchKernelEx(&cfg, k, p), "qmv_stream launch");
 }
 
+// ---- int8 tensor-core path (decode, up to four rows, affine codes) -----------------------------------------------
+// Returns kOk after a launch, 1 when the shape does not fit this path (the caller falls back), or an error.
+int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
+    if (c.mode != kModePlain || c.tiles != nullptr || c.rows > 16 || c.rows < 1) return 1;
+    if (c.fmt != kFmtAffine4 && c.fmt != kFmtAffine8) return 1;
+    if (c.K % 2048 != 0 || c.N < kQiRows) return 1;
+    if ((reinterpret_cast<uintptr_t>(c.w[0]) & 15) || (reinterpret_cast<uintptr_t>(c.s[0]) & 15) ||
+        (reinterpret_cast<uintptr_t>(c.b[0]) & 15))
+        return 1;
+    const bool w8 = c.fmt == kFmtAffine8;
+    const int G = c.K / 64;
+    QiParams p;
+    memset(&p, 0, sizeof(p));
+    p.row_bytes = w8 ? c.K : c.K / 2;
+    p.row_pitch = p.row_bytes + (w8 ? 64 : 32);  // rows land in different banks for the fragment loads
+    p.srow_bytes = G * 2;
+    p.stage_bytes = kQiRows * p.row_pitch + 2 * kQiRows * p.srow_bytes;
+    // The path is chosen on what eight rows need, whatever the row count of this call: a row must see the same
+    // arithmetic alone and among sixteen.
+    auto fixed_bytes = [&](int ms) { return G * 512 * ms + G * 32 * ms + 4096 * ms + 256; };
+    if ((kQsSmemMax - fixed_bytes(2)) / p.stage_bytes < 2) return 1;
+    p.w = reinterpret_cast<const unsigned char*>(c.w[0]);
+    p.s = reinterpret_cast<const unsigned char*>(c.s[0]);
+    p.b = reinterpret_cast<const unsigned char*>(c.b[0]);
+    p.N = c.N; p.K = c.K;
+    p.x_dtype = c.x_dtype; p.ldx = c.ldx;
+    p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
+    p.status = ctx->d_status;
+    const int blocks = c.N / kQiRows;
+    const size_t xes = c.x_dtype == kF32 ? 4 : 2, yes = c.y_dtype == kF32 ? 4 : 2;
+    for (int m0 = 0; m0 < c.rows; m0 += 8) {  // nine to sixteen rows: two launches of up to eight
+        const int m = c.rows - m0 < 8 ? c.rows - m0 : 8;
+        const int ms = m > 4 ? 2 : 1;
+        p.M = m;
+        p.x = static_cast<const char*>(c.x) + (size_t)m0 * c.ldx * xes;
+        p.y = static_cast<char*>(c.y) + (size_t)m0 * c.ldy * yes;
+        p.xq_bytes = G * 512 * ms;
+        p.xsc_bytes = G * 32 * ms;
+        int nstages = (kQsSmemMax - fixed_bytes(ms)) / p.stage_bytes;
+        if (nstages > 8) nstages = 8;
+        p.nstages = nstages;
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(blocks < ctx->sms ? blocks : ctx->sms, 1, 1);
+        cfg.blockDim = dim3(kQiThreads, 1, 1);
+        cfg.dynamicSmemBytes = fixed_bytes(ms) + nstages * p.stage_bytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e;
+        if (w8) e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 2>, p) : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 1>, p);
+        else e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 2>, p) : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 1>, p);
+        const int32_t r = check_cuda(ctx, e, "qmv_imma launch");
+        if (r != kOk) return r;
+    }
+    return kOk;
+}
+
 }  // namespace
 
 int32_t gqmv_init(iq_ctx* ctx) {
+    const void* qi[4] = {reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 1>),
+                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 2>),
+                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 1>),
+                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 2>)};
+    for (int i = 0; i < 4; i++) {
+        cudaError_t e = cudaFuncSetAttribute(qi[i], cudaFuncAttributeMaxDynamicSharedMemorySize, kQsSmemMax);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_imma)");
+    }
     for (int fmt = 0; fmt < 3; fmt++)
         for (int mh = 1; mh <= 2; mh++)
             for (int mode = 0; mode < 3; mode++)
@@ -175,11 +245,15 @@ int32_t gqmv_init(iq_ctx* ctx) {
                 if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_stream)");
             }
     const char* env = getenv("INGOT_QMV_PATH");
-    g_path = env == nullptr ? 0 : (strcmp(env, "legacy") == 0 ? 1 : (strcmp(env, "stream") == 0 ? 2 : 0));
+    g_path = env == nullptr ? 0 : (strcmp(env, "legacy") == 0 ? 1 : (strcmp(env, "stream") == 0 ? 2 : 0));  // both: no int8 path
     return kOk;
 }
 
 int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
+    if (g_path == 0) {
+        const int32_t r = launch_qmv_imma(ctx, st, c);
+        if (r != 1) return r;
+    }
     if (g_path != 1) {
         const int32_t r = launch_qmv_stream(ctx, st, c);
         if (r != 1) return r;

@@ -1,0 +1,302 @@
+// Decode GEMV on the int8 tensor-core path: y[m, n] = sum_k x[m, k] * (s[n, g] * q[n, k] + b[n, g]) for up to eight
+// activation rows per launch (the host cuts 9..16 rows into two launches) and affine 4- or 8-bit weights.
+//
+// Why integers. The fp16 formulation converts every code to a half (several ALU instructions per code) before the MMA
+// and ends up bound by instruction issue at a third of the memory roofline. Here the codes go into the MMA as they
+// are: 8-bit codes untouched, 4-bit codes split by two masks per 32-bit word. The activations are what gets
+// converted, once per call: per group of 64 inputs they become block fixed point, X = round(x * 2^(13 - e)) with
+// 2^e >= max|x| of the group, split into two signed 7-bit digits X = 128 * hi + lo. The digits are the B operand
+// (m16n8k32, u8 x s8 -> s32): the eight B columns are (row, digit) pairs, so one MMA serves four rows (rows 4..7 take
+// a second pair of MMAs on the same unpacked codes). A row's arithmetic does not depend on the other rows of the
+// call, which is what makes its bits the same alone, among 4 and among 16. Per group the
+// exact integer sums give
+//     sum_k x q  ~=  2^(e - 13) * (128 * acc_hi + acc_lo)        (error <= 2^-14 of the group's largest |x| per input)
+// and the group's contribution is s * that + b * sum_k x, with sum_k x kept in fp32. That is two MMAs, two integer
+// and six float instructions per 64 x 16 weights, against several hundred in the fp16 formulation.
+//
+// Structure: one persistent CTA per SM owns a contiguous range of weight rows (any length: the bytes are what has to
+// balance) and walks it 16 rows at a time. Warp 8 streams each 16-row block through a ring of bulk copies (one per
+// row, into rows padded so that the fragment loads are free of bank conflicts, plus scales and biases); warps 0-7
+// take one eighth of K each, and their partial sums meet in shared memory in a fixed order. Every wait is bounded.
+//
+// Same operator as the reference's vnax_qmv* kernels (Shaders/verify_nax.metal:105-230); taken when K is a multiple
+// of 2048 and the activations of eight rows plus two stages fit shared memory (a choice that does not look at the row
+// count), the fp16 kernels serve the rest.
+#pragma once
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace iq {
+
+constexpr int kQiThreads = 288;     // 8 consumer warps + 1 producer warp
+constexpr int kQiRows = 16;         // weight rows per stage (MMA M)
+constexpr int kQiPiece = 8192;      // bytes per bulk copy
+
+struct QiParams {
+    const unsigned char* w;
+    const unsigned char* s;
+    const unsigned char* b;
+    int32_t N, K, M;
+    const void* x;
+    int32_t x_dtype;
+    int64_t ldx;
+    void* y;
+    int32_t y_dtype;
+    int64_t ldy;
+    int32_t accumulate;
+    int32_t row_bytes;    // code bytes per weight row
+    int32_t row_pitch;    // ... and the padded pitch of a row inside a stage
+    int32_t srow_bytes;   // scale bytes per weight row (= bias bytes)
+    int32_t stage_bytes, nstages;
+    int32_t xq_bytes, xsc_bytes;
+    int32_t* status;
+};
+
+__device__ __forceinline__ void imma16832_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1, const int (&c)[4]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ void qi_consumer_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ bool qi_consumer_barrier_or(bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n.reg .pred p, q;\nsetp.ne.u32 p, %1, 0;\nbar.red.or.pred q, 1, 256, p;\nselp.u32 %0, 1, 0, q;\n}\n"
+        : "=r"(r)
+        : "r"((uint32_t)pred)
+        : "memory");
+    return r != 0;
+}
+
+template <int FMT, int MS>  // kFmtAffine4 or kFmtAffine8; MS sets of four activation rows (1 or 2)
+__global__ void __launch_bounds__(kQiThreads, 1) qmv_imma_kernel(const QiParams p) {
+    constexpr bool W8 = FMT == kFmtAffine8;
+    constexpr int GB = W8 ? 64 : 32;  // code bytes per group of 64 inputs
+    extern __shared__ __align__(16) unsigned char smem[];
+    unsigned char* xq = smem;                                            // [groups][MS][32 lanes] uint4: B fragments
+    float2* xsc = reinterpret_cast<float2*>(smem + p.xq_bytes);          // [groups][MS * 4 rows] {2^(e-13), sum x}
+    float* red = reinterpret_cast<float*>(smem + p.xq_bytes + p.xsc_bytes);  // [2][8 warps][MS][32 lanes][2]
+    unsigned char* stages = smem + p.xq_bytes + p.xsc_bytes + 4096 * MS;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(stages + (size_t)p.nstages * p.stage_bytes);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * p.nstages;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * p.nstages);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        for (int s = 0; s < p.nstages; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 8);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    // this CTA's rows: a contiguous range, cut 16 rows at a time
+    const int lo = (int)((int64_t)p.N * blockIdx.x / gridDim.x), hi = (int)((int64_t)p.N * (blockIdx.x + 1) / gridDim.x);
+    const int items = (hi - lo + kQiRows - 1) / kQiRows;
+    const int G = p.K / 64;
+    const int codes_bytes = kQiRows * p.row_pitch;
+    const int sc_bytes = kQiRows * p.srow_bytes;
+
+    if (warp == 8) {
+        // ================= producer: weights do not depend on the previous kernel, so it starts at once =========
+        bool ok = true;
+        for (int it = 0; it < items && ok; it++) {
+            const int s = it % p.nstages;
+            const uint32_t ph = (it / p.nstages) & 1;
+            const int r0 = lo + it * kQiRows;
+            const int rows = min(kQiRows, hi - r0);
+            ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, rows * (p.row_bytes + 2 * p.srow_bytes));
+            __syncwarp();
+            const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
+            if (lane < rows) {
+                const unsigned char* src = p.w + (size_t)(r0 + lane) * p.row_bytes;
+                for (int off = 0; off < p.row_bytes; off += kQiPiece)
+                    bulk_g2s(st + lane * p.row_pitch + off, src + off, min(kQiPiece, p.row_bytes - off), bar_full + 8 * s);
+            } else if (lane == 16) {
+                bulk_g2s(st + codes_bytes, p.s + (size_t)r0 * p.srow_bytes, rows * p.srow_bytes, bar_full + 8 * s);
+            } else if (lane == 17) {
+                bulk_g2s(st + codes_bytes + sc_bytes, p.b + (size_t)r0 * p.srow_bytes, rows * p.srow_bytes, bar_full + 8 * s);
+            }
+        }
+        if (!ok) {  // give copies in flight time to land before the CTA's shared memory is released
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000) {}
+        }
+    } else {
+        // ================= consumers =================
+        pdl_wait();  // the activations (and y) belong to the previous kernel until here
+        // ---- activations -> block fixed point, two 7-bit digits, in B-fragment order --------------------------------
+        for (int u = tid; u < G * 4 * MS; u += 256) {
+            const int j = u / (4 * MS), m = u % (4 * MS);
+            float v[64];
+            float amax = 0.f, sum = 0.f;
+            if (m < p.M) {
+#pragma unroll
+                for (int c = 0; c < 8; c++) load_x8(p.x, p.x_dtype, (size_t)m * p.ldx + j * 64 + c * 8, *reinterpret_cast<float (*)[8]>(&v[c * 8]));
+#pragma unroll
+                for (int k = 0; k < 64; k++) {
+                    amax = fmaxf(amax, fabsf(v[k]));
+                    sum += v[k];
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < 64; k++) v[k] = 0.f;
+            }
+            float scale = 0.f, inv = 0.f;
+            if (amax > 0.f && amax < 3.0e38f) {
+                int e;
+                frexpf(amax, &e);               // amax = f * 2^e, 0.5 <= f < 1
+                e = max(e, -100);
+                scale = ldexpf(1.f, e - 13);
+                inv = ldexpf(1.f, 13 - e);
+            }
+            xsc[j * 4 * MS + m] = make_float2(scale, sum);
+            const int fb = ((j * MS + (m >> 2)) * 32 + 8 * (m & 3)) * 16;  // the row's hi-digit column, lane t = 0
+#pragma unroll
+            for (int k = 0; k < 64; k++) {
+                const int X = __float2int_rn(v[k] * inv);       // |X| <= 8192
+                const int hi_d = (X + 64) >> 7, lo_d = X - (hi_d << 7);
+                // where input k of the group sits in the fragments: lane t of the four that share a column, MMA mm of
+                // the group's two, register half (b0 / b1), byte i
+                int t, mm, half, i;
+                if (W8) {
+                    const int word = k >> 2;
+                    t = word >> 2; mm = (word >> 1) & 1; half = word & 1; i = k & 3;
+                } else {
+                    const int word = k >> 3, r = k & 7;
+                    t = word >> 1; mm = word & 1; half = r & 1; i = r >> 1;
+                }
+                const int off = mm * 8 + half * 4 + i;
+                xq[fb + t * 16 + off] = (unsigned char)(hi_d & 0xFF);
+                xq[fb + (4 + t) * 16 + off] = (unsigned char)(lo_d & 0xFF);
+            }
+        }
+        qi_consumer_barrier();
+
+        const int g = lane >> 2, t = lane & 3;
+        const int gw = G / 8;                       // groups per warp (a multiple of 4)
+        const int g0 = warp * gw;
+        const uint32_t xq32 = smem_u32(xq) + lane * 16, xsc32 = smem_u32(xsc) + t * 8;
+        for (int it = 0; it < items; it++) {
+            const int s = it % p.nstages;
+            const uint32_t ph = (it / p.nstages) & 1;
+            const int r0 = lo + it * kQiRows;
+            const int rows = min(kQiRows, hi - r0);
+            const bool ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+            float acc0[MS], acc1[MS];  // rows g and g + 8 of the block, activation rows t, 4 + t
+#pragma unroll
+            for (int c = 0; c < MS; c++) acc0[c] = acc1[c] = 0.f;
+            if (ok) {
+                const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
+                const uint32_t wa0 = st + g * p.row_pitch + t * (W8 ? 16 : 8), wa1 = wa0 + 8 * p.row_pitch;
+                const uint32_t sa0 = st + codes_bytes + g * p.srow_bytes, sa1 = sa0 + 8 * p.srow_bytes;
+                for (int c4 = 0; c4 < gw; c4 += 4) {
+                    // scales and biases of four groups for both rows (bf16 pairs)
+                    const uint2 s0 = lds64(sa0 + (g0 + c4) * 2), s1 = lds64(sa1 + (g0 + c4) * 2);
+                    const uint2 b0 = lds64(sa0 + sc_bytes + (g0 + c4) * 2), b1 = lds64(sa1 + sc_bytes + (g0 + c4) * 2);
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int grp = g0 + c4 + q;
+                        const int z[4] = {0, 0, 0, 0};
+                        uint32_t a[2][4];  // the A fragments of the group's two MMAs
+                        if (W8) {
+                            const uint4 w0 = lds128(wa0 + grp * GB), w1 = lds128(wa1 + grp * GB);
+                            a[0][0] = w0.x; a[0][1] = w1.x; a[0][2] = w0.y; a[0][3] = w1.y;
+                            a[1][0] = w0.z; a[1][1] = w1.z; a[1][2] = w0.w; a[1][3] = w1.w;
+                        } else {
+                            const uint2 w0 = lds64(wa0 + grp * GB), w1 = lds64(wa1 + grp * GB);
+                            constexpr uint32_t MSK = 0x0F0F0F0Fu;
+                            a[0][0] = w0.x & MSK; a[0][1] = w1.x & MSK; a[0][2] = (w0.x >> 4) & MSK; a[0][3] = (w1.x >> 4) & MSK;
+                            a[1][0] = w0.y & MSK; a[1][1] = w1.y & MSK; a[1][2] = (w0.y >> 4) & MSK; a[1][3] = (w1.y >> 4) & MSK;
+                        }
+                        const uint32_t sw0 = q < 2 ? s0.x : s0.y, sw1 = q < 2 ? s1.x : s1.y;
+                        const uint32_t bw0 = q < 2 ? b0.x : b0.y, bw1 = q < 2 ? b1.x : b1.y;
+                        const float sc0 = __uint_as_float((q & 1) ? (sw0 & 0xFFFF0000u) : (sw0 << 16));
+                        const float sc1 = __uint_as_float((q & 1) ? (sw1 & 0xFFFF0000u) : (sw1 << 16));
+                        const float bi0 = __uint_as_float((q & 1) ? (bw0 & 0xFFFF0000u) : (bw0 << 16));
+                        const float bi1 = __uint_as_float((q & 1) ? (bw1 & 0xFFFF0000u) : (bw1 << 16));
+#pragma unroll
+                        for (int c = 0; c < MS; c++) {
+                            int d[4];
+                            const uint4 xb = lds128(xq32 + (grp * MS + c) * 512);
+                            imma16832_u8s8(d, a[0][0], a[0][1], a[0][2], a[0][3], xb.x, xb.y, z);
+                            imma16832_u8s8(d, a[1][0], a[1][1], a[1][2], a[1][3], xb.z, xb.w, d);
+                            const float2 xs = lds64f(xsc32 + (grp * MS + c) * 32);  // {2^(e-13), sum x} of row 4c + t
+                            const float v0 = (float)(d[0] * 128 + d[1]), v1 = (float)(d[2] * 128 + d[3]);
+                            acc0[c] = fmaf(v0, sc0 * xs.x, acc0[c]);
+                            acc0[c] = fmaf(bi0, xs.y, acc0[c]);
+                            acc1[c] = fmaf(v1, sc1 * xs.x, acc1[c]);
+                            acc1[c] = fmaf(bi1, xs.y, acc1[c]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0 && ok) mbar_arrive(bar_empty + 8 * s);  // the stage is free once every warp has read its part
+
+            // ---- the eight K slices meet in shared memory; warp 0 adds them in slice order and stores -----------------
+            float* mine = red + ((it & 1) * 8 + warp) * (64 * MS);
+#pragma unroll
+            for (int c = 0; c < MS; c++) {
+                mine[c * 64 + lane * 2] = acc0[c];
+                mine[c * 64 + lane * 2 + 1] = acc1[c];
+            }
+            if (qi_consumer_barrier_or(!ok)) break;  // a wait gave up somewhere: everybody leaves together
+            if (warp != 0) continue;
+#pragma unroll
+            for (int c = 0; c < MS; c++) {
+                const int m = 4 * c + t;
+                if (m >= p.M) continue;
+                float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    y0 += red[((it & 1) * 8 + k) * (64 * MS) + c * 64 + lane * 2];
+                    y1 += red[((it & 1) * 8 + k) * (64 * MS) + c * 64 + lane * 2 + 1];
+                }
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int r = g + 8 * h;
+                    if (r >= rows) continue;
+                    const float v = h ? y1 : y0;
+                    const size_t o = (size_t)m * p.ldy + r0 + r;
+                    if (p.y_dtype == kF32) {
+                        float* yp = reinterpret_cast<float*>(p.y) + o;
+                        *yp = p.accumulate ? *yp + v : v;
+                    } else if (p.y_dtype == kF16) {
+                        __half* yp = reinterpret_cast<__half*>(p.y) + o;
+                        *yp = __float2half_rn(p.accumulate ? __half2float(*yp) + v : v);
+                    } else {
+                        uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + o;
+                        *yp = (uint16_t)f32_to_bf16_bits(p.accumulate ? bf16_bits_to_f32(*yp) + v : v);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag && tid == 0 && p.status != nullptr) atomicExch(p.status, kErrTimeout);
+}
+
+}  // namespace iq
