@@ -79,6 +79,7 @@ constexpr int kQsSmemMax = 226 * 1024;
 
 // 0: choose per shape; 1: always the register-staged kernel; 2: the streaming kernel wherever it applies
 int g_path = 0;
+int g_qi_ctas = 2;  // INGOT_QMV_CTAS=1: one CTA per SM with a deeper ring (measured 10.7 against 10.0 us)
 
 // Returns kOk after a launch, 1 when the shape does not fit this path (the caller falls back), or an error.
 int32_t launch_qmv_stream(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
@@ -172,10 +173,12 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     p.row_bytes = w8 ? c.K : c.K / 2;
     p.row_pitch = p.row_bytes + (w8 ? 64 : 32);  // rows land in different banks for the fragment loads
     p.srow_bytes = G * 2;
-    p.stage_bytes = kQiRows * p.row_pitch + 2 * kQiRows * p.srow_bytes;
+    p.srow_pitch = p.srow_bytes;
+    p.stage_bytes = kQiRows * p.row_pitch + 2 * kQiRows * p.srow_pitch;
     // The path is chosen on what eight rows need, whatever the row count of this call: a row must see the same
     // arithmetic alone and among sixteen.
-    auto fixed_bytes = [&](int ms) { return G * 512 * ms + G * 32 * ms + 4096 * ms + 256; };
+    const int ncw = 8;  // consumer warps (16 measured slower: 11.3 against 10.0 us on the 14336 x 4096 layer)
+    auto fixed_bytes = [&](int ms) { return G * 512 * ms + G * 32 * ms + 512 * ms * ncw + 256; };
     if ((kQsSmemMax - fixed_bytes(2)) / p.stage_bytes < 2) return 1;
     p.w = reinterpret_cast<const unsigned char*>(c.w[0]);
     p.s = reinterpret_cast<const unsigned char*>(c.s[0]);
@@ -194,13 +197,18 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
         p.y = static_cast<char*>(c.y) + (size_t)m0 * c.ldy * yes;
         p.xq_bytes = G * 512 * ms;
         p.xsc_bytes = G * 32 * ms;
-        int nstages = (kQsSmemMax - fixed_bytes(ms)) / p.stage_bytes;
+        p.red_bytes = 512 * ms * ncw;
+        p.ncw = ncw;
+        // up to four rows: two CTAs per SM when each still gets two stages (twice the warps to hide latencies behind)
+        int ctas = 1;
+        if (ms == 1 && g_qi_ctas == 2 && (kQsSmemMax / 2 - 1024 - fixed_bytes(ms)) / p.stage_bytes >= 2) ctas = 2;
+        int nstages = ((ctas == 2 ? kQsSmemMax / 2 - 1024 : kQsSmemMax) - fixed_bytes(ms)) / p.stage_bytes;
         if (nstages > 8) nstages = 8;
         p.nstages = nstages;
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
-        cfg.gridDim = dim3(blocks < ctx->sms ? blocks : ctx->sms, 1, 1);
-        cfg.blockDim = dim3(kQiThreads, 1, 1);
+        cfg.gridDim = dim3(blocks < ctx->sms * ctas ? blocks : ctx->sms * ctas, 1, 1);
+        cfg.blockDim = dim3(32 * (ncw + 1), 1, 1);
         cfg.dynamicSmemBytes = fixed_bytes(ms) + nstages * p.stage_bytes;
         cfg.stream = st;
         cudaLaunchAttribute attr[1];
@@ -244,6 +252,7 @@ int32_t gqmv_init(iq_ctx* ctx) {
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kQsSmemMax);
                 if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_stream)");
             }
+    if (const char* e2 = getenv("INGOT_QMV_CTAS")) g_qi_ctas = atoi(e2);
     const char* env = getenv("INGOT_QMV_PATH");
     g_path = env == nullptr ? 0 : (strcmp(env, "legacy") == 0 ? 1 : (strcmp(env, "stream") == 0 ? 2 : 0));  // both: no int8 path
     return kOk;

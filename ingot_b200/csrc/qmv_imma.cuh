@@ -16,8 +16,8 @@
 //
 // Structure: one persistent CTA per SM owns a contiguous range of weight rows (any length: the bytes are what has to
 // balance) and walks it 16 rows at a time. Warp 8 streams each 16-row block through a ring of bulk copies (one per
-// row, into rows padded so that the fragment loads are free of bank conflicts, plus scales and biases); warps 0-7
-// take one eighth of K each, and their partial sums meet in shared memory in a fixed order. Every wait is bounded.
+// row, into rows padded so that the fragment loads are free of bank conflicts, plus scales and biases); the 8 or 16
+// consumer warps take one slice of K each, and their partial sums meet in shared memory in a fixed order. Every wait is bounded.
 //
 // Same operator as the reference's vnax_qmv* kernels (Shaders/verify_nax.metal:105-230); taken when K is a multiple
 // of 2048 and the activations of eight rows plus two stages fit shared memory (a choice that does not look at the row
@@ -29,7 +29,7 @@
 
 namespace iq {
 
-constexpr int kQiThreads = 288;     // 8 consumer warps + 1 producer warp
+constexpr int kQiMaxThreads = 544;  // up to 16 consumer warps + 1 producer warp
 constexpr int kQiRows = 16;         // weight rows per stage (MMA M)
 constexpr int kQiPiece = 8192;      // bytes per bulk copy
 
@@ -48,50 +48,66 @@ struct QiParams {
     int32_t row_bytes;    // code bytes per weight row
     int32_t row_pitch;    // ... and the padded pitch of a row inside a stage
     int32_t srow_bytes;   // scale bytes per weight row (= bias bytes)
+    int32_t srow_pitch;   // ... and their padded pitch inside a stage
     int32_t stage_bytes, nstages;
-    int32_t xq_bytes, xsc_bytes;
+    int32_t xq_bytes, xsc_bytes, red_bytes;
+    int32_t ncw;          // consumer warps (8 or 16): K slices per block of rows; the producer is warp ncw
     int32_t* status;
 };
 
 __device__ __forceinline__ void imma16832_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                                uint32_t b1, const int (&c)[4]) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+// Shared-memory loads the compiler may reorder among themselves and around the MMAs (not volatile), but not hoist above
+// the wait whose result is `token`: the token is an input, and it differs from item to item, so a load of one item is
+// never taken for the same address's load of another.
+__device__ __forceinline__ uint2 lds64_after(uint32_t addr, uint32_t token) {
     uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    asm("ld.shared.v2.u32 {%0,%1}, [%2]; // %3" : "=r"(v.x), "=r"(v.y) : "r"(addr), "r"(token));
     return v;
 }
-__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+__device__ __forceinline__ uint4 lds128_after(uint32_t addr, uint32_t token) {
+    uint4 v;
+    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4]; // %5" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "r"(token));
+    return v;
+}
+__device__ __forceinline__ float2 lds64f_after(uint32_t addr, uint32_t token) {
     float2 v;
-    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    asm("ld.shared.v2.f32 {%0,%1}, [%2]; // %3" : "=f"(v.x), "=f"(v.y) : "r"(addr), "r"(token));
     return v;
 }
 
-__device__ __forceinline__ void qi_consumer_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-__device__ __forceinline__ bool qi_consumer_barrier_or(bool pred) {
+// Barrier over the consumer warps; the value it returns (zero) is a token for loads that must stay behind it.
+__device__ __forceinline__ uint32_t qi_consumer_barrier(int threads) {
+    uint32_t t;
+    asm volatile("bar.sync 1, %1;\n\tmov.u32 %0, 0;" : "=r"(t) : "r"(threads) : "memory");
+    return t;
+}
+__device__ __forceinline__ bool qi_consumer_barrier_or(int threads, bool pred) {
     uint32_t r;
     asm volatile(
-        "{\n.reg .pred p, q;\nsetp.ne.u32 p, %1, 0;\nbar.red.or.pred q, 1, 256, p;\nselp.u32 %0, 1, 0, q;\n}\n"
+        "{\n.reg .pred p, q;\nsetp.ne.u32 p, %1, 0;\nbar.red.or.pred q, 1, %2, p;\nselp.u32 %0, 1, 0, q;\n}\n"
         : "=r"(r)
-        : "r"((uint32_t)pred)
+        : "r"((uint32_t)pred), "r"(threads)
         : "memory");
     return r != 0;
 }
 
 template <int FMT, int MS>  // kFmtAffine4 or kFmtAffine8; MS sets of four activation rows (1 or 2)
-__global__ void __launch_bounds__(kQiThreads, 1) qmv_imma_kernel(const QiParams p) {
+__global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kernel(const QiParams p) {
     constexpr bool W8 = FMT == kFmtAffine8;
     constexpr int GB = W8 ? 64 : 32;  // code bytes per group of 64 inputs
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* xq = smem;                                            // [groups][MS][32 lanes] uint4: B fragments
     float2* xsc = reinterpret_cast<float2*>(smem + p.xq_bytes);          // [groups][MS * 4 rows] {2^(e-13), sum x}
-    float* red = reinterpret_cast<float*>(smem + p.xq_bytes + p.xsc_bytes);  // [2][8 warps][MS][32 lanes][2]
-    unsigned char* stages = smem + p.xq_bytes + p.xsc_bytes + 4096 * MS;
+    float* red = reinterpret_cast<float*>(smem + p.xq_bytes + p.xsc_bytes);  // [2][consumer warps][MS][32 lanes][2]
+    unsigned char* stages = smem + p.xq_bytes + p.xsc_bytes + p.red_bytes;
+    const int ncw = p.ncw, nct = 32 * p.ncw;  // consumer warps and threads
     uint64_t* bars = reinterpret_cast<uint64_t*>(stages + (size_t)p.nstages * p.stage_bytes);
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * p.nstages;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * p.nstages);
@@ -100,7 +116,7 @@ __global__ void __launch_bounds__(kQiThreads, 1) qmv_imma_kernel(const QiParams 
     if (tid == 0) {
         for (int s = 0; s < p.nstages; s++) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 8);
+            mbar_init(bar_empty + 8 * s, ncw);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -114,9 +130,9 @@ __global__ void __launch_bounds__(kQiThreads, 1) qmv_imma_kernel(const QiParams 
     const int items = (hi - lo + kQiRows - 1) / kQiRows;
     const int G = p.K / 64;
     const int codes_bytes = kQiRows * p.row_pitch;
-    const int sc_bytes = kQiRows * p.srow_bytes;
+    const int sc_bytes = kQiRows * p.srow_pitch;
 
-    if (warp == 8) {
+    if (warp == ncw) {
         // ================= producer: weights do not depend on the previous kernel, so it starts at once =========
         bool ok = true;
         for (int it = 0; it < items && ok; it++) {
@@ -130,7 +146,7 @@ __global__ void __launch_bounds__(kQiThreads, 1) qmv_imma_kernel(const QiParams 
             if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, rows * (p.row_bytes + 2 * p.srow_bytes));
             __syncwarp();
             const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
-            if (lane < rows) {
+            if (lane < rows) {  // lanes 0-15: the codes of one row each
                 const unsigned char* src = p.w + (size_t)(r0 + lane) * p.row_bytes;
                 for (int off = 0; off < p.row_bytes; off += kQiPiece)
                     bulk_g2s(st + lane * p.row_pitch + off, src + off, min(kQiPiece, p.row_bytes - off), bar_full + 8 * s);
@@ -148,55 +164,64 @@ __global__ void __launch_bounds__(kQiThreads, 1) qmv_imma_kernel(const QiParams 
         // ================= consumers =================
         pdl_wait();  // the activations (and y) belong to the previous kernel until here
         // ---- activations -> block fixed point, two 7-bit digits, in B-fragment order --------------------------------
-        for (int u = tid; u < G * 4 * MS; u += 256) {
-            const int j = u / (4 * MS), m = u % (4 * MS);
-            float v[64];
+        // One thread per eight consecutive inputs (the span of one 32-bit word of 4-bit codes); the eight threads of a
+        // group find its largest magnitude and its sum with a fixed shuffle tree, so a row's digits and sums do not
+        // depend on the other rows.
+        // rows the call does not have: zero digits, zero scale
+        for (int u = tid; u < G * 8 * (4 * MS - p.M); u += nct) {
+            const int m = p.M + u / (G * 8), j = (u >> 3) % G, w8 = u & 7;
+            const int fb = ((j * MS + (m >> 2)) * 32 + 8 * (m & 3)) * 16 + (w8 & 1) * 8 + (w8 >> 1) * 16;
+            *reinterpret_cast<uint2*>(xq + fb) = make_uint2(0, 0);
+            *reinterpret_cast<uint2*>(xq + fb + 64) = make_uint2(0, 0);
+            if (w8 == 0) xsc[j * 4 * MS + m] = make_float2(0.f, 0.f);
+        }
+        for (int u = tid; u < G * 8 * p.M; u += nct) {
+            const int m = u / (G * 8), j = (u >> 3) % G, w8 = u & 7;
+            float v[8];
+            load_x8(p.x, p.x_dtype, (size_t)m * p.ldx + j * 64 + w8 * 8, v);
             float amax = 0.f, sum = 0.f;
-            if (m < p.M) {
 #pragma unroll
-                for (int c = 0; c < 8; c++) load_x8(p.x, p.x_dtype, (size_t)m * p.ldx + j * 64 + c * 8, *reinterpret_cast<float (*)[8]>(&v[c * 8]));
+            for (int k = 0; k < 8; k++) {
+                amax = fmaxf(amax, fabsf(v[k]));
+                sum += v[k];
+            }
 #pragma unroll
-                for (int k = 0; k < 64; k++) {
-                    amax = fmaxf(amax, fabsf(v[k]));
-                    sum += v[k];
-                }
-            } else {
-#pragma unroll
-                for (int k = 0; k < 64; k++) v[k] = 0.f;
+            for (int o = 1; o < 8; o <<= 1) {
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                sum += __shfl_xor_sync(0xffffffffu, sum, o);
             }
             float scale = 0.f, inv = 0.f;
             if (amax > 0.f && amax < 3.0e38f) {
-                int e;
-                frexpf(amax, &e);               // amax = f * 2^e, 0.5 <= f < 1
-                e = max(e, -100);
-                scale = ldexpf(1.f, e - 13);
-                inv = ldexpf(1.f, 13 - e);
+                // 2^e > amax >= 2^(e-1): e from the exponent field (subnormal groups are treated as zero)
+                const int e = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 126;
+                if (e > -100) {
+                    scale = __uint_as_float((uint32_t)(e - 13 + 127) << 23);
+                    inv = __uint_as_float((uint32_t)(13 - e + 127) << 23);
+                }
             }
-            xsc[j * 4 * MS + m] = make_float2(scale, sum);
-            const int fb = ((j * MS + (m >> 2)) * 32 + 8 * (m & 3)) * 16;  // the row's hi-digit column, lane t = 0
+            if (w8 == 0) xsc[j * 4 * MS + m] = make_float2(scale, sum);
+            uint32_t hi_w[2] = {0, 0}, lo_w[2] = {0, 0};  // [b0 / b1 half] bytes i = 0..3
 #pragma unroll
-            for (int k = 0; k < 64; k++) {
+            for (int k = 0; k < 8; k++) {
                 const int X = __float2int_rn(v[k] * inv);       // |X| <= 8192
                 const int hi_d = (X + 64) >> 7, lo_d = X - (hi_d << 7);
-                // where input k of the group sits in the fragments: lane t of the four that share a column, MMA mm of
-                // the group's two, register half (b0 / b1), byte i
-                int t, mm, half, i;
-                if (W8) {
-                    const int word = k >> 2;
-                    t = word >> 2; mm = (word >> 1) & 1; half = word & 1; i = k & 3;
-                } else {
-                    const int word = k >> 3, r = k & 7;
-                    t = word >> 1; mm = word & 1; half = r & 1; i = r >> 1;
-                }
-                const int off = mm * 8 + half * 4 + i;
-                xq[fb + t * 16 + off] = (unsigned char)(hi_d & 0xFF);
-                xq[fb + (4 + t) * 16 + off] = (unsigned char)(lo_d & 0xFF);
+                // input k of the span: 4-bit codes put even k in the low nibbles (b0) and odd k in the high ones (b1);
+                // 8-bit codes put k 0-3 in one word (b0) and k 4-7 in the next (b1)
+                const int half = W8 ? (k >> 2) : (k & 1), i = W8 ? (k & 3) : (k >> 1);
+                hi_w[half] |= (uint32_t)(hi_d & 0xFF) << (8 * i);
+                lo_w[half] |= (uint32_t)(lo_d & 0xFF) << (8 * i);
             }
+            // the span is word w8 of the group's eight (4-bit: lane t = w8 / 2, MMA w8 % 2) or words 2 w8, 2 w8 + 1 of
+            // its sixteen (8-bit: lane t = w8 / 2, MMA w8 % 2): the same slot either way
+            const int t = w8 >> 1, mm = w8 & 1;
+            const int fb = ((j * MS + (m >> 2)) * 32 + 8 * (m & 3)) * 16 + mm * 8;  // the row's hi-digit column, lane 0
+            *reinterpret_cast<uint2*>(xq + fb + t * 16) = make_uint2(hi_w[0], hi_w[1]);
+            *reinterpret_cast<uint2*>(xq + fb + (4 + t) * 16) = make_uint2(lo_w[0], lo_w[1]);
         }
-        qi_consumer_barrier();
+        const uint32_t xtok = qi_consumer_barrier(nct);
 
         const int g = lane >> 2, t = lane & 3;
-        const int gw = G / 8;                       // groups per warp (a multiple of 4)
+        const int gw = G / ncw;                     // groups per warp (a multiple of 4)
         const int g0 = warp * gw;
         const uint32_t xq32 = smem_u32(xq) + lane * 16, xsc32 = smem_u32(xsc) + t * 8;
         for (int it = 0; it < items; it++) {
@@ -205,28 +230,30 @@ __global__ void __launch_bounds__(kQiThreads, 1) qmv_imma_kernel(const QiParams 
             const int r0 = lo + it * kQiRows;
             const int rows = min(kQiRows, hi - r0);
             const bool ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+            const uint32_t tok = (uint32_t)it + (ok ? 0u : 0x80000000u);  // orders the stage's loads after the wait
             float acc0[MS], acc1[MS];  // rows g and g + 8 of the block, activation rows t, 4 + t
 #pragma unroll
             for (int c = 0; c < MS; c++) acc0[c] = acc1[c] = 0.f;
             if (ok) {
                 const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
                 const uint32_t wa0 = st + g * p.row_pitch + t * (W8 ? 16 : 8), wa1 = wa0 + 8 * p.row_pitch;
-                const uint32_t sa0 = st + codes_bytes + g * p.srow_bytes, sa1 = sa0 + 8 * p.srow_bytes;
+                const uint32_t sa0 = st + codes_bytes + g * p.srow_pitch, sa1 = sa0 + 8 * p.srow_pitch;
                 for (int c4 = 0; c4 < gw; c4 += 4) {
                     // scales and biases of four groups for both rows (bf16 pairs)
-                    const uint2 s0 = lds64(sa0 + (g0 + c4) * 2), s1 = lds64(sa1 + (g0 + c4) * 2);
-                    const uint2 b0 = lds64(sa0 + sc_bytes + (g0 + c4) * 2), b1 = lds64(sa1 + sc_bytes + (g0 + c4) * 2);
+                    const uint2 s0 = lds64_after(sa0 + (g0 + c4) * 2, tok), s1 = lds64_after(sa1 + (g0 + c4) * 2, tok);
+                    const uint2 b0 = lds64_after(sa0 + sc_bytes + (g0 + c4) * 2, tok);
+                    const uint2 b1 = lds64_after(sa1 + sc_bytes + (g0 + c4) * 2, tok);
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         const int grp = g0 + c4 + q;
                         const int z[4] = {0, 0, 0, 0};
                         uint32_t a[2][4];  // the A fragments of the group's two MMAs
                         if (W8) {
-                            const uint4 w0 = lds128(wa0 + grp * GB), w1 = lds128(wa1 + grp * GB);
+                            const uint4 w0 = lds128_after(wa0 + grp * GB, tok), w1 = lds128_after(wa1 + grp * GB, tok);
                             a[0][0] = w0.x; a[0][1] = w1.x; a[0][2] = w0.y; a[0][3] = w1.y;
                             a[1][0] = w0.z; a[1][1] = w1.z; a[1][2] = w0.w; a[1][3] = w1.w;
                         } else {
-                            const uint2 w0 = lds64(wa0 + grp * GB), w1 = lds64(wa1 + grp * GB);
+                            const uint2 w0 = lds64_after(wa0 + grp * GB, tok), w1 = lds64_after(wa1 + grp * GB, tok);
                             constexpr uint32_t MSK = 0x0F0F0F0Fu;
                             a[0][0] = w0.x & MSK; a[0][1] = w1.x & MSK; a[0][2] = (w0.x >> 4) & MSK; a[0][3] = (w1.x >> 4) & MSK;
                             a[1][0] = w0.y & MSK; a[1][1] = w1.y & MSK; a[1][2] = (w0.y >> 4) & MSK; a[1][3] = (w1.y >> 4) & MSK;
@@ -240,10 +267,10 @@ __global__ void __launch_bounds__(kQiThreads, 1) qmv_imma_kernel(const QiParams 
 #pragma unroll
                         for (int c = 0; c < MS; c++) {
                             int d[4];
-                            const uint4 xb = lds128(xq32 + (grp * MS + c) * 512);
+                            const uint4 xb = lds128_after(xq32 + (grp * MS + c) * 512, xtok);
                             imma16832_u8s8(d, a[0][0], a[0][1], a[0][2], a[0][3], xb.x, xb.y, z);
                             imma16832_u8s8(d, a[1][0], a[1][1], a[1][2], a[1][3], xb.z, xb.w, d);
-                            const float2 xs = lds64f(xsc32 + (grp * MS + c) * 32);  // {2^(e-13), sum x} of row 4c + t
+                            const float2 xs = lds64f_after(xsc32 + (grp * MS + c) * 32, xtok);  // {2^(e-13), sum x} of row 4c + t
                             const float v0 = (float)(d[0] * 128 + d[1]), v1 = (float)(d[2] * 128 + d[3]);
                             acc0[c] = fmaf(v0, sc0 * xs.x, acc0[c]);
                             acc0[c] = fmaf(bi0, xs.y, acc0[c]);
@@ -257,23 +284,22 @@ __global__ void __launch_bounds__(kQiThreads, 1) qmv_imma_kernel(const QiParams 
             if (lane == 0 && ok) mbar_arrive(bar_empty + 8 * s);  // the stage is free once every warp has read its part
 
             // ---- the eight K slices meet in shared memory; warp 0 adds them in slice order and stores -----------------
-            float* mine = red + ((it & 1) * 8 + warp) * (64 * MS);
+            float* mine = red + ((it & 1) * ncw + warp) * (64 * MS);
 #pragma unroll
             for (int c = 0; c < MS; c++) {
                 mine[c * 64 + lane * 2] = acc0[c];
                 mine[c * 64 + lane * 2 + 1] = acc1[c];
             }
-            if (qi_consumer_barrier_or(!ok)) break;  // a wait gave up somewhere: everybody leaves together
+            if (qi_consumer_barrier_or(nct, !ok)) break;  // a wait gave up somewhere: everybody leaves together
             if (warp != 0) continue;
 #pragma unroll
             for (int c = 0; c < MS; c++) {
                 const int m = 4 * c + t;
                 if (m >= p.M) continue;
                 float y0 = 0.f, y1 = 0.f;
-#pragma unroll
-                for (int k = 0; k < 8; k++) {
-                    y0 += red[((it & 1) * 8 + k) * (64 * MS) + c * 64 + lane * 2];
-                    y1 += red[((it & 1) * 8 + k) * (64 * MS) + c * 64 + lane * 2 + 1];
+                for (int k = 0; k < ncw; k++) {
+                    y0 += red[((it & 1) * ncw + k) * (64 * MS) + c * 64 + lane * 2];
+                    y1 += red[((it & 1) * ncw + k) * (64 * MS) + c * 64 + lane * 2 + 1];
                 }
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
