@@ -222,7 +222,7 @@ def bench_qmv(torch, dev, peaks):
             "bytes_per_call": nbytes, "gbs": round(gbs, 1),
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(gbs / peaks["hbm_gbs"], 4), "frac_of_8TBs_nominal": round(gbs / 8000.0, 4),
-                         "traffic": 33075968, "peak_source": peaks["source"]},
+                         "traffic": 33064192, "peak_source": peaks["source"]},  # ncu dram__bytes_read + write of one launch
             "l2": "8 weight copies in rotation (264 MB > 126 MB L2)", "timing": "CUDA graph of 64 calls, CUDA events"}
 
 
@@ -349,7 +349,8 @@ def run_ours(args):
         tf = flops / (ms_gu * 1e-3) / 1e12
         roof = {"kernel": "experts gate+up+SwiGLU (grouped)", "bound": "tensor", "achieved": round(tf, 2),
                 "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": round(tf / peaks["bf16_tflops_sustained"], 4),
-                "traffic": None, "ms_per_launch": round(ms_gu, 4), "flops_per_launch": flops,
+                "traffic": 405289472 if (t_n == PREFILL_TOKENS and args.layers > 0) else None,  # ncu DRAM read + write per launch
+                "ms_per_launch": round(ms_gu, 4), "flops_per_launch": flops,
                 "peak_source": peaks["source"] + " (sustained: the kernel runs inside a long step)"}
 
     line = None
