@@ -181,7 +181,9 @@ typedef struct iq_moe_views {
     uint32_t* row_map;  /* [T*top_k] sorted position -> pair id (pair = token*top_k + rank) */
     uint32_t* pos;      /* [T*top_k] pair id -> sorted position */
     void* h;            /* fp16 [T*top_k, d_ff] activations at sorted positions */
-    float* yd;          /* fp32 [T*top_k, d_model] expert outputs at sorted positions */
+    void* yd;           /* [T*top_k, d_model] expert outputs at sorted positions: fp16 for affine experts, fp32 for
+                           MXFP4 ones, whose outputs can pass half's range (the reference's choice, MoEPrefill.swift:159) */
+    int32_t yd_dtype;   /* IQ_F16 or IQ_F32 */
 } iq_moe_views;
 
 int32_t iq_moe_create(iq_ctx* ctx, const iq_moe_desc* desc, iq_moe** out);

@@ -44,7 +44,7 @@ class MoeDesc(C.Structure):
 class MoeViews(C.Structure):
     _fields_ = [("logits", C.c_void_p), ("ld", C.c_int32), ("inds", C.c_void_p), ("wts", C.c_void_p),
                 ("offsets", C.c_void_p), ("row_map", C.c_void_p), ("pos", C.c_void_p), ("h", C.c_void_p),
-                ("yd", C.c_void_p)]
+                ("yd", C.c_void_p), ("yd_dtype", C.c_int32)]
 
 
 class IngotError(RuntimeError):

@@ -26,10 +26,11 @@ struct MoeWs {
     uint32_t* row_map;
     uint32_t* pos;
     uint32_t* ntiles;
+    uint32_t* chunk_hist;
     Tile* tiles_a;
     Tile* tiles_b;
     __half* h;
-    float* yd;
+    void* yd;
     __half* xs;  // activations in expert order, fp16 [P, d_model] (tensor-core path)
     size_t bytes;
 };
@@ -44,7 +45,12 @@ constexpr int kPrefillTileRowsBig = 256;   // ... and once they see many: every 
 constexpr int kTensorPathRowsPerExpert = 24;
 constexpr int kBigTileRowsPerExpert = 96;
 constexpr int kRouterSmemMax = 200 * 1024;
+constexpr int kGroupChunkedMinPairs = 4096;  // from here on the permutation runs as a chunked counting sort
 constexpr int kRouterTiledMinTokens = 64;  // above this the router runs as a tiled float64 GEMM
+
+// Expert outputs between the down projection and the combine: fp16 for affine experts, fp32 for MXFP4 ones, whose
+// outputs can pass half's range (the reference makes the same choice, MoEPrefill.swift:159-160).
+int32_t yd_dtype_of(const iq_moe* l) { return l->fmt == kFmtMxfp4 ? kF32 : kF16; }
 
 MoeWs carve(const iq_moe* l, void* base, int tokens) {
     const iq_moe_desc& d = l->d;
@@ -64,10 +70,11 @@ MoeWs carve(const iq_moe* l, void* base, int tokens) {
     w.row_map = static_cast<uint32_t*>(take(P * 4));
     w.pos = static_cast<uint32_t*>(take(P * 4));
     w.ntiles = static_cast<uint32_t*>(take(16));
+    w.chunk_hist = static_cast<uint32_t*>(take((P / kGroupChunk + 1) * (size_t)d.experts * 4));
     w.tiles_a = static_cast<Tile*>(take((d.experts + P / 8 + 1) * sizeof(Tile)));
     w.tiles_b = static_cast<Tile*>(take((d.experts + P / kPrefillTileRows + 1) * sizeof(Tile)));
     w.h = static_cast<__half*>(take(P * d.d_ff * 2));
-    w.yd = static_cast<float*>(take(P * d.d_model * 4));
+    w.yd = take(P * d.d_model * (yd_dtype_of(l) == kF16 ? 2 : 4));
     w.xs = static_cast<__half*>(take(P * d.d_model * 2));
     w.bytes = off;
     return w;
@@ -373,7 +380,7 @@ extern "C" int32_t iq_moe_get_views(const iq_moe* l, void* workspace, int32_t to
     v->inds = l->ext_inds ? const_cast<uint32_t*>(l->ext_inds) : w.inds;
     v->wts = l->ext_wts ? const_cast<float*>(l->ext_wts) : w.wts;
     v->offsets = w.offsets; v->row_map = w.row_map; v->pos = w.pos;
-    v->h = w.h; v->yd = w.yd;
+    v->h = w.h; v->yd = w.yd; v->yd_dtype = yd_dtype_of(l);
     return kOk;
 }
 
@@ -474,8 +481,17 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
         gp.tiles_a = w.tiles_a; gp.tiles_b = w.tiles_b; gp.ntiles = w.ntiles;
         gp.P = P; gp.E = d.experts; gp.bm_a = bm; gp.bm_b = tensor_tile_rows(P, d.expert_count);
         gp.e_lo = d.expert_lo; gp.e_hi = d.expert_lo + d.expert_count;
-        moe_count_kernel<<<d.experts, 256, 0, cs>>>(gp);
-        moe_scatter_kernel<<<d.experts, 256, 0, cs>>>(gp);
+        gp.chunk_hist = w.chunk_hist;
+        gp.chunks = (P + kGroupChunk - 1) / kGroupChunk;
+        if (P >= kGroupChunkedMinPairs && d.experts * 8 * 4 <= 48 * 1024) {
+            // many pairs: a chunked counting sort touches each pair once per kernel instead of once per expert
+            moe_hist_kernel<<<gp.chunks, 256, d.experts * 4, cs>>>(gp);
+            moe_scan_kernel<<<1, 256, 0, cs>>>(gp);
+            moe_place_kernel<<<gp.chunks, 256, d.experts * 8 * 4, cs>>>(gp);
+        } else {
+            moe_count_kernel<<<d.experts, 256, 0, cs>>>(gp);
+            moe_scatter_kernel<<<d.experts, 256, 0, cs>>>(gp);
+        }
         st = check_cuda(ctx, cudaGetLastError(), "moe_group launch");
         if (st != kOk) return st;
     }
@@ -495,13 +511,13 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
         if (st != kOk) return st;
     }
     if (pieces & IQ_PIECE_DOWN) {
-        st = tc ? run_down_tc(l, cs, w.h, P, w.tiles_b, w.ntiles + 1, w.yd, kF32, tensor_tile_rows(P, d.expert_count))
-                : run_down(l, cs, w.h, w.tiles_a, w.ntiles, max_tiles, bm, w.yd, kF32);
+        st = tc ? run_down_tc(l, cs, w.h, P, w.tiles_b, w.ntiles + 1, w.yd, yd_dtype_of(l), tensor_tile_rows(P, d.expert_count))
+                : run_down(l, cs, w.h, w.tiles_a, w.ntiles, max_tiles, bm, w.yd, yd_dtype_of(l));
         if (st != kOk) return st;
     }
     if (pieces & IQ_PIECE_COMBINE) {
         CombineParams cp;
-        cp.yd = w.yd; cp.yd_dtype = kF32; cp.pos = w.pos; cp.wts = wts;
+        cp.yd = w.yd; cp.yd_dtype = yd_dtype_of(l); cp.pos = w.pos; cp.wts = wts;
         cp.out = out; cp.out_dtype = out_dtype; cp.ldo = ldo;
         cp.T = tokens; cp.D = d.d_model; cp.topk = d.top_k;
         cp.accumulate = (flags & IQ_FLAG_ACCUMULATE) ? 1 : 0;

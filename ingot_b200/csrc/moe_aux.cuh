@@ -369,6 +369,8 @@ struct GroupParams {
     uint32_t* ntiles;       // [2]
     int32_t P, E, bm_a, bm_b;
     int32_t e_lo, e_hi;     // experts owned here (expert parallel); tiles are emitted only for these
+    uint32_t* chunk_hist;   // [chunks, E] scratch of the chunked form (many pairs)
+    int32_t chunks;
 };
 
 __global__ void __launch_bounds__(256) moe_count_kernel(const GroupParams p) {
@@ -455,6 +457,108 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const GroupParams p) {
             p.pos[i] = r;
         }
         placed += total;
+    }
+}
+
+// The same grouping for many pairs, as a stable counting sort over chunks of kGroupChunk pairs: every kernel touches
+// each pair once instead of once per expert. (1) per-chunk histograms; (2) one block turns them into per-chunk bases,
+// expert offsets and the tile lists; (3) every chunk places its pairs: position = expert offset + pairs of that expert
+// in earlier chunks + in earlier warps of the chunk + earlier in the warp's walk. Nothing depends on timing.
+constexpr int kGroupChunk = 1024;
+
+__global__ void __launch_bounds__(256) moe_hist_kernel(const GroupParams p) {
+    extern __shared__ uint32_t hist[];
+    for (int e = threadIdx.x; e < p.E; e += 256) hist[e] = 0;
+    __syncthreads();
+    const int i0 = blockIdx.x * kGroupChunk, i1 = min(p.P, i0 + kGroupChunk);
+    for (int i = i0 + threadIdx.x; i < i1; i += 256) atomicAdd(&hist[p.inds[i]], 1u);
+    __syncthreads();
+    for (int e = threadIdx.x; e < p.E; e += 256) p.chunk_hist[(size_t)blockIdx.x * p.E + e] = hist[e];
+}
+
+__global__ void __launch_bounds__(256) moe_scan_kernel(const GroupParams p) {
+    __shared__ uint32_t sc[256], sa[256], sb[256];
+    const int tid = threadIdx.x;
+    // experts handled by this thread: a contiguous run, so that a block-wide scan over threads orders the experts
+    const int per = (p.E + 255) / 256;
+    const int e0 = tid * per, e1 = min(p.E, e0 + per);
+    uint32_t c_sum = 0, a_sum = 0, b_sum = 0;
+    for (int e = e0; e < e1; e++) {
+        uint32_t run = 0;
+        for (int c = 0; c < p.chunks; c++) {  // histogram -> exclusive prefix over the chunks
+            const uint32_t t = p.chunk_hist[(size_t)c * p.E + e];
+            p.chunk_hist[(size_t)c * p.E + e] = run;
+            run += t;
+        }
+        p.counts[e] = run;
+        c_sum += run;
+        if (e >= p.e_lo && e < p.e_hi) {
+            a_sum += (run + p.bm_a - 1) / p.bm_a;
+            b_sum += (run + p.bm_b - 1) / p.bm_b;
+        }
+    }
+    sc[tid] = c_sum; sa[tid] = a_sum; sb[tid] = b_sum;
+    __syncthreads();
+    uint32_t off = 0, ta = 0, tb = 0;
+    for (int i = 0; i < tid; i++) { off += sc[i]; ta += sa[i]; tb += sb[i]; }
+    for (int e = e0; e < e1; e++) {
+        const uint32_t cnt = p.counts[e];
+        p.offsets[e] = off;
+        if (e >= p.e_lo && e < p.e_hi) {
+            for (uint32_t j = 0; j * p.bm_a < cnt; j++)
+                p.tiles_a[ta++] = Tile{(uint32_t)e, off + j * p.bm_a, min((uint32_t)p.bm_a, cnt - j * p.bm_a), 0};
+            for (uint32_t j = 0; j * p.bm_b < cnt; j++)
+                p.tiles_b[tb++] = Tile{(uint32_t)e, off + j * p.bm_b, min((uint32_t)p.bm_b, cnt - j * p.bm_b), 0};
+        }
+        off += cnt;
+    }
+    if (tid == 255) {
+        p.offsets[p.E] = off;
+        p.ntiles[0] = ta;
+        p.ntiles[1] = tb;
+    }
+}
+
+__global__ void __launch_bounds__(256) moe_place_kernel(const GroupParams p) {
+    extern __shared__ uint32_t sm[];  // [8 warps][E] pairs of each expert in each warp's share, then running counts
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < 8 * p.E; i += 256) sm[i] = 0;
+    __syncthreads();
+    // warp w walks pairs [i0 + 128 w, i0 + 128 w + 128) of the chunk, 32 at a time
+    const int i0 = blockIdx.x * kGroupChunk + warp * (kGroupChunk / 8);
+    uint32_t* mine = sm + warp * p.E;
+    uint32_t ev[4];
+#pragma unroll
+    for (int st = 0; st < 4; st++) {
+        const int i = i0 + st * 32 + lane;
+        ev[st] = i < p.P ? p.inds[i] : 0xFFFFFFFFu;
+        const uint32_t same = __match_any_sync(0xffffffffu, ev[st]);
+        if (ev[st] != 0xFFFFFFFFu && lane == __ffs(same) - 1) mine[ev[st]] += __popc(same);
+        __syncwarp();
+    }
+    __syncthreads();
+    // per expert: exclusive prefix over the warps, on top of the expert's offset and its pairs in earlier chunks
+    for (int e = tid; e < p.E; e += 256) {
+        uint32_t run = p.offsets[e] + p.chunk_hist[(size_t)blockIdx.x * p.E + e];
+        for (int w = 0; w < 8; w++) {
+            const uint32_t t = sm[w * p.E + e];
+            sm[w * p.E + e] = run;
+            run += t;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int st = 0; st < 4; st++) {
+        const int i = i0 + st * 32 + lane;
+        const uint32_t same = __match_any_sync(0xffffffffu, ev[st]);
+        if (ev[st] != 0xFFFFFFFFu) {
+            const uint32_t r = mine[ev[st]] + __popc(same & ((1u << lane) - 1u));
+            p.row_map[r] = (uint32_t)i;
+            p.pos[i] = r;
+        }
+        __syncwarp();
+        if (ev[st] != 0xFFFFFFFFu && lane == __ffs(same) - 1) mine[ev[st]] += __popc(same);
+        __syncwarp();
     }
 }
 

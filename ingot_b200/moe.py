@@ -146,7 +146,7 @@ class MoELayer:
             "row_map": view(v.row_map, torch.int32, (rows * k,)),
             "pos": view(v.pos, torch.int32, (rows * k,)),
             "h": view(v.h, torch.float16, (rows * k, self.I)),
-            "yd": view(v.yd, torch.float32, (rows * k, self.D)),
+            "yd": view(v.yd, torch.float16 if v.yd_dtype == capi.IQ_F16 else torch.float32, (rows * k, self.D)),
         }
 
     # ---- expert-parallel pieces (no counterpart in the single-GPU reference) ---------------------------------------
