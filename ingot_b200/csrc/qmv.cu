@@ -216,9 +216,15 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
+        // up to four rows and eight groups per warp (K = 4096): the activation fragments stay in registers
+        const bool hoist = ms == 1 && G / ncw == 8;
         cudaError_t e;
-        if (w8) e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 2>, p) : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 1>, p);
-        else e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 2>, p) : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 1>, p);
+        if (w8) e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 2, 0>, p)
+                            : (hoist ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 1, 8>, p)
+                                     : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 1, 0>, p));
+        else e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 2, 0>, p)
+                         : (hoist ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 1, 8>, p)
+                                  : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 1, 0>, p));
         const int32_t r = check_cuda(ctx, e, "qmv_imma launch");
         if (r != kOk) return r;
     }
@@ -228,11 +234,13 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
 }  // namespace
 
 int32_t gqmv_init(iq_ctx* ctx) {
-    const void* qi[4] = {reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 1>),
-                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 2>),
-                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 1>),
-                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 2>)};
-    for (int i = 0; i < 4; i++) {
+    const void* qi[6] = {reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 1, 0>),
+                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 1, 8>),
+                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 2, 0>),
+                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 1, 0>),
+                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 1, 8>),
+                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 2, 0>)};
+    for (int i = 0; i < 6; i++) {
         cudaError_t e = cudaFuncSetAttribute(qi[i], cudaFuncAttributeMaxDynamicSharedMemorySize, kQsSmemMax);
         if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_imma)");
     }

@@ -14,8 +14,8 @@
 // and the group's contribution is s * that + b * sum_k x, with sum_k x kept in fp32. That is two MMAs, two integer
 // and six float instructions per 64 x 16 weights, against several hundred in the fp16 formulation.
 //
-// Structure: one persistent CTA per SM owns a contiguous range of weight rows (any length: the bytes are what has to
-// balance) and walks it 16 rows at a time. Warp 8 streams each 16-row block through a ring of bulk copies (one per
+// Structure: persistent CTAs (two per SM up to four rows) each own a contiguous range of 16-row blocks and walk it block
+// by block. Warp 8 streams each 16-row block through a ring of bulk copies (one per
 // row, into rows padded so that the fragment loads are free of bank conflicts, plus scales and biases); the 8 or 16
 // consumer warps take one slice of K each, and their partial sums meet in shared memory in a fixed order. Every wait is bounded.
 //
@@ -29,7 +29,7 @@
 
 namespace iq {
 
-constexpr int kQiMaxThreads = 544;  // up to 16 consumer warps + 1 producer warp
+constexpr int kQiMaxThreads = 288;  // 8 consumer warps + 1 producer warp
 constexpr int kQiRows = 16;         // weight rows per stage (MMA M)
 constexpr int kQiPiece = 8192;      // bytes per bulk copy
 
@@ -98,7 +98,10 @@ __device__ __forceinline__ bool qi_consumer_barrier_or(int threads, bool pred) {
     return r != 0;
 }
 
-template <int FMT, int MS>  // kFmtAffine4 or kFmtAffine8; MS sets of four activation rows (1 or 2)
+// FMT: kFmtAffine4 or kFmtAffine8; MS: sets of four activation rows (1 or 2); GW: groups of 64 inputs per consumer warp
+// when known at compile time (the activation fragments of the warp's K slice then live in registers across all row
+// blocks), 0 when not.
+template <int FMT, int MS, int GW>
 __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kernel(const QiParams p) {
     constexpr bool W8 = FMT == kFmtAffine8;
     constexpr int GB = W8 ? 64 : 32;  // code bytes per group of 64 inputs
@@ -125,8 +128,12 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
     __syncthreads();
     pdl_launch_dependents();
 
-    // this CTA's rows: a contiguous range, cut 16 rows at a time
-    const int lo = (int)((int64_t)p.N * blockIdx.x / gridDim.x), hi = (int)((int64_t)p.N * (blockIdx.x + 1) / gridDim.x);
+    // This CTA's rows: a contiguous range of whole 16-row blocks (the last block of the matrix may be short). Cutting the
+    // range at arbitrary rows would balance the bytes better, but a block with one row costs the instructions of a full
+    // one, and the kernel is bound by instruction issue before it is bound by bytes.
+    const int nblk = (p.N + kQiRows - 1) / kQiRows;
+    const int lo = (int)((int64_t)nblk * blockIdx.x / gridDim.x) * kQiRows;
+    const int hi = min(p.N, (int)((int64_t)nblk * (blockIdx.x + 1) / gridDim.x) * kQiRows);
     const int items = (hi - lo + kQiRows - 1) / kQiRows;
     const int G = p.K / 64;
     const int codes_bytes = kQiRows * p.row_pitch;
@@ -221,9 +228,20 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
         const uint32_t xtok = qi_consumer_barrier(nct);
 
         const int g = lane >> 2, t = lane & 3;
-        const int gw = G / ncw;                     // groups per warp (a multiple of 4)
+        const int gw = GW > 0 ? GW : G / ncw;       // groups per warp (a multiple of 4)
         const int g0 = warp * gw;
         const uint32_t xq32 = smem_u32(xq) + lane * 16, xsc32 = smem_u32(xsc) + t * 8;
+        uint4 xbr[GW > 0 ? GW : 1][MS];
+        float2 xsr[GW > 0 ? GW : 1][MS];
+        if (GW > 0) {
+#pragma unroll
+            for (int q = 0; q < GW; q++)
+#pragma unroll
+                for (int c = 0; c < MS; c++) {
+                    xbr[q][c] = lds128_after(xq32 + ((g0 + q) * MS + c) * 512, xtok);
+                    xsr[q][c] = lds64f_after(xsc32 + ((g0 + q) * MS + c) * 32, xtok);
+                }
+        }
         for (int it = 0; it < items; it++) {
             const int s = it % p.nstages;
             const uint32_t ph = (it / p.nstages) & 1;
@@ -238,7 +256,8 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
                 const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
                 const uint32_t wa0 = st + g * p.row_pitch + t * (W8 ? 16 : 8), wa1 = wa0 + 8 * p.row_pitch;
                 const uint32_t sa0 = st + codes_bytes + g * p.srow_pitch, sa1 = sa0 + 8 * p.srow_pitch;
-                for (int c4 = 0; c4 < gw; c4 += 4) {
+#pragma unroll
+                for (int c4 = 0; c4 < (GW > 0 ? GW : gw); c4 += 4) {
                     // scales and biases of four groups for both rows (bf16 pairs)
                     const uint2 s0 = lds64_after(sa0 + (g0 + c4) * 2, tok), s1 = lds64_after(sa1 + (g0 + c4) * 2, tok);
                     const uint2 b0 = lds64_after(sa0 + sc_bytes + (g0 + c4) * 2, tok);
@@ -267,10 +286,11 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
 #pragma unroll
                         for (int c = 0; c < MS; c++) {
                             int d[4];
-                            const uint4 xb = lds128_after(xq32 + (grp * MS + c) * 512, xtok);
+                            const uint4 xb = GW > 0 ? xbr[GW > 0 ? c4 + q : 0][c] : lds128_after(xq32 + (grp * MS + c) * 512, xtok);
                             imma16832_u8s8(d, a[0][0], a[0][1], a[0][2], a[0][3], xb.x, xb.y, z);
                             imma16832_u8s8(d, a[1][0], a[1][1], a[1][2], a[1][3], xb.z, xb.w, d);
-                            const float2 xs = lds64f_after(xsc32 + (grp * MS + c) * 32, xtok);  // {2^(e-13), sum x} of row 4c + t
+                            // {2^(e-13), sum x} of activation row 4c + t
+                            const float2 xs = GW > 0 ? xsr[GW > 0 ? c4 + q : 0][c] : lds64f_after(xsc32 + (grp * MS + c) * 32, xtok);
                             const float v0 = (float)(d[0] * 128 + d[1]), v1 = (float)(d[2] * 128 + d[3]);
                             acc0[c] = fmaf(v0, sc0 * xs.x, acc0[c]);
                             acc0[c] = fmaf(bi0, xs.y, acc0[c]);
