@@ -76,6 +76,11 @@ __device__ __forceinline__ uint4 lds128_after(uint32_t addr, uint32_t token) {
     asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4]; // %5" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "r"(token));
     return v;
 }
+__device__ __forceinline__ uint32_t lds_u16_after(uint32_t addr, uint32_t token) {
+    uint32_t v;
+    asm("ld.shared.u16 %0, [%1]; // %2" : "=r"(v) : "r"(addr), "r"(token));
+    return v;
+}
 __device__ __forceinline__ float2 lds64f_after(uint32_t addr, uint32_t token) {
     float2 v;
     asm("ld.shared.v2.f32 {%0,%1}, [%2]; // %3" : "=f"(v.x), "=f"(v.y) : "r"(addr), "r"(token));
