@@ -69,11 +69,20 @@ extern "C" int32_t iq_ctx_create(int32_t device, iq_ctx** out) {
         ctx->encode_tiled = fn;
     int32_t st = kOk;
     if (cudaMalloc(&ctx->d_status, 256) != cudaSuccess || cudaMemset(ctx->d_status, 0, 256) != cudaSuccess) st = kErrCuda;
+    // set-up time allocations of the GEMV's tail split: [slots][pieces][2 row sets][64] floats, [slots][blocks] counters
+    const size_t tail_bytes = (size_t)iq::kQmvTailSlots * iq::kQmvTailPieces * 2 * 64 * sizeof(float);
+    const size_t cnt_bytes = (size_t)iq::kQmvTailSlots * iq::kQmvTailBlocks * sizeof(uint32_t);
+    if (st == kOk && (cudaMalloc(&ctx->qmv_tail_scratch, tail_bytes) != cudaSuccess ||
+                      cudaMalloc(&ctx->qmv_tail_counters, cnt_bytes) != cudaSuccess ||
+                      cudaMemset(ctx->qmv_tail_counters, 0, cnt_bytes) != cudaSuccess))
+        st = kErrCuda;
     if (st == kOk) st = gqmv_init(ctx);
     if (st == kOk) st = qmm_init(ctx);
     if (st == kOk) st = moe_init(ctx);
     if (st != kOk) {
         if (ctx->d_status) cudaFree(ctx->d_status);
+        if (ctx->qmv_tail_scratch) cudaFree(ctx->qmv_tail_scratch);
+        if (ctx->qmv_tail_counters) cudaFree(ctx->qmv_tail_counters);
         delete ctx;
         return st;
     }
@@ -84,6 +93,8 @@ extern "C" int32_t iq_ctx_create(int32_t device, iq_ctx** out) {
 extern "C" void iq_ctx_destroy(iq_ctx* ctx) {
     if (ctx == nullptr) return;
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->qmv_tail_scratch) cudaFree(ctx->qmv_tail_scratch);
+    if (ctx->qmv_tail_counters) cudaFree(ctx->qmv_tail_counters);
     delete ctx;
 }
 

@@ -15,10 +15,18 @@ struct iq_ctx {
     // cuTensorMapEncodeTiled, resolved through the runtime so that the library does not link libcuda directly
     void* encode_tiled = nullptr;
     int32_t* d_status = nullptr;  // device status word written by kernels whose bounded waits gave up
+    // scratch of the GEMV's tail split (csrc/qmv_imma.cuh): a ring of kQmvTailSlots slots, one per launch in turn
+    float* qmv_tail_scratch = nullptr;
+    uint32_t* qmv_tail_counters = nullptr;
+    uint32_t qmv_tail_seq = 0;
     char last_error[256] = {0};
 };
 
 namespace iq {
+
+constexpr int kQmvTailSlots = 16;         // launches whose tail scratch may be live at once (different streams)
+constexpr int kQmvTailPieces = 512;       // at most this many (block, K slice) pieces per launch
+constexpr int kQmvTailBlocks = 64;        // ... over at most this many 16-row blocks
 
 int32_t fail(iq_ctx* ctx, int32_t code, const char* fmt, ...);
 int32_t check_cuda(iq_ctx* ctx, cudaError_t e, const char* what);

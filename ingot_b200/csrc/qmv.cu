@@ -189,6 +189,17 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
     p.status = ctx->d_status;
     const int blocks = c.N / kQiRows;
+    // Tail split, decided from the matrix and the GPU alone (not from the row count, so a row sees the same arithmetic
+    // in every call): when the blocks do not divide over two CTAs per SM and few are left over, the left-over blocks
+    // are cut into K slices and dealt out one piece per CTA.
+    const int slots = 2 * ctx->sms;
+    const int per2 = blocks / slots, tail = blocks - per2 * slots;
+    int tail_slices = 0;
+    if (c.N % kQiRows == 0 && per2 >= 1 && tail > 0 && tail * 8 <= slots && tail <= kQmvTailBlocks) {
+        tail_slices = 1;
+        while (tail_slices * 2 * tail <= slots && tail_slices * 2 <= 32 && G % (tail_slices * 2) == 0) tail_slices *= 2;
+        if (tail_slices < 8 || tail * tail_slices > kQmvTailPieces) tail_slices = 0;
+    }
     const size_t xes = c.x_dtype == kF32 ? 4 : 2, yes = c.y_dtype == kF32 ? 4 : 2;
     for (int m0 = 0; m0 < c.rows; m0 += 8) {  // nine to sixteen rows: two launches of up to eight
         const int m = c.rows - m0 < 8 ? c.rows - m0 : 8;
@@ -209,7 +220,17 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
         cfg.gridDim = dim3(blocks < ctx->sms * ctas ? blocks : ctx->sms * ctas, 1, 1);
-        cfg.blockDim = dim3(32 * (ncw + 1), 1, 1);
+        p.tail_blocks = 0;
+        if (tail_slices > 0) {
+            const uint32_t slot = ctx->qmv_tail_seq++ % kQmvTailSlots;
+            p.tail_blocks = tail;
+            p.tail_slices = tail_slices;
+            p.blocks_per_cta = per2 * (2 / ctas);
+            p.tail_scratch = ctx->qmv_tail_scratch + (size_t)slot * kQmvTailPieces * 2 * 64;
+            p.tail_counters = ctx->qmv_tail_counters + (size_t)slot * kQmvTailBlocks;
+            cfg.gridDim = dim3(ctx->sms * ctas, 1, 1);
+        }
+        cfg.blockDim = dim3(32 * (ncw + 2), 1, 1);
         cfg.dynamicSmemBytes = fixed_bytes(ms) + nstages * p.stage_bytes;
         cfg.stream = st;
         cudaLaunchAttribute attr[1];
@@ -300,7 +321,7 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)(items < slots ? items : slots), 1, 1);
-    cfg.blockDim = dim3(kQiMaxThreads, 1, 1);
+    cfg.blockDim = dim3(kQgThreads, 1, 1);
     cfg.dynamicSmemBytes = fixed + nstages * p.stage_bytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];

@@ -29,7 +29,7 @@
 
 namespace iq {
 
-constexpr int kQiMaxThreads = 288;  // 8 consumer warps + 1 producer warp
+constexpr int kQiMaxThreads = 320;  // 8 consumer warps + the producer warp + the tail warp
 constexpr int kQiRows = 16;         // weight rows per stage (MMA M)
 constexpr int kQiPiece = 8192;      // bytes per bulk copy
 
@@ -52,6 +52,11 @@ struct QiParams {
     int32_t stage_bytes, nstages;
     int32_t xq_bytes, xsc_bytes, red_bytes;
     int32_t ncw;          // consumer warps (8 or 16): K slices per block of rows; the producer is warp ncw
+    // Tail split (tail_blocks > 0): every CTA walks blocks_per_cta whole blocks; the tail_blocks blocks left over are cut
+    // into tail_slices K slices each and dealt out one piece per CTA, so that no CTA walks one block more than the rest.
+    int32_t blocks_per_cta, tail_blocks, tail_slices;
+    float* tail_scratch;        // [tail_blocks * tail_slices][MS][64] partial sums of the pieces
+    uint32_t* tail_counters;    // [tail_blocks] pieces done; the CTA that finishes a block's last piece adds them up
     int32_t* status;
 };
 
@@ -137,12 +142,112 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
     // range at arbitrary rows would balance the bytes better, but a block with one row costs the instructions of a full
     // one, and the kernel is bound by instruction issue before it is bound by bytes.
     const int nblk = (p.N + kQiRows - 1) / kQiRows;
-    const int lo = (int)((int64_t)nblk * blockIdx.x / gridDim.x) * kQiRows;
-    const int hi = min(p.N, (int)((int64_t)nblk * (blockIdx.x + 1) / gridDim.x) * kQiRows);
+    int lo, hi;
+    if (p.tail_blocks > 0) {
+        lo = blockIdx.x * p.blocks_per_cta * kQiRows;
+        hi = lo + p.blocks_per_cta * kQiRows;
+    } else {
+        lo = (int)((int64_t)nblk * blockIdx.x / gridDim.x) * kQiRows;
+        hi = min(p.N, (int)((int64_t)nblk * (blockIdx.x + 1) / gridDim.x) * kQiRows);
+    }
     const int items = (hi - lo + kQiRows - 1) / kQiRows;
     const int G = p.K / 64;
     const int codes_bytes = kQiRows * p.row_pitch;
     const int sc_bytes = kQiRows * p.srow_pitch;
+
+    // ---- tail pieces: (left-over block, K slice), one warp per piece, weights straight from global memory. Run by a
+    // warp of its own beside the row blocks, so that the pieces' latencies (global loads, fence, counter) cost them nothing.
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t xq32 = smem_u32(xq) + lane * 16, xsc32 = smem_u32(xsc) + t * 8;
+    auto tail_pieces = [&](uint32_t xtok) {
+        const int gp = G / p.tail_slices;  // groups per piece
+        const int base_rows = (int)gridDim.x * p.blocks_per_cta * kQiRows;
+        for (int pc = blockIdx.x; pc < p.tail_blocks * p.tail_slices; pc += gridDim.x) {
+            const int tb = pc / p.tail_slices, sl = pc % p.tail_slices;
+            const int r0 = base_rows + tb * kQiRows;
+            const unsigned char* w0p = p.w + (size_t)(r0 + g) * p.row_bytes + t * (W8 ? 16 : 8);
+            const unsigned char* w1p = w0p + (size_t)8 * p.row_bytes;
+            const uint16_t* s0p = reinterpret_cast<const uint16_t*>(p.s + (size_t)(r0 + g) * p.srow_bytes);
+            const uint16_t* s1p = reinterpret_cast<const uint16_t*>(p.s + (size_t)(r0 + g + 8) * p.srow_bytes);
+            const uint16_t* b0p = reinterpret_cast<const uint16_t*>(p.b + (size_t)(r0 + g) * p.srow_bytes);
+            const uint16_t* b1p = reinterpret_cast<const uint16_t*>(p.b + (size_t)(r0 + g + 8) * p.srow_bytes);
+            float a0[MS], a1[MS];
+#pragma unroll
+            for (int c = 0; c < MS; c++) a0[c] = a1[c] = 0.f;
+            for (int grp = sl * gp; grp < (sl + 1) * gp; grp++) {
+                const int z[4] = {0, 0, 0, 0};
+                uint32_t a[2][4];
+                if (W8) {
+                    const uint4 w0 = ldg_nc_u4(w0p + grp * GB), w1 = ldg_nc_u4(w1p + grp * GB);
+                    a[0][0] = w0.x; a[0][1] = w1.x; a[0][2] = w0.y; a[0][3] = w1.y;
+                    a[1][0] = w0.z; a[1][1] = w1.z; a[1][2] = w0.w; a[1][3] = w1.w;
+                } else {
+                    const uint2 w0 = *reinterpret_cast<const uint2*>(w0p + grp * GB);
+                    const uint2 w1 = *reinterpret_cast<const uint2*>(w1p + grp * GB);
+                    constexpr uint32_t MSK = 0x0F0F0F0Fu;
+                    a[0][0] = w0.x & MSK; a[0][1] = w1.x & MSK; a[0][2] = (w0.x >> 4) & MSK; a[0][3] = (w1.x >> 4) & MSK;
+                    a[1][0] = w0.y & MSK; a[1][1] = w1.y & MSK; a[1][2] = (w0.y >> 4) & MSK; a[1][3] = (w1.y >> 4) & MSK;
+                }
+                const float sc0 = bf16_bits_to_f32(s0p[grp]), sc1 = bf16_bits_to_f32(s1p[grp]);
+                const float bi0 = bf16_bits_to_f32(b0p[grp]), bi1 = bf16_bits_to_f32(b1p[grp]);
+#pragma unroll
+                for (int c = 0; c < MS; c++) {
+                    int d[4];
+                    const uint4 xb = lds128_after(xq32 + (grp * MS + c) * 512, xtok);
+                    imma16832_u8s8(d, a[0][0], a[0][1], a[0][2], a[0][3], xb.x, xb.y, z);
+                    imma16832_u8s8(d, a[1][0], a[1][1], a[1][2], a[1][3], xb.z, xb.w, d);
+                    const float2 xs = lds64f_after(xsc32 + (grp * MS + c) * 32, xtok);
+                    const float v0 = (float)(d[0] * 128 + d[1]), v1 = (float)(d[2] * 128 + d[3]);
+                    a0[c] = fmaf(v0, sc0 * xs.x, a0[c]);
+                    a0[c] = fmaf(bi0, xs.y, a0[c]);
+                    a1[c] = fmaf(v1, sc1 * xs.x, a1[c]);
+                    a1[c] = fmaf(bi1, xs.y, a1[c]);
+                }
+            }
+            float* part = p.tail_scratch + (size_t)pc * (MS * 64);
+#pragma unroll
+            for (int c = 0; c < MS; c++) {
+                __stcg(part + c * 64 + lane * 2, a0[c]);
+                __stcg(part + c * 64 + lane * 2 + 1, a1[c]);
+            }
+            __threadfence();
+            __syncwarp();
+            uint32_t done = 0;
+            if (lane == 0) done = atomicAdd(p.tail_counters + tb, 1u);
+            done = __shfl_sync(0xffffffffu, done, 0);
+            if (done != (uint32_t)p.tail_slices - 1) continue;
+            // this warp finished the block's last piece: add the slices up in slice order and store
+            __threadfence();
+#pragma unroll
+            for (int c = 0; c < MS; c++) {
+                const int m = 4 * c + t;
+                float y0 = 0.f, y1 = 0.f;
+                for (int k = 0; k < p.tail_slices; k++) {
+                    const float* q = p.tail_scratch + (size_t)(tb * p.tail_slices + k) * (MS * 64) + c * 64 + lane * 2;
+                    y0 += __ldcg(q);
+                    y1 += __ldcg(q + 1);
+                }
+                if (m >= p.M) continue;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const float v = h ? y1 : y0;
+                    const size_t o = (size_t)m * p.ldy + r0 + g + 8 * h;
+                    if (p.y_dtype == kF32) {
+                        float* yp = reinterpret_cast<float*>(p.y) + o;
+                        *yp = p.accumulate ? *yp + v : v;
+                    } else if (p.y_dtype == kF16) {
+                        __half* yp = reinterpret_cast<__half*>(p.y) + o;
+                        *yp = __float2half_rn(p.accumulate ? __half2float(*yp) + v : v);
+                    } else {
+                        uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + o;
+                        *yp = (uint16_t)f32_to_bf16_bits(p.accumulate ? bf16_bits_to_f32(*yp) + v : v);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) atomicExch(p.tail_counters + tb, 0u);  // ready for the slot's next launch
+        }
+    };
 
     if (warp == ncw) {
         // ================= producer: weights do not depend on the previous kernel, so it starts at once =========
@@ -171,6 +276,14 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
         if (!ok) {  // give copies in flight time to land before the CTA's shared memory is released
             const long long t0 = clock64();
             while (clock64() - t0 < 2000000) {}
+        }
+    } else if (warp == ncw + 1) {
+        // ================= tail warp: the left-over blocks' pieces, beside the row blocks =================
+        if (p.tail_blocks > 0) {
+            uint32_t tk;
+            pdl_wait();  // y belongs to the previous kernel until here
+            asm volatile("bar.sync 2, %1;\n\tmov.u32 %0, 0;" : "=r"(tk) : "r"(nct + 32) : "memory");  // xq is ready
+            tail_pieces(tk);
         }
     } else {
         // ================= consumers =================
@@ -231,11 +344,10 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
             *reinterpret_cast<uint2*>(xq + fb + (4 + t) * 16) = make_uint2(lo_w[0], lo_w[1]);
         }
         const uint32_t xtok = qi_consumer_barrier(nct);
+        if (p.tail_blocks > 0) asm volatile("bar.arrive 2, %0;" ::"r"(nct + 32) : "memory");  // the producer may read xq
 
-        const int g = lane >> 2, t = lane & 3;
         const int gw = GW > 0 ? GW : G / ncw;       // groups per warp (a multiple of 4)
         const int g0 = warp * gw;
-        const uint32_t xq32 = smem_u32(xq) + lane * 16, xsc32 = smem_u32(xsc) + t * 8;
         uint4 xbr[GW > 0 ? GW : 1][MS];
         float2 xsr[GW > 0 ? GW : 1][MS];
         if (GW > 0) {

@@ -20,6 +20,8 @@
 
 namespace iq {
 
+constexpr int kQgThreads = 288;  // 8 consumer warps + 1 producer warp
+
 struct QgParams {
     const unsigned char* w[2];
     const unsigned char* s[2];
@@ -48,7 +50,7 @@ struct QgParams {
 
 // MODE: kModeGateUp (two matrices, h = act(gate, up)) or kModeDown; MS: sets of four activation rows per tile (2 or 4)
 template <int MODE, int MS>
-__global__ void __launch_bounds__(kQiMaxThreads, 1) qmv_imma_grouped_kernel(const QgParams p) {
+__global__ void __launch_bounds__(kQgThreads, 1) qmv_imma_grouped_kernel(const QgParams p) {
     constexpr int NW = MODE == kModeGateUp ? 2 : 1;
     constexpr int GB = 32;  // code bytes per group of 64 inputs (4-bit)
     extern __shared__ __align__(16) unsigned char smem[];

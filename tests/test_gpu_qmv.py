@@ -109,6 +109,26 @@ def test_qmv_row_invariance(cuda_device):
         assert torch.equal(alone[0], full[i])
 
 
+@pytest.mark.parametrize("bits", [4, 8])
+def test_qmv_tail_split_parity_and_row_invariance(cuda_device, bits):
+    """A matrix whose 16-row blocks do not divide over the CTAs (304 blocks on 148 SMs x 2: eight left over, cut into K
+    slices): parity with the oracle, the same bits for a row alone, among 4, 7 and 16, and on a second call."""
+    rng = np.random.default_rng(21 + bits)
+    N, K = 4864, 2048
+    m, host = affine_case(rng, N, K, bits, cuda_device)
+    x = synth.activations_np(rng, 16, K)
+    xt = x_tensor(x, cuda_device)
+    full = run(m, xt, 16)
+    assert qref.max_rel(full.cpu().numpy(), qref.matmul_t(x, deq(host, bits))) <= TOL
+    again = run(m, xt, 16)
+    assert torch.equal(full, again)
+    for rows in (1, 4, 7):
+        part = run(m, xt[:rows].contiguous(), rows)
+        assert torch.equal(part, full[:rows])
+    alone = run(m, xt[9:10].contiguous(), 1)
+    assert torch.equal(alone[0], full[9])
+
+
 def test_qmv_strides_accumulate_prefix_dtypes(cuda_device):
     rng = np.random.default_rng(12)
     N, K, rows = 256, 512, 5
