@@ -47,8 +47,14 @@ typedef enum iq_status {
 
 typedef enum iq_dtype { IQ_F32 = 0, IQ_F16 = 1, IQ_BF16 = 2 } iq_dtype;
 typedef enum iq_mode { IQ_MODE_AFFINE = 0, IQ_MODE_MXFP4 = 1 } iq_mode;
-typedef enum iq_act { IQ_ACT_SILU = 0, IQ_ACT_SWIGLU_OAI = 2 } iq_act; /* qmm.metal:17-31 ACT0 / ACT2 */
+/* FFN activations, numbered as the reference's lab_glu (qmm.metal:9-31): SiLU gate, GELU (tanh form) gate, gpt-oss's
+ * clamped swiglu_oai, and relu^2 of the up projection alone (the gate tensor is then the up tensor, MoE.swift:130-133). */
+typedef enum iq_act { IQ_ACT_SILU = 0, IQ_ACT_GELU = 1, IQ_ACT_SWIGLU_OAI = 2, IQ_ACT_RELU2 = 3 } iq_act;
 typedef enum iq_router_kind { IQ_ROUTER_BF16 = 0, IQ_ROUTER_Q8 = 1 } iq_router_kind;
+/* How the router scores experts (RouterSpec, Loader/ModelSpecParts.swift:64; kernels verify.metal:181-260 and
+ * ab_moe_route.metal:20-53): softmax over the chosen logits, or a sigmoid per expert with an optional bias that only
+ * steers the selection and weights p / (sum of the chosen p + eps). */
+typedef enum iq_router_score { IQ_SCORE_SOFTMAX = 0, IQ_SCORE_SIGMOID = 1 } iq_router_score;
 
 enum { IQ_FLAG_ACCUMULATE = 1 }; /* y += result (VQMV.encode accumulate:, encodeQmmF32 accumulate:) */
 
@@ -157,6 +163,10 @@ typedef struct iq_moe_desc {
     int32_t expert_lo;      /* first expert held here (expert parallel); 0 on one GPU */
     int32_t expert_count;   /* experts held here; == experts on one GPU. The reference's analogue is the
                                expert->slot table `smap` (MoE.swift:104) */
+    int32_t router_score;   /* iq_router_score */
+    float route_eps;        /* sigmoid scoring: added to the sum of the chosen scores before the division */
+    const float* router_select_bias; /* sigmoid scoring: fp32 [E] added to the scores for the selection only
+                                        (e_score_correction_bias) or NULL */
 } iq_moe_desc;
 
 /* Pieces of a forward call, for timing and for callers that run an exchange between them. The names are the

@@ -25,8 +25,9 @@ enum : int32_t { kF32 = 0, kF16 = 1, kBF16 = 2 };
 // Weight formats.
 enum : int32_t { kFmtAffine4 = 0, kFmtAffine8 = 1, kFmtMxfp4 = 2 };
 
-// Gated activations (qmm.metal:17-31 of the reference: ACT0 SiLU, ACT2 swiglu_oai).
-enum : int32_t { kActSilu = 0, kActSwigluOai = 2 };
+// FFN activations, numbered as the reference's lab_glu (qmm.metal:9-31): 0 SiLU gate, 1 GELU (tanh form) gate,
+// 2 gpt-oss's swiglu_oai, 3 relu^2 of the up projection alone (no gate).
+enum : int32_t { kActSilu = 0, kActGelu = 1, kActSwigluOai = 2, kActRelu2 = 3 };
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t u16) { return __uint_as_float(u16 << 16); }
 
@@ -86,10 +87,25 @@ __device__ __forceinline__ float glu(float g, float u, float limit) {
     // noticeable share of the grouped GEMM's epilogue
     if (ACT == kActSilu) {
         return __fdividef(g, 1.0f + __expf(-g)) * u;
+    } else if (ACT == kActGelu) {
+        // g * sigmoid(2z), z = sqrt(2/pi) (g + 0.044715 g^3): 0.5 g (1 + tanh z) without the cancellation in the tail
+        const float z2 = 1.5957691216057308f * (g + 0.044715f * g * g * g);
+        return __fdividef(g, 1.0f + __expf(-z2)) * u;
+    } else if (ACT == kActRelu2) {
+        const float r = fmaxf(u, 0.f);
+        return r * r;
     } else {
         const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
         return __fdividef(gc, 1.0f + __expf(-1.702f * gc)) * (uc + 1.0f);
     }
+}
+
+// The same with the activation chosen at run time (uniform over a launch).
+__device__ __forceinline__ float glu_rt(int32_t act, float g, float u, float limit) {
+    if (act == kActSilu) return glu<kActSilu>(g, u, 0.f);
+    if (act == kActSwigluOai) return glu<kActSwigluOai>(g, u, limit);
+    if (act == kActGelu) return glu<kActGelu>(g, u, 0.f);
+    return glu<kActRelu2>(g, u, 0.f);
 }
 
 // D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)

@@ -55,6 +55,7 @@ struct GqmvParams {
     int32_t accumulate;
     const float* ebias[2];  // expert biases fp32 [E, N] (gate/up: gate and up; down: [0]) or null
     float limit;            // swiglu_oai clamp
+    int32_t act;            // gate/up mode: activation (kAct*)
     // K tiling (host-chosen): K is walked in tiles of `kt` inputs, kt a multiple of 512
     int32_t kt;
     int32_t xs_bytes;    // bytes of the staged-x region (sized for the largest tile)
@@ -383,7 +384,7 @@ __global__ void __launch_bounds__(RG* WK * 32) gqmv_kernel(const GqmvParams p) {
                     v += p.ebias[0][(size_t)tile.expert * p.N + n];
                     u += p.ebias[1][(size_t)tile.expert * p.N + n];
                 }
-                v = p.limit > 0.f ? glu<kActSwigluOai>(v, u, p.limit) : glu<kActSilu>(v, u, 0.f);
+                v = glu_rt(p.act, v, u, p.limit);
             } else if (MODE == kModeDown) {
                 if (p.ebias[0] != nullptr) v += p.ebias[0][(size_t)tile.expert * p.N + n];
             }

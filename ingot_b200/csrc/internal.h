@@ -66,6 +66,7 @@ struct GqmvCall {
     int32_t accumulate = 0;
     const float* ebias[2] = {nullptr, nullptr};
     float limit = 0.f;
+    int32_t act = 0;  // gate/up mode: activation (kAct*)
 };
 int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c);
 
@@ -92,6 +93,7 @@ struct QmmCall {
     int32_t accumulate = 0;
     const float* ebias[2] = {nullptr, nullptr};
     float limit = 0.f;
+    int32_t act = 0;  // gate/up epilogue: activation (kAct*)
 };
 int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c);
 int32_t gqmv_init(iq_ctx* ctx);

@@ -103,6 +103,9 @@ int32_t launch_route(iq_moe* l, cudaStream_t st, const float* logits, int ld, in
     rp.wts = wts;
     rp.T = tokens; rp.E = l->d.experts; rp.ld = ld; rp.topk = l->d.top_k;
     rp.scale = l->d.routed_scale;
+    rp.sigmoid = l->d.router_score == IQ_SCORE_SIGMOID ? 1 : 0;
+    rp.select_bias = l->d.router_select_bias;
+    rp.eps = l->d.route_eps;
     route_kernel_for(l->d.experts)<<<(tokens + 3) / 4, 128, 0, st>>>(rp);
     return check_cuda(l->ctx, cudaGetLastError(), "route_topk launch");
 }
@@ -138,6 +141,7 @@ int32_t run_gateup(iq_moe* l, cudaStream_t cs, const void* x, int32_t x_dtype, i
         c.ebias[1] = d.up_bias - lo * d.d_ff;
     }
     c.limit = d.act == IQ_ACT_SWIGLU_OAI ? d.act_limit : 0.f;
+    c.act = d.act;
     return launch_gqmv(l->ctx, cs, c);
 }
 
@@ -186,6 +190,7 @@ int32_t run_gateup_tc(iq_moe* l, cudaStream_t cs, const __half* rows16, int64_t 
     c.y = h; c.y_dtype = kF16; c.ldy = d.d_ff;
     c.ebias[0] = d.gate_bias; c.ebias[1] = d.up_bias;
     c.limit = d.act == IQ_ACT_SWIGLU_OAI ? d.act_limit : 0.f;
+    c.act = d.act;
     return launch_qmm(l->ctx, cs, c);
 }
 
@@ -236,7 +241,7 @@ __global__ void dswiglu_kernel(const float* __restrict__ gu, __half* __restrict_
     if (i >= (size_t)rows * d_ff) return;
     const size_t r = i / d_ff, c = i % d_ff;
     const float g = gu[r * 2 * d_ff + c], u = gu[r * 2 * d_ff + d_ff + c];
-    h[i] = __float2half_rn(act == kActSwigluOai ? glu<kActSwigluOai>(g, u, limit) : glu<kActSilu>(g, u, 0.f));
+    h[i] = __float2half_rn(glu_rt(act, g, u, limit));
 }
 
 }  // namespace iq
@@ -301,6 +306,7 @@ extern "C" int32_t iq_dense_ffn(iq_ctx* ctx, void* stream, const void* x, int32_
         c.rows = rows; c.max_rows = rows;
         c.y = h; c.y_dtype = kF16; c.ldy = d_ff;
         c.limit = act == IQ_ACT_SWIGLU_OAI ? act_limit : 0.f;
+        c.act = act;
         st = launch_gqmv(ctx, cs, c);
         if (st != kOk) return st;
         return iq_qmv(ctx, stream, h, IQ_F16, d_ff, down, out, out_dtype, ldo, rows, flags, 0);
@@ -333,7 +339,9 @@ extern "C" int32_t iq_moe_create(iq_ctx* ctx, const iq_moe_desc* d, iq_moe** out
     if (d->d_ff <= 0 || d->d_ff % 64 != 0) return fail(ctx, kErrUnsupported, "moe: d_ff = %d (a multiple of 64)", d->d_ff);
     if (d->d_model < 128 || d->d_model % 64 != 0)
         return fail(ctx, kErrUnsupported, "moe: d_model = %d (a multiple of 64, at least 128)", d->d_model);
-    if (d->act != IQ_ACT_SILU && d->act != IQ_ACT_SWIGLU_OAI) return fail(ctx, kErrUnsupported, "moe: activation %d", d->act);
+    if (d->act < IQ_ACT_SILU || d->act > IQ_ACT_RELU2) return fail(ctx, kErrUnsupported, "moe: activation %d", d->act);
+    if (d->router_score != IQ_SCORE_SOFTMAX && d->router_score != IQ_SCORE_SIGMOID)
+        return fail(ctx, kErrUnsupported, "moe: router score %d", d->router_score);
     if (d->router_kind != IQ_ROUTER_BF16 && d->router_kind != IQ_ROUTER_Q8)
         return fail(ctx, kErrUnsupported, "moe: router kind %d (bf16 or 8-bit g64; a 4-bit router is not supported)",
                     d->router_kind);

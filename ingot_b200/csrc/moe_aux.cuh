@@ -293,6 +293,9 @@ struct RouteParams {
     float* wts;                // [T, topk]
     int32_t T, E, ld, topk;
     float scale;
+    int32_t sigmoid;           // 0: softmax over the chosen logits; 1: sigmoid scores
+    const float* select_bias;  // sigmoid: [E] added to the scores for the selection only, or null
+    float eps;                 // sigmoid: added to the sum of the chosen scores
 };
 
 template <int VPL>
@@ -301,18 +304,27 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (t >= p.T) return;
     const float* lr = p.logits + (size_t)t * p.ld;
-    float v[VPL];
+    float v[VPL];   // what the selection compares
+    float pv[VPL];  // sigmoid: the unbiased score the weight is made of
     uint32_t taken = 0;
 #pragma unroll
     for (int j = 0; j < VPL; j++) {
         const int e = j * 32 + lane;
         float f = e < p.E ? lr[e] : -INFINITY;
         if (e < p.E && p.logit_bias != nullptr) f += p.logit_bias[e];
+        pv[j] = 0.f;
+        if (p.sigmoid) {
+            // the fp32 score is the correctly rounded sigmoid (evaluated in float64), so that the selection does not
+            // depend on an exp implementation
+            f = (float)(1.0 / (1.0 + exp(-(double)f)));
+            pv[j] = f;
+            if (e < p.E && p.select_bias != nullptr) f += p.select_bias[e];
+        }
         if (f != f) f = -INFINITY;
         v[j] = f;
         if (e >= p.E) taken |= 1u << j;
     }
-    float myv = -INFINITY;
+    float myv = -INFINITY, myp = 0.f;
     uint32_t myi = 0;
     for (int k = 0; k < p.topk; k++) {
         float bv = -INFINITY;
@@ -337,10 +349,27 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
         uint32_t gi = (bi != 0xFFFFFFFFu && bv == gv) ? bi : 0xFFFFFFFFu;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) gi = min(gi, __shfl_xor_sync(0xffffffffu, gi, o));
+        float gp = 0.f;  // the chosen expert's unbiased score, from the lane that holds it
 #pragma unroll
         for (int j = 0; j < VPL; j++)
-            if ((uint32_t)(j * 32 + lane) == gi) taken |= 1u << j;
-        if (lane == k) { myv = gv; myi = gi; }
+            if ((uint32_t)(j * 32 + lane) == gi) {
+                taken |= 1u << j;
+                gp = pv[j];
+            }
+        gp = __shfl_sync(0xffffffffu, gp, gi & 31u);
+        if (lane == k) { myv = gv; myi = gi; myp = gp; }
+    }
+    if (p.sigmoid) {
+        float sum = 0.f;
+        for (int k = 0; k < p.topk; k++) sum += __shfl_sync(0xffffffffu, myp, k);
+        sum += p.eps;
+        if (lane < p.topk) {
+            float w = myp / sum * p.scale;
+            if (p.pes != nullptr) w *= p.pes[myi];
+            p.inds[(size_t)t * p.topk + lane] = myi;
+            p.wts[(size_t)t * p.topk + lane] = w;
+        }
+        return;
     }
     const float top1 = __shfl_sync(0xffffffffu, myv, 0);
     const float ex = lane < p.topk ? expf(myv - top1) : 0.f;

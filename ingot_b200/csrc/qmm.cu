@@ -16,13 +16,14 @@ struct KernelEntry {
     int32_t fmt;
     int bn;
     int epi;
+    int act;
     QmmKernel fn;
     int smem;
 };
 
-template <int FMT, int BN, int EPI>
+template <int FMT, int BN, int EPI, int ACT = kActSilu>
 KernelEntry entry() {
-    return KernelEntry{FMT, BN, EPI, qmm_tc_kernel<FMT, BN, EPI>, QmmSmem<FMT, BN, EPI>::TOTAL};
+    return KernelEntry{FMT, BN, EPI, ACT, qmm_tc_kernel<FMT, BN, EPI, ACT>, QmmSmem<FMT, BN, EPI>::TOTAL};
 }
 
 const KernelEntry* table(int* n) {
@@ -32,16 +33,23 @@ const KernelEntry* table(int* n) {
         entry<kFmtMxfp4, 256, kEpiStore>(),   entry<kFmtMxfp4, 128, kEpiStore>(),
         entry<kFmtAffine4, 128, kEpiGateUp>(), entry<kFmtMxfp4, 128, kEpiGateUp>(),
         entry<kFmtAffine4, 256, kEpiGateUp>(), entry<kFmtMxfp4, 256, kEpiGateUp>(),
+        entry<kFmtAffine4, 128, kEpiGateUp, kActSwigluOai>(), entry<kFmtMxfp4, 128, kEpiGateUp, kActSwigluOai>(),
+        entry<kFmtAffine4, 256, kEpiGateUp, kActSwigluOai>(), entry<kFmtMxfp4, 256, kEpiGateUp, kActSwigluOai>(),
+        entry<kFmtAffine4, 128, kEpiGateUp, kActGelu>(), entry<kFmtAffine4, 256, kEpiGateUp, kActGelu>(),
+        entry<kFmtAffine4, 128, kEpiGateUp, kActRelu2>(), entry<kFmtAffine4, 256, kEpiGateUp, kActRelu2>(),
+        entry<kFmtMxfp4, 128, kEpiGateUp, kActGelu>(), entry<kFmtMxfp4, 256, kEpiGateUp, kActGelu>(),
+        entry<kFmtMxfp4, 128, kEpiGateUp, kActRelu2>(), entry<kFmtMxfp4, 256, kEpiGateUp, kActRelu2>(),
     };
     *n = (int)(sizeof(t) / sizeof(t[0]));
     return t;
 }
 
-const KernelEntry* find(int32_t fmt, int bn, int epi) {
+const KernelEntry* find(int32_t fmt, int bn, int epi, int act) {
     int n;
     const KernelEntry* t = table(&n);
+    if (epi != kEpiGateUp) act = kActSilu;
     for (int i = 0; i < n; i++)
-        if (t[i].fmt == fmt && t[i].bn == bn && t[i].epi == epi) return &t[i];
+        if (t[i].fmt == fmt && t[i].bn == bn && t[i].epi == epi && t[i].act == act) return &t[i];
     return nullptr;
 }
 
@@ -78,7 +86,7 @@ int32_t make_map_2d(iq_ctx* ctx, CUtensorMap* map, const void* base, bool f16, u
 }
 
 int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
-    const KernelEntry* ke = find(c.fmt, c.bn, c.epi);
+    const KernelEntry* ke = find(c.fmt, c.bn, c.epi, c.act);
     if (ke == nullptr) return fail(ctx, kErrNoKernel, "qmm: no kernel for format %d, tile %d, epilogue %d", c.fmt, c.bn, c.epi);
     const int pack_row = c.fmt == kFmtAffine8 ? 64 : 32;
     const uint64_t row_bytes = (uint64_t)c.K / kBK * pack_row;

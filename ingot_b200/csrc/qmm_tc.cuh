@@ -143,7 +143,9 @@ struct QmmSmem {
     static_assert(STAGES >= 2, "need at least two stages");
 };
 
-template <int FMT, int BN, int EPI>
+// ACT: activation of the gate/up epilogue (kAct*), fixed at compile time: the epilogue is on the critical path when gate
+// and up fill tensor memory, and a run-time choice in its inner loop measured a quarter slower.
+template <int FMT, int BN, int EPI, int ACT = kActSilu>
 __global__ void __launch_bounds__(kQmmThreads, 1)
     qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w0,
                   const __grid_constant__ CUtensorMap map_w1, const QmmParams p) {
@@ -304,7 +306,7 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                         // half first, GU_HALF, Shaders/qmm_nax_moe.metal:491-505: a storage choice, not needed here)
                         const float g = v;
                         const float u = __uint_as_float(r1[j]) + bias1;
-                        v = p.limit > 0.f ? glu<kActSwigluOai>(g, u, p.limit) : glu<kActSilu>(g, u, 0.f);
+                        v = glu<ACT>(g, u, p.limit);
                     }
                     const size_t o = (size_t)(row0 + c0 + j) * p.ldy + n;
                     if (p.y_dtype == kF32) {

@@ -135,6 +135,7 @@ int32_t launch_qmv_stream(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     p.tiles = c.tiles; p.ntiles = c.ntiles; p.M = c.rows;
     p.y = c.y; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
     p.limit = c.limit;
+    p.act = c.act;
     p.R = R; p.NB = (c.N + R - 1) / R; p.rgs = rgs; p.wk = 8 / rgs;
     p.row_bytes = row_bytes; p.srow_bytes = srow_bytes; p.mat_bytes = mat_bytes; p.stage_bytes = stage_bytes;
     p.nstages = nstages;
@@ -315,6 +316,7 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
     p.tiles = c.tiles; p.ntiles = c.ntiles;
     p.y = c.y; p.y_dtype = c.y_dtype; p.ldy = c.ldy;
     p.limit = c.limit;
+    p.act = c.act;
     p.status = ctx->d_status;
     const int64_t items = (int64_t)p.NB * c.grid_tiles;
     const int64_t slots = (int64_t)ctx->sms * ctas;
@@ -429,6 +431,7 @@ int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     p.tiles = c.tiles; p.ntiles = c.ntiles; p.M = c.rows;
     p.y = c.y; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
     p.limit = c.limit;
+    p.act = c.act;
     p.kt = kt; p.xs_bytes = xs_bytes;
 
     dim3 grid((c.N / 16 + rg - 1) / rg, c.grid_tiles, 1);

@@ -40,6 +40,7 @@ struct QgParams {
     int64_t ldy;
     const float* ebias[2];
     float limit;
+    int32_t act;
     int32_t rgs, wk;             // row blocks of 16 per item x K slices = 8 consumer warps
     int32_t NB;                  // items per tile
     int32_t row_bytes, row_pitch, srow_bytes;
@@ -287,7 +288,7 @@ __global__ void __launch_bounds__(kQgThreads, 1) qmv_imma_grouped_kernel(const Q
                             v += p.ebias[0][(size_t)tile.expert * p.N + n];
                             u += p.ebias[1][(size_t)tile.expert * p.N + n];
                         }
-                        v = p.limit > 0.f ? glu<kActSwigluOai>(v, u, p.limit) : glu<kActSilu>(v, u, 0.f);
+                        v = glu_rt(p.act, v, u, p.limit);
                     } else {
                         if (p.ebias[0] != nullptr) v += p.ebias[0][(size_t)tile.expert * p.N + n];
                     }

@@ -45,6 +45,7 @@ struct QsParams {
     int32_t accumulate;
     const float* ebias[2];
     float limit;
+    int32_t act;
     // blocking
     int32_t R;          // weight rows per block (16 * rgs)
     int32_t NB;         // blocks per expert
@@ -342,7 +343,7 @@ __global__ void __launch_bounds__(kQsThreads, (MH == 1 && MODE != kModeGateUp) ?
                             v += p.ebias[0][(size_t)tile.expert * p.N + n];
                             u += p.ebias[1][(size_t)tile.expert * p.N + n];
                         }
-                        v = p.limit > 0.f ? glu<kActSwigluOai>(v, u, p.limit) : glu<kActSilu>(v, u, 0.f);
+                        v = glu_rt(p.act, v, u, p.limit);
                     } else if (MODE == kModeDown) {
                         if (p.ebias[0] != nullptr) v += p.ebias[0][(size_t)tile.expert * p.N + n];
                     }

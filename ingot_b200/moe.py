@@ -22,12 +22,17 @@ PIECES = {
 
 
 class RouterSpec:
-    """What the router does (the softmax family of the reference's RouterSpec, Loader/ModelSpecParts.swift:64)."""
+    """What the router does (the reference's RouterSpec, Loader/ModelSpecParts.swift:64): softmax over the chosen logits
+    (score="softmax") or a sigmoid per expert (score="sigmoid") with an optional selection bias and eps."""
 
     def __init__(self, experts: int, top_k: int, scale: float = 1.0, logit_bias: Optional[torch.Tensor] = None,
-                 per_expert_scale: Optional[torch.Tensor] = None):
+                 per_expert_scale: Optional[torch.Tensor] = None, score: str = "softmax",
+                 select_bias: Optional[torch.Tensor] = None, eps: float = 0.0):
+        if score not in ("softmax", "sigmoid"):
+            raise ValueError("score is 'softmax' or 'sigmoid'")
         self.experts, self.top_k, self.scale = experts, top_k, scale
         self.logit_bias, self.per_expert_scale = logit_bias, per_expert_scale
+        self.score, self.select_bias, self.eps = score, select_bias, eps
 
 
 class MoELayer:
@@ -38,13 +43,13 @@ class MoELayer:
                  router_biases: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None,
                  up_bias: Optional[torch.Tensor] = None, down_bias: Optional[torch.Tensor] = None, expert_lo: int = 0,
                  max_tokens: int = 16):
-        _need_cuda(router_w, gate_bias, up_bias, down_bias, router.logit_bias, router.per_expert_scale)
+        _need_cuda(router_w, gate_bias, up_bias, down_bias, router.logit_bias, router.per_expert_scale, router.select_bias)
         self.router, self.gate, self.up, self.down = router, gate, up, down
         self.D, self.I = gate.K, gate.N
         self.device = gate.w.device
         self._keep = [router_w, router_scales, router_biases, gate_bias, up_bias, down_bias, router.logit_bias,
-                      router.per_expert_scale]
-        for t in (gate_bias, up_bias, down_bias, router.logit_bias, router.per_expert_scale):
+                      router.per_expert_scale, router.select_bias]
+        for t in (gate_bias, up_bias, down_bias, router.logit_bias, router.per_expert_scale, router.select_bias):
             if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
                 raise TypeError("expert biases, router bias and per-expert scale are contiguous float32 tensors")
         if router_w.dtype == torch.bfloat16:
@@ -56,7 +61,8 @@ class MoELayer:
         ptr = lambda t: 0 if t is None else t.data_ptr()
         d = capi.MoeDesc()
         d.experts, d.top_k, d.d_model, d.d_ff = router.experts, router.top_k, self.D, self.I
-        d.act = {"silu": capi.IQ_ACT_SILU, "swiglu_oai": capi.IQ_ACT_SWIGLU_OAI}[act]
+        d.act = {"silu": capi.IQ_ACT_SILU, "gelu": capi.IQ_ACT_GELU, "swiglu_oai": capi.IQ_ACT_SWIGLU_OAI,
+                 "relu2": capi.IQ_ACT_RELU2}[act]
         d.act_limit = limit
         d.router_kind = kind
         d.routed_scale = router.scale
@@ -65,6 +71,9 @@ class MoELayer:
         d.gate, d.up, d.down = gate.qlinear(), up.qlinear(), down.qlinear()
         d.gate_bias, d.up_bias, d.down_bias = ptr(gate_bias), ptr(up_bias), ptr(down_bias)
         d.expert_lo, d.expert_count = expert_lo, gate.experts
+        d.router_score = capi.IQ_SCORE_SIGMOID if router.score == "sigmoid" else capi.IQ_SCORE_SOFTMAX
+        d.route_eps = router.eps
+        d.router_select_bias = ptr(router.select_bias)
         self.ctx = capi.context(self.device.index or 0)
         self._h = C.c_void_p()
         self.ctx.check(capi.lib().iq_moe_create(self.ctx.handle, C.byref(d), C.byref(self._h)))

@@ -133,7 +133,22 @@ def swiglu_oai(g, u, limit: float = 7.0, alpha: float = 1.702):
     return ((u + np.float32(1)) * (g / (np.float32(1) + np.exp(np.float32(-alpha) * g)))).astype(np.float32)
 
 
-ACTS = {"silu": silu_glu, "swiglu_oai": swiglu_oai}
+def gelu_glu(g, u):
+    """GELU (tanh form, mlx-lm nn.gelu_approx) gate: 0.5 g (1 + tanh z) u, z = sqrt(2/pi) (g + 0.044715 g^3), written as
+    g sigmoid(2z) u like the reference (qmm.metal:11-13, 21-23)."""
+    g = np.asarray(g, dtype=np.float32)
+    z2 = (np.float32(1.5957691216057308) * (g + np.float32(0.044715) * g * g * g)).astype(np.float32)
+    with np.errstate(over="ignore"):
+        return (g / (np.float32(1) + np.exp(-z2)) * np.asarray(u, dtype=np.float32)).astype(np.float32)
+
+
+def relu2(g, u):
+    """Nemotron-H's relu^2 without gate (qmm.metal:15-16, 24-26): max(u, 0)^2; g is ignored."""
+    r = np.maximum(np.asarray(u, dtype=np.float32), np.float32(0))
+    return (r * r).astype(np.float32)
+
+
+ACTS = {"silu": silu_glu, "swiglu_oai": swiglu_oai, "gelu": gelu_glu, "relu2": relu2}
 
 # ----------------------------------------------------------------------------------------------------------------
 # router
@@ -160,7 +175,9 @@ def route(logits: np.ndarray, top_k: int, *, logit_bias=None, select_bias=None, 
     if logit_bias is not None:
         l = (l + np.asarray(logit_bias, dtype=np.float32)[None, :]).astype(np.float32)
     if sigmoid:
-        p = (np.float32(1) / (np.float32(1) + np.exp(-l))).astype(np.float32)
+        # the fp32 score is the correctly rounded sigmoid (evaluated in float64): independent of an exp implementation
+        with np.errstate(over="ignore"):
+            p = (1.0 / (1.0 + np.exp(-l.astype(np.float64)))).astype(np.float32)
     else:
         p = l
     sel = p if select_bias is None else (p + np.asarray(select_bias, dtype=np.float32)[None, :]).astype(np.float32)

@@ -108,12 +108,12 @@ def test_moe_c3_configuration(cuda_device, T):
     check_layer(layer, host, synth.activations_np(rng, T, 2880), T, "swiglu_oai")
 
 
-def softmax_cases():
+def router_cases():
     with open(os.path.join(GOLD, "router_vectors.json")) as f:
-        return [c for c in json.load(f)["cases"] if c["score"] == "softmax"]
+        return json.load(f)["cases"]
 
 
-@pytest.mark.parametrize("case", softmax_cases(), ids=lambda c: c["name"])
+@pytest.mark.parametrize("case", router_cases(), ids=lambda c: c["name"])
 def test_route_kernel_against_mlx_lm_vectors(cuda_device, case):
     """The route kernel on the reference's router vectors (logits at the stride padded to 64): indices bit-exact against
     the CPU rule, weights 1e-5, chosen sets and weights against mlx-lm on rows 2.. (KernelCaseRouter.swift:110-141)."""
@@ -121,11 +121,13 @@ def test_route_kernel_against_mlx_lm_vectors(cuda_device, case):
     E, K, B = case["experts"], case["topK"], case["rows"]
     lb = case.get("logitBias")
     pes = case.get("perExpertScale")
+    sig = case["score"] == "sigmoid"
+    sb = case.get("bias") if sig else None  # sigmoid families: the bias only steers the selection
+    dev_f32 = lambda v: None if v is None else torch.tensor(v, dtype=torch.float32, device=cuda_device)
     g, u, d = synth.affine_np(rng, 64, 128, 4, E), synth.affine_np(rng, 64, 128, 4, E), synth.affine_np(rng, 128, 64, 4, E)
     mk = lambda t: synth.dense_q_affine(t[0], t[1], t[2], 4, cuda_device)
-    spec = RouterSpec(E, K, scale=case["scale"],
-                      logit_bias=None if lb is None else torch.tensor(lb, dtype=torch.float32, device=cuda_device),
-                      per_expert_scale=None if pes is None else torch.tensor(pes, dtype=torch.float32, device=cuda_device))
+    spec = RouterSpec(E, K, scale=case["scale"], logit_bias=dev_f32(lb), per_expert_scale=dev_f32(pes),
+                      score=case["score"], select_bias=dev_f32(sb), eps=case["eps"] if sig else 0.0)
     layer = MoELayer(spec, synth.bf16_values_tensor(synth.router_np(rng, E, 128), cuda_device), mk(g), mk(u), mk(d))
     ld = (E + 63) // 64 * 64
     lg = np.array(case["logits"], dtype=np.float32).reshape(B, E)
@@ -133,7 +135,8 @@ def test_route_kernel_against_mlx_lm_vectors(cuda_device, case):
     padded[:, :E] = lg
     inds, wts = layer.route(torch.from_numpy(padded).to(cuda_device), B)
     torch.cuda.synchronize()
-    ri, rw = qref.route(lg, K, logit_bias=lb, scale=case["scale"], per_expert_scale=pes)
+    ri, rw = qref.route(lg, K, logit_bias=lb, scale=case["scale"], per_expert_scale=pes, sigmoid=sig, select_bias=sb,
+                        eps=case["eps"] if sig else 0.0)
     assert np.array_equal(inds.cpu().numpy().astype(np.uint32), ri)
     assert qref.max_rel(wts.cpu().numpy(), rw) <= 1e-5
     dense = np.zeros((B, E), dtype=np.float32)
@@ -194,6 +197,16 @@ def test_router_8bit_affine(cuda_device, T):
     assert np.array_equal(v["logits"][:, :E].cpu().numpy(), logits)
     inds, _ = qref.route(logits, K)
     assert np.array_equal(v["inds"].cpu().numpy().astype(np.uint32), inds)
+
+
+@pytest.mark.parametrize("act", ["gelu", "relu2"])
+@pytest.mark.parametrize("T", [3, 40, 700])
+def test_moe_other_activations(cuda_device, act, T):
+    """GELU (tanh form) gate and relu^2 without gate (qmm.metal:9-31 ACT 1 and 3) through the decode tiles (int8 and fp16
+    GEMV kernels) and the tcgen05 grouped GEMM."""
+    rng = np.random.default_rng(90 + T)
+    layer, host = build_layer(rng, cuda_device, 32, 2, 2048, 128, act=act, max_tokens=T)
+    check_layer(layer, host, synth.activations_np(rng, T, 2048), T, act)
 
 
 def test_moe_load_guards(cuda_device):
