@@ -55,6 +55,8 @@ typedef enum iq_router_kind { IQ_ROUTER_BF16 = 0, IQ_ROUTER_Q8 = 1 } iq_router_k
  * ab_moe_route.metal:20-53): softmax over the chosen logits, or a sigmoid per expert with an optional bias that only
  * steers the selection and weights p / (sum of the chosen p + eps). */
 typedef enum iq_router_score { IQ_SCORE_SOFTMAX = 0, IQ_SCORE_SIGMOID = 1 } iq_router_score;
+/* Shared expert: none, with a sigmoid gate per token, or with weight 1 (LAB_MOE_SHARED 0 / 1 / 2, verify.metal:165). */
+typedef enum iq_shared_kind { IQ_SHARED_NONE = 0, IQ_SHARED_GATED = 1, IQ_SHARED_UNGATED = 2 } iq_shared_kind;
 
 enum { IQ_FLAG_ACCUMULATE = 1 }; /* y += result (VQMV.encode accumulate:, encodeQmmF32 accumulate:) */
 
@@ -167,6 +169,13 @@ typedef struct iq_moe_desc {
     float route_eps;        /* sigmoid scoring: added to the sum of the chosen scores before the division */
     const float* router_select_bias; /* sigmoid scoring: fp32 [E] added to the scores for the selection only
                                         (e_score_correction_bias) or NULL */
+    /* Shared expert (MoE.swift:140-154): one more FFN that every token goes through, 4-bit affine g64, its own width
+     * (shared_gate_proj.n); out += w_s * down_s(act(gate_s x, up_s x)) with w_s = sigmoid(x . shared_gate) or 1. */
+    int32_t shared;                  /* iq_shared_kind */
+    iq_qlinear shared_gate_proj;     /* [1, d_ff_s, d_model] (relu^2: pass the up tensor) */
+    iq_qlinear shared_up;            /* [1, d_ff_s, d_model] */
+    iq_qlinear shared_down;          /* [1, d_model, d_ff_s] */
+    iq_qlinear shared_gate;          /* IQ_SHARED_GATED: 8-bit affine g64 [1, 1, d_model], the gate's logit weights */
 } iq_moe_desc;
 
 /* Pieces of a forward call, for timing and for callers that run an exchange between them. The names are the

@@ -12,6 +12,7 @@ IQ_MODE_AFFINE, IQ_MODE_MXFP4 = 0, 1
 IQ_ACT_SILU, IQ_ACT_GELU, IQ_ACT_SWIGLU_OAI, IQ_ACT_RELU2 = 0, 1, 2, 3
 IQ_ROUTER_BF16, IQ_ROUTER_Q8 = 0, 1
 IQ_SCORE_SOFTMAX, IQ_SCORE_SIGMOID = 0, 1
+IQ_SHARED_NONE, IQ_SHARED_GATED, IQ_SHARED_UNGATED = 0, 1, 2
 IQ_FLAG_ACCUMULATE = 1
 IQ_PIECE_ROUTER, IQ_PIECE_ROUTE, IQ_PIECE_GROUP, IQ_PIECE_GATEUP, IQ_PIECE_DOWN, IQ_PIECE_COMBINE = 1, 2, 4, 8, 16, 32
 IQ_PIECE_ALL = 63
@@ -40,7 +41,9 @@ class MoeDesc(C.Structure):
                 ("gate", QLinear), ("up", QLinear), ("down", QLinear),
                 ("gate_bias", C.c_void_p), ("up_bias", C.c_void_p), ("down_bias", C.c_void_p),
                 ("expert_lo", C.c_int32), ("expert_count", C.c_int32),
-                ("router_score", C.c_int32), ("route_eps", C.c_float), ("router_select_bias", C.c_void_p)]
+                ("router_score", C.c_int32), ("route_eps", C.c_float), ("router_select_bias", C.c_void_p),
+                ("shared", C.c_int32), ("shared_gate_proj", QLinear), ("shared_up", QLinear), ("shared_down", QLinear),
+                ("shared_gate", QLinear)]
 
 
 class MoeViews(C.Structure):

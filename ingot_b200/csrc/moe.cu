@@ -32,6 +32,13 @@ struct MoeWs {
     __half* h;
     void* yd;
     __half* xs;  // activations in expert order, fp16 [P, d_model] (tensor-core path)
+    // shared expert (only when the layer has one): fp16 copy of x, h, output, per-token weight, tile list
+    __half* s_x16;
+    __half* s_h;
+    void* s_yd;
+    float* s_w;
+    Tile* s_tiles;
+    uint32_t* s_ntiles;
     size_t bytes;
 };
 
@@ -76,6 +83,16 @@ MoeWs carve(const iq_moe* l, void* base, int tokens) {
     w.h = static_cast<__half*>(take(P * d.d_ff * 2));
     w.yd = take(P * d.d_model * (yd_dtype_of(l) == kF16 ? 2 : 4));
     w.xs = static_cast<__half*>(take(P * d.d_model * 2));
+    w.s_x16 = nullptr; w.s_h = nullptr; w.s_yd = nullptr; w.s_w = nullptr; w.s_tiles = nullptr; w.s_ntiles = nullptr;
+    if (d.shared != IQ_SHARED_NONE) {
+        const size_t T = (size_t)tokens;
+        w.s_x16 = static_cast<__half*>(take(T * d.d_model * 2));
+        w.s_h = static_cast<__half*>(take(T * d.shared_up.n * 2));
+        w.s_yd = take(T * d.d_model * 4);
+        w.s_w = static_cast<float*>(take(T * 4));
+        w.s_tiles = static_cast<Tile*>(take((T / 16 + 2) * sizeof(Tile)));
+        w.s_ntiles = static_cast<uint32_t*>(take(16));
+    }
     w.bytes = off;
     return w;
 }
@@ -207,6 +224,47 @@ int32_t run_down_tc(iq_moe* l, cudaStream_t cs, const __half* h, int64_t n_rows,
     c.y = yd; c.y_dtype = yd_dtype; c.ldy = d.d_model;
     c.ebias[0] = d.down_bias;
     return launch_qmm(l->ctx, cs, c);
+}
+
+// The shared expert (MoE.swift:140-154; the reference runs it as expert id E of the same kernels): one more FFN over all
+// tokens, rows in place, through the same tile kernels with a copy of the layer whose expert tensors are the shared
+// expert's; out += w_s * y_s with w_s = sigmoid(x . shared_gate) or 1.
+int32_t run_shared_expert(iq_moe* l, cudaStream_t cs, const void* x, int32_t x_dtype, int64_t ldx, int tokens, const MoeWs& w,
+                          void* out, int32_t out_dtype, int64_t ldo) {
+    const iq_moe_desc& d = l->d;
+    iq_ctx* ctx = l->ctx;
+    iq_moe tmp = *l;
+    tmp.d.gate = d.shared_gate_proj; tmp.d.up = d.shared_up; tmp.d.down = d.shared_down;
+    tmp.d.d_ff = d.shared_up.n;
+    tmp.d.expert_lo = 0; tmp.d.expert_count = 1;
+    tmp.d.gate_bias = nullptr; tmp.d.up_bias = nullptr; tmp.d.down_bias = nullptr;
+    const bool gated = d.shared == IQ_SHARED_GATED;
+    shared_gate_kernel<<<(tokens + 3) / 4, 128, 0, cs>>>(
+        x, x_dtype, ldx, gated ? static_cast<const uint32_t*>(d.shared_gate.w) : nullptr,
+        static_cast<const uint16_t*>(d.shared_gate.scales), static_cast<const uint16_t*>(d.shared_gate.biases), w.s_w, tokens,
+        d.d_model);
+    int32_t st = check_cuda(ctx, cudaGetLastError(), "shared_gate launch");
+    if (st != kOk) return st;
+    const int32_t ydt = yd_dtype_of(l);
+    if (use_tensor_path(tokens, 1)) {
+        const int bn = tensor_tile_rows(tokens, 1);
+        const size_t units = (size_t)tokens * d.d_model / 8;
+        rows_to_f16_kernel<<<(unsigned)((units + 255) / 256), 256, 0, cs>>>(x, x_dtype, ldx, w.s_x16, tokens, d.d_model);
+        shared_tiles_kernel<<<1, 128, 0, cs>>>(tokens, bn, 0u, w.s_tiles, w.s_ntiles);
+        st = check_cuda(ctx, cudaGetLastError(), "shared tiles launch");
+        if (st == kOk) st = run_gateup_tc(&tmp, cs, w.s_x16, tokens, w.s_tiles, w.s_ntiles, w.s_h, bn);
+        if (st == kOk) st = run_down_tc(&tmp, cs, w.s_h, tokens, w.s_tiles, w.s_ntiles, w.s_yd, ydt, bn);
+    } else {
+        const int bm = 16;
+        shared_tiles_kernel<<<1, 128, 0, cs>>>(tokens, bm, 0u, w.s_tiles, w.s_ntiles);
+        st = check_cuda(ctx, cudaGetLastError(), "shared tiles launch");
+        const int max_tiles = (tokens + bm - 1) / bm;
+        if (st == kOk) st = run_gateup(&tmp, cs, x, x_dtype, ldx, nullptr, w.s_tiles, w.s_ntiles, max_tiles, bm, w.s_h);
+        if (st == kOk) st = run_down(&tmp, cs, w.s_h, w.s_tiles, w.s_ntiles, max_tiles, bm, w.s_yd, ydt);
+    }
+    if (st != kOk) return st;
+    shared_add_kernel<<<tokens, 256, 0, cs>>>(w.s_yd, ydt, w.s_w, out, out_dtype, ldo, tokens, d.d_model);
+    return check_cuda(ctx, cudaGetLastError(), "shared_add launch");
 }
 
 // The experts' kernels wrote yd; the rows then go where the caller's table points (peer memory included).
@@ -363,6 +421,29 @@ extern "C" int32_t iq_moe_create(iq_ctx* ctx, const iq_moe_desc* d, iq_moe** out
         return fail(ctx, kErrInvalidArg, "moe: affine experts without biases");
     if ((d->gate_bias != nullptr) != (d->up_bias != nullptr))
         return fail(ctx, kErrInvalidArg, "moe: gate and up expert biases go together");
+    if (d->shared != IQ_SHARED_NONE) {
+        // the reference's load guards (MoE.swift:186-219, MoEPrefill.swift:129-141): 4-bit affine shared expert, 8-bit
+        // gate, width a multiple of 64, no shared expert beside MXFP4 experts
+        if (d->shared != IQ_SHARED_GATED && d->shared != IQ_SHARED_UNGATED)
+            return fail(ctx, kErrUnsupported, "moe: shared expert kind %d", d->shared);
+        if (fg == kFmtMxfp4) return fail(ctx, kErrUnsupported, "moe: MXFP4 experts have no shared expert");
+        if (format_of(&d->shared_gate_proj) != kFmtAffine4 || format_of(&d->shared_up) != kFmtAffine4 ||
+            format_of(&d->shared_down) != kFmtAffine4)
+            return fail(ctx, kErrUnsupported, "moe: the shared expert must be 4-bit affine g64 (got %d/%d/%d bits)",
+                        d->shared_gate_proj.bits, d->shared_up.bits, d->shared_down.bits);
+        const int si = d->shared_up.n;
+        if (si < 64 || si % 64 != 0 || d->shared_gate_proj.n != si || d->shared_up.k != d->d_model ||
+            d->shared_gate_proj.k != d->d_model || d->shared_down.n != d->d_model || d->shared_down.k != si ||
+            d->shared_up.experts != 1 || d->shared_gate_proj.experts != 1 || d->shared_down.experts != 1)
+            return fail(ctx, kErrInvalidArg, "moe: shared expert shapes (width %d)", si);
+        if (!d->shared_gate_proj.w || !d->shared_up.w || !d->shared_down.w || !d->shared_gate_proj.biases ||
+            !d->shared_up.biases || !d->shared_down.biases)
+            return fail(ctx, kErrInvalidArg, "moe: shared expert tensors missing");
+        if (d->shared == IQ_SHARED_GATED &&
+            (format_of(&d->shared_gate) != kFmtAffine8 || d->shared_gate.n != 1 || d->shared_gate.k != d->d_model ||
+             !d->shared_gate.w || !d->shared_gate.scales || !d->shared_gate.biases))
+            return fail(ctx, kErrUnsupported, "moe: the shared expert's gate must be 8-bit affine g64 [1, d_model]");
+    }
     iq_moe* l = new (std::nothrow) iq_moe();
     if (l == nullptr) return kErrCuda;
     l->ctx = ctx;
@@ -532,6 +613,10 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
         moe_combine_kernel<<<tokens, 256, 0, cs>>>(cp);
         st = check_cuda(ctx, cudaGetLastError(), "moe_combine launch");
         if (st != kOk) return st;
+        if (d.shared != IQ_SHARED_NONE) {
+            st = run_shared_expert(l, cs, x, x_dtype, ldx, tokens, w, out, out_dtype, ldo);
+            if (st != kOk) return st;
+        }
     }
     return kOk;
 }

@@ -733,6 +733,72 @@ __global__ void __launch_bounds__(256) moe_scatter_rows_kernel(const void* __res
     for (int u = threadIdx.x & 63; u < row_bytes / 16; u += 64) d[u] = ldg_nc_u4(s + u);
 }
 
+// Shared expert: the per-token weight sigmoid(x . w) with w an 8-bit affine g64 row (verify.metal:262-277), or 1 without
+// a gate tensor. One warp per token, fixed lane order.
+__global__ void __launch_bounds__(128) shared_gate_kernel(const void* __restrict__ x, int32_t x_dtype, int64_t ldx,
+                                                         const uint32_t* __restrict__ gw, const uint16_t* __restrict__ gs,
+                                                         const uint16_t* __restrict__ gb, float* __restrict__ sg, int T,
+                                                         int D) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (t >= T) return;
+    float w = 1.f;
+    if (gw != nullptr) {
+        float acc = 0.f;
+        for (int u = lane; u < D / 8; u += 32) {
+            float v[8];
+            load_x8(x, x_dtype, (size_t)t * ldx + u * 8, v);
+            const uint2 q = *reinterpret_cast<const uint2*>(gw + u * 2);
+            const float sc = bf16_bits_to_f32(gs[u / 8]), bi = bf16_bits_to_f32(gb[u / 8]);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                acc = fmaf(v[j], fmaf(sc, (float)((q.x >> (8 * j)) & 0xFFu), bi), acc);
+                acc = fmaf(v[4 + j], fmaf(sc, (float)((q.y >> (8 * j)) & 0xFFu), bi), acc);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        w = 1.0f / (1.0f + expf(-acc));
+    }
+    if (lane == 0) sg[t] = w;
+}
+
+// fp16 copy of x [T, D] (rows in place), the tensor-core GEMM's operand type
+__global__ void __launch_bounds__(256) rows_to_f16_kernel(const void* __restrict__ x, int32_t x_dtype, int64_t ldx,
+                                                         __half* __restrict__ out, int T, int D) {
+    const size_t i = ((size_t)blockIdx.x * 256 + threadIdx.x) * 8;
+    if (i >= (size_t)T * D) return;
+    const size_t r = i / D, c = i % D;
+    float v[8];
+    load_x8(x, x_dtype, r * ldx + c, v);
+    uint4 o;
+    o.x = pack_half2(v[0], v[1]); o.y = pack_half2(v[2], v[3]); o.z = pack_half2(v[4], v[5]); o.w = pack_half2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(out + i) = o;
+}
+
+// Tile list of the shared expert: all T rows in place, tiles of bm rows, expert id `expert`.
+__global__ void shared_tiles_kernel(int T, int bm, uint32_t expert, Tile* __restrict__ tiles, uint32_t* __restrict__ ntiles) {
+    const int n = (T + bm - 1) / bm;
+    for (int j = threadIdx.x; j < n; j += blockDim.x)
+        tiles[j] = Tile{expert, (uint32_t)(j * bm), (uint32_t)min(bm, T - j * bm), 0};
+    if (threadIdx.x == 0) ntiles[0] = (uint32_t)n;
+}
+
+// out[t, :] += sg[t] * ys[t, :] (the shared expert's contribution)
+__global__ void __launch_bounds__(256) shared_add_kernel(const void* __restrict__ ys, int32_t ys_dtype, const float* __restrict__ sg,
+                                                        void* __restrict__ out, int32_t out_dtype, int64_t ldo, int T, int D) {
+    const int t = blockIdx.x;
+    const float w = sg[t];
+    for (int d = threadIdx.x; d < D; d += 256) {
+        const float y = ys_dtype == kF32 ? reinterpret_cast<const float*>(ys)[(size_t)t * D + d]
+                                         : __half2float(reinterpret_cast<const __half*>(ys)[(size_t)t * D + d]);
+        const size_t o = (size_t)t * ldo + d;
+        if (out_dtype == kF32) reinterpret_cast<float*>(out)[o] += w * y;
+        else if (out_dtype == kF16) reinterpret_cast<__half*>(out)[o] = __float2half_rn(__half2float(reinterpret_cast<__half*>(out)[o]) + w * y);
+        else reinterpret_cast<uint16_t*>(out)[o] = (uint16_t)f32_to_bf16_bits(bf16_bits_to_f32(reinterpret_cast<uint16_t*>(out)[o]) + w * y);
+    }
+}
+
 // Unit-weight RMSNorm of fp32 rows (the layer-stack skeleton's input normalisation; Shaders/verify.metal:503-523 of
 // the reference): out = x / sqrt(mean(x^2) + eps), written as bf16 / fp16 / fp32. One block per row.
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x, int64_t ldx, void* __restrict__ out,

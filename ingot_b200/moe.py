@@ -42,7 +42,9 @@ class MoELayer:
                  act: str = "silu", limit: float = 7.0, router_scales: Optional[torch.Tensor] = None,
                  router_biases: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None,
                  up_bias: Optional[torch.Tensor] = None, down_bias: Optional[torch.Tensor] = None, expert_lo: int = 0,
-                 max_tokens: int = 16):
+                 max_tokens: int = 16, shared: Optional[tuple] = None, shared_gate: Optional[DenseQ] = None):
+        """shared: (gate, up, down) DenseQ of the shared expert (MoE.swift:140-154), with shared_gate the 8-bit [1, D]
+        tensor of its sigmoid gate, or None for weight 1."""
         _need_cuda(router_w, gate_bias, up_bias, down_bias, router.logit_bias, router.per_expert_scale, router.select_bias)
         self.router, self.gate, self.up, self.down = router, gate, up, down
         self.D, self.I = gate.K, gate.N
@@ -74,6 +76,13 @@ class MoELayer:
         d.router_score = capi.IQ_SCORE_SIGMOID if router.score == "sigmoid" else capi.IQ_SCORE_SOFTMAX
         d.route_eps = router.eps
         d.router_select_bias = ptr(router.select_bias)
+        self._shared = (shared, shared_gate)
+        d.shared = capi.IQ_SHARED_NONE
+        if shared is not None:
+            d.shared = capi.IQ_SHARED_UNGATED if shared_gate is None else capi.IQ_SHARED_GATED
+            d.shared_gate_proj, d.shared_up, d.shared_down = shared[0].qlinear(), shared[1].qlinear(), shared[2].qlinear()
+            if shared_gate is not None:
+                d.shared_gate = shared_gate.qlinear()
         self.ctx = capi.context(self.device.index or 0)
         self._h = C.c_void_p()
         self.ctx.check(capi.lib().iq_moe_create(self.ctx.handle, C.byref(d), C.byref(self._h)))

@@ -259,6 +259,22 @@ def moe_ffn(x: np.ndarray, inds: np.ndarray, wts: np.ndarray, expert_weights, *,
     return y.astype(np.float32)
 
 
+def shared_expert(x, gate, up, down, gate_w=None, *, act: str = "silu", round_h: bool = True):
+    """The shared expert's contribution (MoE.swift:140-154; verify.metal:262-281): w_s * down(half(act(gate x, up x))) with
+    w_s = sigmoid(x . gate_w) per token, or 1 without a gate tensor. gate/up [I_s, D], down [D, I_s], gate_w [D]."""
+    x = np.asarray(x, dtype=np.float32)
+    h = ACTS[act](matmul_t(x, gate), matmul_t(x, up))
+    if round_h:
+        h = round_f16(h)
+    y = matmul_t(h, down)
+    if gate_w is None:
+        return y
+    logit = (x.astype(np.float64) @ np.asarray(gate_w, dtype=np.float64)).astype(np.float32)
+    with np.errstate(over="ignore"):
+        w = (1.0 / (1.0 + np.exp(-logit.astype(np.float64)))).astype(np.float32)
+    return (w[:, None] * y).astype(np.float32)
+
+
 def moe_block(x, router_w, top_k, expert_weights, *, router_bias=None, **kw):
     """Router + MoE FFN: returns (y, inds, wts, logits). Equals ref/moe_ref.py:107-136 without its shared expert:
     softmax over all experts, top-k, renormalise == softmax over the top-k logits (the engine's form)."""

@@ -209,6 +209,32 @@ def test_moe_other_activations(cuda_device, act, T):
     check_layer(layer, host, synth.activations_np(rng, T, 2048), T, act)
 
 
+@pytest.mark.parametrize("gated", [True, False])
+@pytest.mark.parametrize("T", [1, 19, 300])
+def test_moe_shared_expert(cuda_device, T, gated):
+    """A shared expert of its own width beside the routed experts, with its 8-bit sigmoid gate or weight 1
+    (MoE.swift:140-154; KernelCaseMoE.swift:45-114): GEMV tiles for few tokens, the tcgen05 path for many."""
+    rng = np.random.default_rng(300 + T)
+    E, K, D, I, IS = 32, 4, 256, 128, 192
+    sg, su, sd = synth.affine_np(rng, IS, D, 4), synth.affine_np(rng, IS, D, 4), synth.affine_np(rng, D, IS, 4)
+    gw = synth.affine_np(rng, 1, D, 8)
+    mk = lambda t, bits: synth.dense_q_affine(t[0], t[1], t[2], bits, cuda_device)
+    g, u, d = synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, D, I, 4, E)
+    wr = synth.router_np(rng, E, D)
+    layer = MoELayer(RouterSpec(E, K), synth.bf16_values_tensor(wr, cuda_device), mk(g, 4), mk(u, 4), mk(d, 4), max_tokens=T,
+                     shared=(mk(sg, 4), mk(su, 4), mk(sd, 4)), shared_gate=mk(gw, 8) if gated else None)
+    x = synth.activations_np(rng, T, D)
+    out = torch.zeros(T, D, dtype=torch.float32, device=cuda_device)
+    layer.encode(x_tensor(x, cuda_device), out, T)
+    torch.cuda.synchronize()
+    assert capi.context(0).device_status() == 0
+    deq = lambda t, e=0, bits=4: qref.dequant_affine(t[0][e], t[1][e], t[2][e], bits)
+    inds, wts = qref.route(qref.router_logits(x, wr), K)
+    ref = qref.moe_ffn(x, inds, wts, lambda e: (deq(g, e), deq(u, e), deq(d, e)))
+    ref = ref + qref.shared_expert(x, deq(sg), deq(su), deq(sd), deq(gw, 0, 8)[0] if gated else None)
+    assert qref.max_rel(out.cpu().numpy(), ref) <= TOL
+
+
 def test_moe_load_guards(cuda_device):
     """Shapes the reference refuses at load (MoE.swift:186-219) come back as named errors."""
     rng = np.random.default_rng(3)
