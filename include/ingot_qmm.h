@@ -42,7 +42,10 @@ typedef enum iq_status {
     IQ_ERR_WORKSPACE = -4,   /* workspace missing or too small */
     IQ_ERR_NO_KERNEL = -5,
     IQ_ERR_TIMEOUT = -6, /* a bounded device-side wait gave up (status word written by the kernel) */
-    IQ_ERR_COMM = -7
+    IQ_ERR_COMM = -7,
+    IQ_ERR_IO = -8,      /* loader: a file could not be opened, mapped or read */
+    IQ_ERR_FORMAT = -9,  /* loader: not a safetensors file / inconsistent header */
+    IQ_ERR_MISSING = -10 /* loader: no such tensor */
 } iq_status;
 
 typedef enum iq_dtype { IQ_F32 = 0, IQ_F16 = 1, IQ_BF16 = 2 } iq_dtype;
@@ -294,6 +297,34 @@ int32_t iq_ep_return_rows(iq_ep* ep, void* stream, int32_t yd_dtype, int32_t d_m
  * with sources = 1, region_rows = 0. After iq_ep_barrier(then_plan = 1). */
 int32_t iq_ep_compact(iq_ep* ep, void* stream, const void* recv_rows, int32_t d_model, int32_t yd_dtype, void* rows_out,
                       void** table, const uint32_t** merged_counts);
+
+/* ---- weight loader (host only; no GPU needed) -------------------------------------------------------------------------
+ * One safetensors file mapped read-only with its header parsed into a tensor table: MappedFile + the per-shard part of
+ * SafetensorsStore (Loader/Safetensors.swift:46-148). `data` points into the mapping (it may be unaligned) and stays
+ * valid until iq_st_close. Directory / index.json handling, per-path quantization from config.json and the assembly of
+ * device layouts live in the host mirror (ingot_b200/loader.py), as they live in Swift in the reference. */
+typedef enum iq_st_dtype { IQ_ST_BF16 = 0, IQ_ST_F16 = 1, IQ_ST_F32 = 2, IQ_ST_U32 = 3, IQ_ST_I32 = 4, IQ_ST_U8 = 5 } iq_st_dtype;
+typedef struct iq_st iq_st;
+typedef struct iq_st_tensor {
+    const char* name;            /* owned by the file handle */
+    int32_t dtype;               /* iq_st_dtype */
+    int32_t rank;
+    int64_t shape[8];
+    uint64_t file_offset;        /* absolute offset in the file (header included) */
+    uint64_t bytes;
+    const unsigned char* data;   /* file_offset into the mapping */
+} iq_st_tensor;
+int32_t iq_st_open(const char* path, iq_st** out);
+void iq_st_close(iq_st* file);
+int32_t iq_st_count(const iq_st* file);
+int32_t iq_st_entry(const iq_st* file, int32_t index, iq_st_tensor* out);
+int32_t iq_st_find(const iq_st* file, const char* name, iq_st_tensor* out);
+const char* iq_st_last_error(void);  /* message of the calling thread's last failed iq_st_* call */
+/* Packed 4-bit words to 8-bit words with every value times 16 (source_words words in, twice as many out; src may be
+ * unaligned), and the matching bf16 scales divided by 16, which is exact: a 4-bit piece concatenated with 8-bit ones
+ * keeps its values bit for bit (widen4to8Words, Layers/Linear.swift:599-610, :170-175). */
+void iq_widen4to8_words(const void* src, void* dst, size_t source_words);
+void iq_scales_div16_bf16(const void* src, void* dst, size_t count);
 
 /* ---- layer-stack helper ----------------------------------------------------------------------------------------------
  * out = x / sqrt(mean(x^2) + eps) per row, unit weight: the input normalisation between the fp32 residual and an FFN

@@ -25,6 +25,8 @@ SYMBOLS = [
     "iq_moe_get_views", "iq_moe_pack_rows", "iq_moe_experts_workspace_bytes", "iq_moe_experts", "iq_moe_combine_rows",
     "iq_rmsnorm", "iq_qmm_noalloc", "iq_ep_create", "iq_ep_destroy", "iq_ep_share_counts", "iq_ep_barrier", "iq_ep_plan",
     "iq_ep_pack_push", "iq_ep_return_push", "iq_ep_return_rows", "iq_ep_compact",
+    "iq_st_open", "iq_st_close", "iq_st_count", "iq_st_entry", "iq_st_find", "iq_st_last_error", "iq_widen4to8_words",
+    "iq_scales_div16_bf16",
 ]
 
 
@@ -44,6 +46,11 @@ class MoeDesc(C.Structure):
                 ("router_score", C.c_int32), ("route_eps", C.c_float), ("router_select_bias", C.c_void_p),
                 ("shared", C.c_int32), ("shared_gate_proj", QLinear), ("shared_up", QLinear), ("shared_down", QLinear),
                 ("shared_gate", QLinear)]
+
+
+class StTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dtype", C.c_int32), ("rank", C.c_int32), ("shape", C.c_int64 * 8),
+                ("file_offset", C.c_uint64), ("bytes", C.c_uint64), ("data", C.c_void_p)]
 
 
 class MoeViews(C.Structure):
@@ -96,6 +103,20 @@ def lib() -> C.CDLL:
         l.iq_moe_get_views.argtypes = [vp, vp, i32, C.POINTER(MoeViews)]
         l.iq_qmm_noalloc.argtypes = [vp, vp, vp, i32, i64, C.POINTER(QLinear), vp, i32, i64, i32, u32]
         l.iq_qmm_noalloc.restype = i32
+        l.iq_st_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+        l.iq_st_close.argtypes = [vp]
+        l.iq_st_close.restype = None
+        l.iq_st_count.argtypes = [vp]
+        l.iq_st_entry.argtypes = [vp, i32, C.POINTER(StTensor)]
+        l.iq_st_find.argtypes = [vp, C.c_char_p, C.POINTER(StTensor)]
+        l.iq_st_last_error.argtypes = []
+        l.iq_st_last_error.restype = C.c_char_p
+        l.iq_widen4to8_words.argtypes = [vp, vp, sz]
+        l.iq_widen4to8_words.restype = None
+        l.iq_scales_div16_bf16.argtypes = [vp, vp, sz]
+        l.iq_scales_div16_bf16.restype = None
+        for name in ("iq_st_open", "iq_st_count", "iq_st_entry", "iq_st_find"):
+            getattr(l, name).restype = i32
         l.iq_ep_create.argtypes = [vp, i32, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]
         l.iq_ep_destroy.argtypes = [vp]
         l.iq_ep_destroy.restype = None
