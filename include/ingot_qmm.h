@@ -298,6 +298,19 @@ int32_t iq_ep_return_rows(iq_ep* ep, void* stream, int32_t yd_dtype, int32_t d_m
 int32_t iq_ep_compact(iq_ep* ep, void* stream, const void* recv_rows, int32_t d_model, int32_t yd_dtype, void* rows_out,
                       void** table, const uint32_t** merged_counts);
 
+/* ---- after the lm_head GEMV (decode) ----------------------------------------------------------------------------------
+ * out[r] = index of the largest of x[r, 0..n), ties to the lower index (argmax_rows, Shaders/verify.metal:525-547). */
+int32_t iq_argmax_rows(iq_ctx* ctx, void* stream, const float* x, int64_t ldx, int32_t rows, int32_t n, uint32_t* out);
+/* The 64 candidates of each row of logits the sampler works on (TopK64: topk64_part + topk64_merge, zz_sample.metal;
+ * contract in Tests/IngotTests/TopK64Tests.swift): idx / val [rows, 64] = the logits x >= -FLT_MAX ordered by value
+ * descending, ties to the lower id, padded with (0xFFFFFFFF, -FLT_MAX); val holds the logits' own bits; z[2r] = the
+ * row maximum, z[2r+1] = sum_i exp((x_i - max) / T_r). temperatures: host array of 1 value or one per row. 1..16 rows,
+ * up to 262,144 logits per row. */
+int32_t iq_topk64_scratch_bytes(int32_t rows, int32_t vocab, size_t* bytes);
+int32_t iq_topk64(iq_ctx* ctx, void* stream, const float* x, int64_t ldx, int32_t rows, int32_t vocab,
+                  const float* temperatures, int32_t n_temperatures, uint32_t* idx, float* val, float* z, void* scratch,
+                  size_t scratch_bytes);
+
 /* ---- weight loader (host only; no GPU needed) -------------------------------------------------------------------------
  * One safetensors file mapped read-only with its header parsed into a tensor table: MappedFile + the per-shard part of
  * SafetensorsStore (Loader/Safetensors.swift:46-148). `data` points into the mapping (it may be unaligned) and stays

@@ -302,3 +302,30 @@ def max_rel(got: np.ndarray, ref: np.ndarray) -> float:
     if np.isnan(got).any():
         return float("inf")
     return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# sampling candidates
+
+
+def topk64(row: np.ndarray, temperature: float, k: int = 64):
+    """The sampler's candidates of one row of logits (TopK64Tests.swift:44-63): the logits x >= -FLT_MAX by value
+    descending, ties to the lower id, padded with (0xFFFFFFFF, -FLT_MAX); the row maximum; Z = sum exp((x - max) / T)
+    in float64."""
+    row = np.asarray(row, dtype=np.float32)
+    fmax = np.float32(np.finfo(np.float32).max)
+    cand = np.nonzero(row >= -fmax)[0]
+    order = cand[np.lexsort((cand, -row[cand].astype(np.float64)))][:k]
+    ids = np.full(k, 0xFFFFFFFF, dtype=np.uint32)
+    vals = np.full(k, -fmax, dtype=np.float32)
+    ids[: len(order)] = order
+    vals[: len(order)] = row[order]
+    with np.errstate(invalid="ignore", over="ignore"):
+        mx = np.float32(np.nanmax(row)) if row.size else np.float32(-np.inf)
+        z = float(np.sum(np.exp((row.astype(np.float64) - float(mx)) / temperature)))
+    return ids, vals, mx, z
+
+
+def argmax_rows(x: np.ndarray) -> np.ndarray:
+    """Index of the largest value of each row, ties to the lower index (verify.metal:525-547)."""
+    return np.argmax(np.asarray(x, dtype=np.float32), axis=1).astype(np.uint32)
