@@ -144,15 +144,15 @@ __global__ void __launch_bounds__(256) ep_compact_kernel(const __half* __restric
                                                         PeerPtrs back, int D, int row_bytes_back, int world, int El,
                                                         uint32_t region_rows, __half* __restrict__ xc,
                                                         uint64_t* __restrict__ table) {
-    const uint32_t j = blockIdx.x * 4 + (threadIdx.x >> 6);
-    const int t = threadIdx.x & 63;
-    const uint32_t s = j / region_rows;
-    if ((int)s >= world) return;
     // rows past the total keep a zero in the table (j runs over the capacity; the total is small next to it)
     uint32_t total = 0;
     for (int q = 0; q < world; q++) total += plan->from[q];
+    const int t = threadIdx.x & 63;
+    // the capacity is many times what arrives: a fixed grid walks the row slots instead of one block per four slots
+    for (uint32_t j = blockIdx.x * 4 + (threadIdx.x >> 6); j < (uint32_t)world * region_rows; j += gridDim.x * 4) {
+    const uint32_t s = j / region_rows;
     if (j >= total && t == 0) table[j] = 0;
-    if (j - s * region_rows >= plan->from[s]) return;
+    if (j - s * region_rows >= plan->from[s]) continue;
     int lo = s * El, hi = (s + 1) * El;
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
@@ -171,6 +171,7 @@ __global__ void __launch_bounds__(256) ep_compact_kernel(const __half* __restric
         out[u] = a; out[u + 64] = b; out[u + 128] = c; out[u + 192] = d;
     }
     for (; u < n16; u += 64) out[u] = ldg_nc_u4(src + u);
+    }
 }
 
 // The same mapping as a table: table[j] = address, in the source rank's return buffer, of the output of received row j
@@ -353,7 +354,8 @@ extern "C" int32_t iq_ep_compact(iq_ep* ep, void* stream, const void* recv_rows,
         d_model % 8 != 0)
         return fail(ep->ctx, kErrInvalidArg, "ep_compact: arguments");
     const int64_t rows = (int64_t)ep->world * ep->region_rows;
-    ep_compact_kernel<<<(unsigned)((rows + 3) / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+    const int64_t want = (rows + 3) / 4, cap = (int64_t)ep->ctx->sms * 8;
+    ep_compact_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(recv_rows), ep->plan, ep->back, d_model, d_model * (yd_dtype == kF32 ? 4 : 2), ep->world,
         ep->experts / ep->world, (uint32_t)ep->region_rows, static_cast<__half*>(rows_out), reinterpret_cast<uint64_t*>(table));
     if (merged_counts != nullptr) *merged_counts = ep->plan->merged;

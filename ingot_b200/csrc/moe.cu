@@ -271,7 +271,8 @@ int32_t run_shared_expert(iq_moe* l, cudaStream_t cs, const void* x, int32_t x_d
 int32_t scatter_rows(iq_ctx* ctx, cudaStream_t cs, const void* yd, void* const* yd_rows, int max_rows, int d_model,
                      int32_t yd_dtype) {
     const int row_bytes = d_model * (yd_dtype == kF32 ? 4 : 2);
-    moe_scatter_rows_kernel<<<(max_rows + 3) / 4, 256, 0, cs>>>(yd, reinterpret_cast<const uint64_t*>(yd_rows), max_rows, row_bytes);
+    const int want = (max_rows + 3) / 4, cap = ctx->sms * 8;
+    moe_scatter_rows_kernel<<<want < cap ? want : cap, 256, 0, cs>>>(yd, reinterpret_cast<const uint64_t*>(yd_rows), max_rows, row_bytes);
     return check_cuda(ctx, cudaGetLastError(), "moe_scatter_rows launch");
 }
 

@@ -724,13 +724,14 @@ __global__ void __launch_bounds__(512) ep_tiles_kernel(const uint32_t* __restric
 // Four rows per block, 64 threads per row.
 __global__ void __launch_bounds__(256) moe_scatter_rows_kernel(const void* __restrict__ src, const uint64_t* __restrict__ row_ptr,
                                                               int rows, int row_bytes) {
-    const int r = blockIdx.x * 4 + (threadIdx.x >> 6);
-    if (r >= rows) return;
-    const uint64_t dptr = row_ptr[r];
-    if (dptr == 0) return;
-    const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(src) + (size_t)r * row_bytes);
-    uint4* d = reinterpret_cast<uint4*>(dptr);
-    for (int u = threadIdx.x & 63; u < row_bytes / 16; u += 64) d[u] = ldg_nc_u4(s + u);
+    // most slots are empty when the table is sized for the worst case: a fixed grid walks them
+    for (int r = blockIdx.x * 4 + (threadIdx.x >> 6); r < rows; r += gridDim.x * 4) {
+        const uint64_t dptr = row_ptr[r];
+        if (dptr == 0) continue;
+        const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(src) + (size_t)r * row_bytes);
+        uint4* d = reinterpret_cast<uint4*>(dptr);
+        for (int u = threadIdx.x & 63; u < row_bytes / 16; u += 64) d[u] = ldg_nc_u4(s + u);
+    }
 }
 
 // Shared expert: the per-token weight sigmoid(x . w) with w an 8-bit affine g64 row (verify.metal:262-277), or 1 without

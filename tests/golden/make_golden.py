@@ -50,7 +50,9 @@ def bf16_round(v: float) -> float:
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <checkout of the reference>")
+    ref = sys.argv[1]
     tests = os.path.join(ref, "Tests", "IngotTests")
 
     # --- MXFP4 ---------------------------------------------------------------------------------------------
