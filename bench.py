@@ -333,9 +333,10 @@ def run_ours(args):
 
     # the dominant kernel of the prefill stack: the experts' gate+up GEMM; timed alone over the layers (rank 0's share)
     roof = None
-    # kernels per layer: norm, router, top-k, count, scatter, pack, gate/up, down, combine; expert-parallel: norm, router,
-    # top-k, count, scatter, pack+push, barrier(+plan), compact, tile list, gate/up, down(+return), barrier, combine
-    launches_per_layer = 9 if world == 1 else 13
+    # kernels per layer: norm, router, top-k, histogram, scan, place, pack, gate/up, down, combine; expert-parallel: norm,
+    # router, top-k, histogram, scan, place, pack+push, barrier(+plan), compact, tile list, gate/up, down, return, barrier,
+    # combine
+    launches_per_layer = 10 if world == 1 else 15
     if world == 1:
         xn = stack.xn
 
