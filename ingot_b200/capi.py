@@ -26,7 +26,7 @@ SYMBOLS = [
     "iq_rmsnorm", "iq_qmm_noalloc", "iq_ep_create", "iq_ep_destroy", "iq_ep_share_counts", "iq_ep_barrier", "iq_ep_plan",
     "iq_ep_pack_push", "iq_ep_return_push", "iq_ep_return_rows", "iq_ep_compact",
     "iq_st_open", "iq_st_close", "iq_st_count", "iq_st_entry", "iq_st_find", "iq_st_last_error", "iq_widen4to8_words",
-    "iq_scales_div16_bf16", "iq_argmax_rows", "iq_topk64_scratch_bytes", "iq_topk64",
+    "iq_scales_div16_bf16", "iq_argmax_rows", "iq_topk64_scratch_bytes", "iq_topk64", "iq_embed_rows",
 ]
 
 
@@ -106,7 +106,8 @@ def lib() -> C.CDLL:
         l.iq_argmax_rows.argtypes = [vp, vp, vp, i64, i32, i32, vp]
         l.iq_topk64_scratch_bytes.argtypes = [i32, i32, C.POINTER(sz)]
         l.iq_topk64.argtypes = [vp, vp, vp, i64, i32, i32, C.POINTER(C.c_float), i32, vp, vp, vp, vp, sz]
-        for name in ("iq_argmax_rows", "iq_topk64_scratch_bytes", "iq_topk64"):
+        l.iq_embed_rows.argtypes = [vp, vp, C.POINTER(QLinear), vp, i32, vp, vp, i64]
+        for name in ("iq_argmax_rows", "iq_topk64_scratch_bytes", "iq_topk64", "iq_embed_rows"):
             getattr(l, name).restype = i32
         l.iq_st_open.argtypes = [C.c_char_p, C.POINTER(vp)]
         l.iq_st_close.argtypes = [vp]

@@ -74,6 +74,11 @@ struct FmtTraits<kFmtAffine8> {
     static constexpr bool PERM = false, BIAS = true;
 };
 template <>
+struct FmtTraits<kFmtAffine4G32> {  // one scale and bias per 16-byte chunk
+    static constexpr int CK = 32, QU = 4, CPG = 1, GROUP = 32;
+    static constexpr bool PERM = true, BIAS = true;
+};
+template <>
 struct FmtTraits<kFmtMxfp4> {
     static constexpr int CK = 32, QU = 4, CPG = 1, GROUP = 32;
     static constexpr bool PERM = false, BIAS = false;
@@ -134,7 +139,7 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t magic_plus_v, uint32_t s2, 
 // 4-bit / mxfp4: two MMAs (k-slot pairs p[0], p[1] then p[2], p[3]); 8-bit: one MMA (p[0], p[1]).
 template <int FMT>
 __device__ __forceinline__ void dequant_word(uint32_t w, const DqConst& d, uint32_t (&p)[4]) {
-    if (FMT == kFmtAffine4) {
+    if (FMT == kFmtAffine4 || FMT == kFmtAffine4G32) {
         const uint32_t w8 = w >> 8;
         p[0] = dq_pair((w & 0x000F000Fu) | 0x64006400u, d.s2, d.b2);    // (n0, n4)
         p[1] = dq_pair((w & 0x00F000F0u) | 0x64006400u, d.s16, d.b2);   // (n1, n5): the codes sit 16x up

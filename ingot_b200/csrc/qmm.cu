@@ -31,6 +31,7 @@ const KernelEntry* table(int* n) {
         entry<kFmtAffine4, 256, kEpiStore>(), entry<kFmtAffine4, 128, kEpiStore>(),
         entry<kFmtAffine8, 256, kEpiStore>(), entry<kFmtAffine8, 128, kEpiStore>(),
         entry<kFmtMxfp4, 256, kEpiStore>(),   entry<kFmtMxfp4, 128, kEpiStore>(),
+        entry<kFmtAffine4G32, 256, kEpiStore>(), entry<kFmtAffine4G32, 128, kEpiStore>(),
         entry<kFmtAffine4, 128, kEpiGateUp>(), entry<kFmtMxfp4, 128, kEpiGateUp>(),
         entry<kFmtAffine4, 256, kEpiGateUp>(), entry<kFmtMxfp4, 256, kEpiGateUp>(),
         entry<kFmtAffine4, 128, kEpiGateUp, kActSwigluOai>(), entry<kFmtMxfp4, 128, kEpiGateUp, kActSwigluOai>(),
@@ -138,7 +139,7 @@ extern "C" int32_t iq_qmm(iq_ctx* ctx, void* stream, const void* x, int32_t x_dt
         return fail(ctx, kErrInvalidArg, "qmm: null pointer");
     const int32_t fmt = format_of(m);
     if (fmt < 0)
-        return fail(ctx, kErrUnsupported, "qmm: %d-bit group %d mode %d has no kernel (affine 4/8-bit g64, mxfp4 g32)",
+        return fail(ctx, kErrUnsupported, "qmm: %d-bit group %d mode %d has no kernel (affine 4/8-bit g64, 4-bit g32, mxfp4 g32)",
                     m->bits, m->group, m->mode);
     if (fmt != kFmtMxfp4 && m->biases == nullptr) return fail(ctx, kErrInvalidArg, "qmm: affine layer without biases");
     // the reference's preconditions (Layers/Linear.swift:695)

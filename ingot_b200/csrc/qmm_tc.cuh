@@ -76,7 +76,7 @@ template <int FMT>
 __device__ __forceinline__ void dequant32(uint32_t packed_row_half, uint32_t sc_raw, uint32_t bi_raw, uint4 (&out)[4]) {
     // packed_row_half: shared-memory address (explicit shared-space loads: a generic load here costs the long latency
     // path and showed up as the dequantisers' main stall)
-    if (FMT == kFmtAffine4) {
+    if (FMT == kFmtAffine4 || FMT == kFmtAffine4G32) {
         const uint4 v = lds128(packed_row_half);
         const float s = bf16_bits_to_f32(sc_raw), b = bf16_bits_to_f32(bi_raw);
         const uint32_t s2 = pack_half2(s, s * 0.0625f), b2 = pack_half2(b, b);
@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
         total_work = m_tiles * n_tiles_n;
     }
     const int ksteps = p.K / kBK;
-    const int row_groups = p.K / (FMT == kFmtMxfp4 ? 32 : 64);
+    const int row_groups = p.K / ((FMT == kFmtMxfp4 || FMT == kFmtAffine4G32) ? 32 : 64);
 
     // Decodes work item `wi` into (expert, first token row, live token rows, first weight row).
     auto decode = [&](int wi, uint32_t& expert, int& row0, int& rows, int& n0) {
@@ -335,7 +335,9 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
         const int row = dt & 127;                 // weight row inside the tile
         const int sw = row & 7;
         bool ok = true;
-        struct SB { uint32_t sc[NWT][2], bi[NWT]; };   // mxfp4: two scale bytes per step, affine: one scale and bias
+        // mxfp4: two scale bytes per step; affine g64: one scale and bias; affine g32: two of each
+        constexpr int NB = FMT == kFmtAffine4G32 ? 2 : 1;
+        struct SB { uint32_t sc[NWT][2], bi[NWT][NB]; };
         struct Cursor { int wi, ks; uint32_t lin; size_t srow; bool live; };
         auto locate = [&](Cursor& c) {  // srow / live of the item c.wi
             c.live = false;
@@ -362,10 +364,16 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                     const unsigned char* sp = reinterpret_cast<const unsigned char*>(p.s[wt]) + c.srow + 2 * c.ks;
                     v.sc[wt][0] = live ? ldg_nc_u8_early(sp) : 127u;
                     v.sc[wt][1] = live ? ldg_nc_u8_early(sp + 1) : 127u;
-                    v.bi[wt] = 0;
+                    v.bi[wt][0] = 0;
+                } else if (FMT == kFmtAffine4G32) {
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        v.sc[wt][h] = live ? ldg_nc_u16_early(reinterpret_cast<const uint16_t*>(p.s[wt]) + c.srow + 2 * c.ks + h) : 0u;
+                        v.bi[wt][h % NB] = live ? ldg_nc_u16_early(reinterpret_cast<const uint16_t*>(p.b[wt]) + c.srow + 2 * c.ks + h) : 0u;
+                    }
                 } else {
                     v.sc[wt][0] = v.sc[wt][1] = live ? ldg_nc_u16_early(reinterpret_cast<const uint16_t*>(p.s[wt]) + c.srow + c.ks) : 0u;
-                    v.bi[wt] = live ? ldg_nc_u16_early(reinterpret_cast<const uint16_t*>(p.b[wt]) + c.srow + c.ks) : 0u;
+                    v.bi[wt][0] = live ? ldg_nc_u16_early(reinterpret_cast<const uint16_t*>(p.b[wt]) + c.srow + c.ks) : 0u;
                 }
             }
         };
@@ -383,7 +391,7 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                     const uint32_t pk = st + S::X_BYTES + NWT * S::WD_BYTES + wt * S::WP_BYTES + row * S::PACK_ROW +
                                         half * (S::PACK_ROW / 2);
                     uint4 o[4];
-                    dequant32<FMT>(pk, v.sc[wt][half], v.bi[wt], o);
+                    dequant32<FMT>(pk, v.sc[wt][half], v.bi[wt][half % NB], o);
 #pragma unroll
                     for (int j = 0; j < 4; j++) sts128(wd + (((half * 4 + j) ^ sw) << 4), o[j]);
                 }

@@ -51,6 +51,7 @@ GqmvKernel pick(int32_t fmt, int mh, int mode, int wk) {
         case kFmtAffine4: return pick_mh<kFmtAffine4>(mh, mode, wk);
         case kFmtAffine8: return pick_mh<kFmtAffine8>(mh, mode, wk);
         case kFmtMxfp4: return pick_mh<kFmtMxfp4>(mh, mode, wk);
+        case kFmtAffine4G32: return pick_mh<kFmtAffine4G32>(mh, mode, wk);
         default: return nullptr;
     }
 }
@@ -84,6 +85,7 @@ int g_qi_ctas = 2;  // INGOT_QMV_CTAS=1: one CTA per SM with a deeper ring (meas
 
 // Returns kOk after a launch, 1 when the shape does not fit this path (the caller falls back), or an error.
 int32_t launch_qmv_stream(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
+    if (c.fmt == kFmtAffine4G32) return 1;  // groups of 32: the register-staged kernel only
     const bool has_bias = c.fmt != kFmtMxfp4;
     const int nw = c.mode == kModeGateUp ? 2 : 1;
     const int mh = c.max_rows > 8 ? 2 : 1;
@@ -353,7 +355,7 @@ int32_t gqmv_init(iq_ctx* ctx) {
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kQsSmemMax);
             if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_imma_grouped)");
         }
-    for (int fmt = 0; fmt < 3; fmt++)
+    for (int fmt = 0; fmt < 4; fmt++)
         for (int mh = 1; mh <= 2; mh++)
             for (int mode = 0; mode < 3; mode++)
                 for (int wk = 2; wk <= 8; wk *= 2) {
@@ -441,7 +443,9 @@ int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
 
 int32_t format_of(const iq_qlinear* m) {
     if (m->mode == IQ_MODE_MXFP4) return (m->bits == 4 && m->group == 32) ? kFmtMxfp4 : -1;
-    if (m->mode != IQ_MODE_AFFINE || m->group != 64) return -1;
+    if (m->mode != IQ_MODE_AFFINE) return -1;
+    if (m->group == 32) return m->bits == 4 ? kFmtAffine4G32 : -1;
+    if (m->group != 64) return -1;
     if (m->bits == 4) return kFmtAffine4;
     if (m->bits == 8) return kFmtAffine8;
     return -1;
@@ -458,7 +462,7 @@ extern "C" int32_t iq_qmv(iq_ctx* ctx, void* stream, const void* x, int32_t x_dt
         return fail(ctx, kErrInvalidArg, "qmv: null pointer");
     const int32_t fmt = format_of(m);
     if (fmt < 0)
-        return fail(ctx, kErrUnsupported, "qmv: %d-bit group %d mode %d has no kernel (affine 4/8-bit g64, mxfp4 g32)",
+        return fail(ctx, kErrUnsupported, "qmv: %d-bit group %d mode %d has no kernel (affine 4/8-bit g64, 4-bit g32, mxfp4 g32)",
                     m->bits, m->group, m->mode);
     if (fmt != kFmtMxfp4 && m->biases == nullptr) return fail(ctx, kErrInvalidArg, "qmv: affine layer without biases");
     if (rows < 1 || rows > 16) return fail(ctx, kErrInvalidArg, "qmv: rows = %d (1..16)", rows);

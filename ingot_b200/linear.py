@@ -42,6 +42,14 @@ class DenseQ:
 
     def __init__(self, w: torch.Tensor, scales: torch.Tensor, biases: Optional[torch.Tensor], N: int, K: int, bits: int,
                  gs: int = 64, mode: str = "affine", experts: int = 1):
+        if bits == 16:
+            # a plain bf16 table (an unquantized embedding, Linear.swift:58-63): only encode_embed takes it
+            _need_cuda(w)
+            if w.dtype != torch.bfloat16 or w.numel() != N * K or scales is not None or biases is not None:
+                raise ValueError("a 16-bit table is bf16 [N, K] without scales or biases")
+            self.w, self.s, self.b = w.contiguous(), None, None
+            self.N, self.K, self.bits, self.gs, self.mode, self.experts = N, K, 16, 64, "affine", 1
+            return
         _need_cuda(w, scales, biases)
         if mode not in ("affine", "mxfp4"):
             raise ValueError(f"quantization mode «{mode}» not supported (affine and mxfp4)")
@@ -64,7 +72,8 @@ class DenseQ:
         self.N, self.K, self.bits, self.gs, self.mode, self.experts = N, K, bits, gs, mode, experts
 
     def qlinear(self) -> capi.QLinear:
-        return capi.QLinear(self.w.data_ptr(), self.s.data_ptr(), 0 if self.b is None else self.b.data_ptr(), self.N,
+        return capi.QLinear(self.w.data_ptr(), 0 if self.s is None else self.s.data_ptr(),
+                            0 if self.b is None else self.b.data_ptr(), self.N,
                             self.K, self.bits, self.gs, capi.IQ_MODE_MXFP4 if self.mode == "mxfp4" else capi.IQ_MODE_AFFINE,
                             self.experts)
 
@@ -74,8 +83,29 @@ class DenseQ:
 
     def weight_bytes(self) -> int:
         """Bytes of codes + scales + biases (what one pass over the matrix reads)."""
-        n = self.w.numel() * 4 + self.s.numel() * self.s.element_size()
+        n = self.w.numel() * self.w.element_size() + (0 if self.s is None else self.s.numel() * self.s.element_size())
         return n + (0 if self.b is None else self.b.numel() * 2)
+
+    # ---- embedding (Linear.swift:65-93) -------------------------------------------------------------------------
+    def encode_embed(self, tok: torch.Tensor, rows: int, out_f: Optional[torch.Tensor] = None,
+                     out_h: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None):
+        """Rows tok[r] of the table, dequantised, into out_f (float32 [rows, >=K]) and / or out_h (float16): affine
+        4-bit (groups of 64 or 32), 8-bit, or a bf16 table. tok is an int32/uint32 device tensor."""
+        _need_cuda(tok, out_f, out_h)
+        if tok.dtype not in (torch.int32, torch.uint32) or tok.numel() < rows:
+            raise TypeError("tokens are 32-bit integers, one per row")
+        if out_f is None and out_h is None:
+            raise ValueError("one of out_f, out_h is needed")
+        if (out_f is not None and out_f.dtype != torch.float32) or (out_h is not None and out_h.dtype != torch.float16):
+            raise TypeError("out_f is float32, out_h float16")
+        if out_f is not None and out_h is not None and out_f.stride(0) != out_h.stride(0):
+            raise ValueError("out_f and out_h share one row stride")
+        o = out_f if out_f is not None else out_h
+        ctx = capi.context(self.device_index)
+        q = self.qlinear()
+        ctx.check(capi.lib().iq_embed_rows(ctx.handle, _stream_ptr(stream), C.byref(q), tok.data_ptr(), rows,
+                                           0 if out_f is None else out_f.data_ptr(),
+                                           0 if out_h is None else out_h.data_ptr(), o.stride(0)))
 
     # ---- prefill GEMM (Linear.swift:688-713) --------------------------------------------------------------------
     def qmm_workspace_bytes(self, rows: int, x_dtype: torch.dtype) -> int:
