@@ -72,7 +72,7 @@ typedef struct iq_qlinear {
     const void* biases; /* NULL for mxfp4 */
     int32_t n;          /* output features (rows of W) */
     int32_t k;          /* input features */
-    int32_t bits;       /* 4 or 8 */
+    int32_t bits;       /* 4 or 8; 6 for the decode GEMV (k a multiple of 2048) and the embedding */
     int32_t group;      /* 64 (affine; 32 also for the 4-bit decode GEMV and the embedding) or 32 (mxfp4) */
     int32_t mode;       /* iq_mode */
     int32_t experts;    /* leading dimension, 1 for a plain layer */
@@ -301,8 +301,9 @@ int32_t iq_ep_compact(iq_ep* ep, void* stream, const void* recv_rows, int32_t d_
 /* ---- before the first layer -------------------------------------------------------------------------------------------
  * Embedding gather: row tokens[r] of the table, dequantised as float(scale) * code + float(bias) in fp32, into out_f32
  * [rows, ldo] and / or its fp16 rounding out_f16 [rows, ldo] (either may be NULL). Replaces embed_rows, embed_rows_g32,
- * embed_rows_b8 and embed_rows_bf16 (Shaders/yy_model.metal:12-95; bit-exact check in KernelCaseG32.swift:80-93).
- * table: affine 4-bit (group 64 or 32) or 8-bit (group 64); bits = 16 is a plain bf16 table (scales and biases unused).
+ * embed_rows_b6, embed_rows_b8 and embed_rows_bf16 (Shaders/yy_model.metal:12-95, Shaders/yw_lfm.metal; bit-exact check in KernelCaseG32.swift:80-93).
+ * table: affine 4-bit (group 64 or 32), 6-bit or 8-bit (group 64); bits = 16 is a plain bf16 table (scales and biases
+ * unused).
  * tokens is a device array; a token >= table->n gives a zero row. */
 int32_t iq_embed_rows(iq_ctx* ctx, void* stream, const iq_qlinear* table, const uint32_t* tokens, int32_t rows,
                       float* out_f32, void* out_f16, int64_t ldo);

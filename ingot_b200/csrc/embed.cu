@@ -2,7 +2,8 @@
 // its fp16 copy. HBM-bound: one CTA per output row, each thread turns one 16-byte piece of the row's codes into 32
 // (4-bit) or 16 (8-bit) values and writes them with 16-byte stores.
 //
-// Replaces embed_rows / embed_rows_g32 / embed_rows_b8 / embed_rows_bf16 (Shaders/yy_model.metal:12-95 of the reference;
+// Replaces embed_rows / embed_rows_g32 / embed_rows_b6 / embed_rows_b8 / embed_rows_bf16 (Shaders/yy_model.metal:12-95,
+// Shaders/yw_lfm.metal of the reference;
 // its check is bit-exact against the dequantised table, Tests/IngotTests/KernelCaseG32.swift:80-93): the value is
 // float(scale) * float(code) + float(bias) in fp32 (the product of a bf16 and a code of at most 8 bits is exact, so a
 // fused and an unfused evaluation agree), the fp16 output its round-to-nearest.
@@ -33,6 +34,35 @@ __device__ __forceinline__ void store8(const EmbedParams& p, size_t at, const fl
         h.x = pack_half2(v[0], v[1]); h.y = pack_half2(v[2], v[3]);
         h.z = pack_half2(v[4], v[5]); h.w = pack_half2(v[6], v[7]);
         *reinterpret_cast<uint4*>(p.oh + at) = h;
+    }
+}
+
+// 6-bit codes (a little-endian bit stream, code j in bits 6j.. of the row; embed_rows_b6 of the reference): one thread
+// per three words = sixteen values.
+__global__ void __launch_bounds__(256) embed_rows6_kernel(const EmbedParams p) {
+    const int row = blockIdx.x;
+    const uint32_t t = p.tokens[row];
+    const bool live = t < (uint32_t)p.vocab;
+    const uint32_t* wr = p.w + (size_t)(live ? t : 0) * (p.K / 16 * 3);
+    const size_t g0 = (size_t)(live ? t : 0) * (p.K / 64);
+    for (int i = threadIdx.x; i < p.K / 16; i += blockDim.x) {
+        const uint32_t w0 = live ? __ldg(wr + 3 * i) : 0u, w1 = live ? __ldg(wr + 3 * i + 1) : 0u;
+        const uint32_t w2 = live ? __ldg(wr + 3 * i + 2) : 0u;
+        const unsigned long long lo = ((unsigned long long)w1 << 32) | w0;  // codes 0..9 and the low bits of code 10
+        const unsigned long long hi = ((unsigned long long)w2 << 28) | (w1 >> 4);  // from bit 36 = code 6 on
+        const float sc = live ? bf16_bits_to_f32(p.s[g0 + i / 4]) : 0.f;
+        const float bi = live ? bf16_bits_to_f32(p.b[g0 + i / 4]) : 0.f;
+        float v[16];
+#pragma unroll
+        for (int e = 0; e < 16; e++) {
+            const uint32_t q = e < 6 ? (uint32_t)(lo >> (6 * e)) & 63u : (uint32_t)(hi >> (6 * (e - 6))) & 63u;
+            v[e] = fmaf(sc, (float)q, bi);
+        }
+        const size_t at = (size_t)row * p.ldo + (size_t)i * 16;
+        const float (&va)[8] = *reinterpret_cast<const float (*)[8]>(v);
+        const float (&vb)[8] = *reinterpret_cast<const float (*)[8]>(v + 8);
+        store8(p, at, va);
+        store8(p, at + 8, vb);
     }
 }
 
@@ -101,8 +131,8 @@ extern "C" int32_t iq_embed_rows(iq_ctx* ctx, void* stream, const iq_qlinear* ta
     const bool plain = table->bits == 16;
     if (!plain) {
         if (table->mode != IQ_MODE_AFFINE || !((table->bits == 4 && (table->group == 64 || table->group == 32)) ||
-                                               (table->bits == 8 && table->group == 64)))
-            return fail(ctx, kErrUnsupported, "embed_rows: %d-bit group %d mode %d (affine 4-bit g64/g32, 8-bit g64, or bf16)",
+                                               ((table->bits == 8 || table->bits == 6) && table->group == 64)))
+            return fail(ctx, kErrUnsupported, "embed_rows: %d-bit group %d mode %d (affine 4-bit g64/g32, 6/8-bit g64, or bf16)",
                         table->bits, table->group, table->mode);
         if (table->scales == nullptr || table->biases == nullptr) return fail(ctx, kErrInvalidArg, "embed_rows: scales/biases");
     }
@@ -118,6 +148,7 @@ extern "C" int32_t iq_embed_rows(iq_ctx* ctx, void* stream, const iq_qlinear* ta
     cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
     if (plain) embed_rows_kernel<16><<<rows, 256, 0, cs>>>(p);
     else if (table->bits == 4) embed_rows_kernel<4><<<rows, 256, 0, cs>>>(p);
+    else if (table->bits == 6) embed_rows6_kernel<<<rows, 256, 0, cs>>>(p);
     else embed_rows_kernel<8><<<rows, 256, 0, cs>>>(p);
     return check_cuda(ctx, cudaGetLastError(), "embed_rows launch");
 }

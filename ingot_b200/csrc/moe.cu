@@ -407,7 +407,7 @@ extern "C" int32_t iq_moe_create(iq_ctx* ctx, const iq_moe_desc* d, iq_moe** out
     if (d->router_w == nullptr || (d->router_kind == IQ_ROUTER_Q8 && (!d->router_scales || !d->router_biases)))
         return fail(ctx, kErrInvalidArg, "moe: router tensors missing");
     const int32_t fg = format_of(&d->gate), fu = format_of(&d->up), fd = format_of(&d->down);
-    if (fg < 0 || fg != fu || fg != fd || fg == kFmtAffine8 || fg == kFmtAffine4G32)
+    if (fg != fu || fg != fd || (fg != kFmtAffine4 && fg != kFmtMxfp4))
         return fail(ctx, kErrUnsupported, "moe: experts must be all affine 4-bit g64 or all mxfp4");
     if (d->gate.n != d->d_ff || d->gate.k != d->d_model || d->up.n != d->d_ff || d->up.k != d->d_model ||
         d->down.n != d->d_model || d->down.k != d->d_ff)

@@ -138,7 +138,7 @@ extern "C" int32_t iq_qmm(iq_ctx* ctx, void* stream, const void* x, int32_t x_dt
     if (x == nullptr || y == nullptr || m == nullptr || m->w == nullptr || m->scales == nullptr)
         return fail(ctx, kErrInvalidArg, "qmm: null pointer");
     const int32_t fmt = format_of(m);
-    if (fmt < 0)
+    if (fmt < 0 || fmt == kFmtAffine6)
         return fail(ctx, kErrUnsupported, "qmm: %d-bit group %d mode %d has no kernel (affine 4/8-bit g64, 4-bit g32, mxfp4 g32)",
                     m->bits, m->group, m->mode);
     if (fmt != kFmtMxfp4 && m->biases == nullptr) return fail(ctx, kErrInvalidArg, "qmm: affine layer without biases");

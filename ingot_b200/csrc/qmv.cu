@@ -85,7 +85,7 @@ int g_qi_ctas = 2;  // INGOT_QMV_CTAS=1: one CTA per SM with a deeper ring (meas
 
 // Returns kOk after a launch, 1 when the shape does not fit this path (the caller falls back), or an error.
 int32_t launch_qmv_stream(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
-    if (c.fmt == kFmtAffine4G32) return 1;  // groups of 32: the register-staged kernel only
+    if (c.fmt == kFmtAffine4G32 || c.fmt == kFmtAffine6) return 1;  // not this kernel's formats
     const bool has_bias = c.fmt != kFmtMxfp4;
     const int nw = c.mode == kModeGateUp ? 2 : 1;
     const int mh = c.max_rows > 8 ? 2 : 1;
@@ -165,17 +165,18 @@ int32_t launch_qmv_stream(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
 // Returns kOk after a launch, 1 when the shape does not fit this path (the caller falls back), or an error.
 int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     if (c.mode != kModePlain || c.tiles != nullptr || c.rows > 16 || c.rows < 1) return 1;
-    if (c.fmt != kFmtAffine4 && c.fmt != kFmtAffine8) return 1;
+    if (c.fmt != kFmtAffine4 && c.fmt != kFmtAffine8 && c.fmt != kFmtAffine6) return 1;
     if (c.K % 2048 != 0 || c.N < kQiRows) return 1;
     if ((reinterpret_cast<uintptr_t>(c.w[0]) & 15) || (reinterpret_cast<uintptr_t>(c.s[0]) & 15) ||
         (reinterpret_cast<uintptr_t>(c.b[0]) & 15))
         return 1;
-    const bool w8 = c.fmt == kFmtAffine8;
+    const bool w8 = c.fmt == kFmtAffine8, w6 = c.fmt == kFmtAffine6;
     const int G = c.K / 64;
     QiParams p;
     memset(&p, 0, sizeof(p));
-    p.row_bytes = w8 ? c.K : c.K / 2;
-    p.row_pitch = p.row_bytes + (w8 ? 64 : 32);  // rows land in different banks for the fragment loads
+    p.row_bytes = w8 ? c.K : (w6 ? c.K / 4 * 3 : c.K / 2);
+    // rows land in different banks for the fragment loads: a lane's piece is 16, 12 or 8 bytes, a quad's 64, 48 or 32
+    p.row_pitch = p.row_bytes + (w8 ? 64 : (w6 ? 48 : 32));
     p.srow_bytes = G * 2;
     p.srow_pitch = p.srow_bytes;
     p.stage_bytes = kQiRows * p.row_pitch + 2 * kQiRows * p.srow_pitch;
@@ -244,7 +245,9 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
         // up to four rows and eight groups per warp (K = 4096): the activation fragments stay in registers
         const bool hoist = ms == 1 && G / ncw == 8;
         cudaError_t e;
-        if (w8) e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 2, 0>, p)
+        if (w6) e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine6, 2, 0>, p)
+                            : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine6, 1, 0>, p);
+        else if (w8) e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 2, 0>, p)
                             : (hoist ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 1, 8>, p)
                                      : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 1, 0>, p));
         else e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 2, 0>, p)
@@ -339,13 +342,15 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
 }  // namespace
 
 int32_t gqmv_init(iq_ctx* ctx) {
-    const void* qi[6] = {reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 1, 0>),
+    const void* qi[8] = {reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine6, 1, 0>),
+                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine6, 2, 0>),
+                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 1, 0>),
                          reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 1, 8>),
                          reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 2, 0>),
                          reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 1, 0>),
                          reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 1, 8>),
                          reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 2, 0>)};
-    for (int i = 0; i < 6; i++) {
+    for (int i = 0; i < 8; i++) {
         cudaError_t e = cudaFuncSetAttribute(qi[i], cudaFuncAttributeMaxDynamicSharedMemorySize, kQsSmemMax);
         if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_imma)");
     }
@@ -388,6 +393,8 @@ int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
         const int32_t r = launch_qmv_stream(ctx, st, c);
         if (r != 1) return r;
     }
+    if (c.fmt == kFmtAffine6)
+        return fail(ctx, kErrUnsupported, "qmv: 6-bit weights run on the int8 kernel only (a plain GEMV, k a multiple of 2048, n >= 16)");
     const int ck = c.fmt == kFmtAffine8 ? 16 : 32;  // inputs per 16-byte chunk
     const int mh = c.max_rows > 8 ? 2 : 1;
     const int nw = c.mode == kModeGateUp ? 2 : 1;
@@ -446,6 +453,7 @@ int32_t format_of(const iq_qlinear* m) {
     if (m->mode != IQ_MODE_AFFINE) return -1;
     if (m->group == 32) return m->bits == 4 ? kFmtAffine4G32 : -1;
     if (m->group != 64) return -1;
+    if (m->bits == 6) return kFmtAffine6;
     if (m->bits == 4) return kFmtAffine4;
     if (m->bits == 8) return kFmtAffine8;
     return -1;
@@ -462,7 +470,7 @@ extern "C" int32_t iq_qmv(iq_ctx* ctx, void* stream, const void* x, int32_t x_dt
         return fail(ctx, kErrInvalidArg, "qmv: null pointer");
     const int32_t fmt = format_of(m);
     if (fmt < 0)
-        return fail(ctx, kErrUnsupported, "qmv: %d-bit group %d mode %d has no kernel (affine 4/8-bit g64, 4-bit g32, mxfp4 g32)",
+        return fail(ctx, kErrUnsupported, "qmv: %d-bit group %d mode %d has no kernel (affine 4/6/8-bit g64, 4-bit g32, mxfp4 g32)",
                     m->bits, m->group, m->mode);
     if (fmt != kFmtMxfp4 && m->biases == nullptr) return fail(ctx, kErrInvalidArg, "qmv: affine layer without biases");
     if (rows < 1 || rows > 16) return fail(ctx, kErrInvalidArg, "qmv: rows = %d (1..16)", rows);

@@ -1,5 +1,5 @@
 // Decode GEMV on the int8 tensor-core path: y[m, n] = sum_k x[m, k] * (s[n, g] * q[n, k] + b[n, g]) for up to eight
-// activation rows per launch (the host cuts 9..16 rows into two launches) and affine 4- or 8-bit weights.
+// activation rows per launch (the host cuts 9..16 rows into two launches) and affine 4-, 6- or 8-bit weights.
 //
 // Why integers. The fp16 formulation converts every code to a half (several ALU instructions per code) before the MMA
 // and ends up bound by instruction issue at a third of the memory roofline. Here the codes go into the MMA as they
@@ -81,6 +81,11 @@ __device__ __forceinline__ uint4 lds128_after(uint32_t addr, uint32_t token) {
     asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4]; // %5" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "r"(token));
     return v;
 }
+__device__ __forceinline__ uint32_t lds32_after(uint32_t addr, uint32_t token) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1]; // %2" : "=r"(v) : "r"(addr), "r"(token));
+    return v;
+}
 __device__ __forceinline__ uint32_t lds_u16_after(uint32_t addr, uint32_t token) {
     uint32_t v;
     asm("ld.shared.u16 %0, [%1]; // %2" : "=r"(v) : "r"(addr), "r"(token));
@@ -90,6 +95,19 @@ __device__ __forceinline__ float2 lds64f_after(uint32_t addr, uint32_t token) {
     float2 v;
     asm("ld.shared.v2.f32 {%0,%1}, [%2]; // %3" : "=f"(v.x), "=f"(v.y) : "r"(addr), "r"(token));
     return v;
+}
+
+// Four 6-bit codes in the low 24 bits of v (whatever sits above them) -> one code per byte.
+__device__ __forceinline__ uint32_t spread6(uint32_t v) {
+    const uint32_t y = (v & 0x00000FFFu) | ((v << 4) & 0x0FFF0000u);  // twelve bits per 16-bit half
+    return (y & 0x003F003Fu) | ((y << 2) & 0x3F003F00u);
+}
+// Sixteen 6-bit codes, a little-endian stream of 96 bits in three words, as sixteen bytes: word j holds codes 4j..4j+3.
+__device__ __forceinline__ void unpack6x16(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t (&o)[4]) {
+    o[0] = spread6(w0);
+    o[1] = spread6(__funnelshift_r(w0, w1, 24));
+    o[2] = spread6(__funnelshift_r(w1, w2, 16));
+    o[3] = spread6(w2 >> 8);
 }
 
 // Barrier over the consumer warps; the value it returns (zero) is a token for loads that must stay behind it.
@@ -108,13 +126,17 @@ __device__ __forceinline__ bool qi_consumer_barrier_or(int threads, bool pred) {
     return r != 0;
 }
 
-// FMT: kFmtAffine4 or kFmtAffine8; MS: sets of four activation rows (1 or 2); GW: groups of 64 inputs per consumer warp
+// FMT: kFmtAffine4, kFmtAffine8 or kFmtAffine6; MS: sets of four activation rows (1 or 2); GW: groups of 64 inputs per consumer warp
 // when known at compile time (the activation fragments of the warp's K slice then live in registers across all row
 // blocks), 0 when not.
 template <int FMT, int MS, int GW>
 __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kernel(const QiParams p) {
-    constexpr bool W8 = FMT == kFmtAffine8;
-    constexpr int GB = W8 ? 64 : 32;  // code bytes per group of 64 inputs
+    constexpr bool W6 = FMT == kFmtAffine6;
+    // W8: one code per operand byte, lane t of a quad owns inputs 16t..16t+15 of a group (8-bit codes as they are, 6-bit
+    // codes after unpacking); otherwise 4-bit codes, two per byte, split by masks
+    constexpr bool W8 = FMT == kFmtAffine8 || W6;
+    constexpr int GB = W6 ? 48 : (W8 ? 64 : 32);  // code bytes per group of 64 inputs
+    constexpr int LB = GB / 4;                    // ... and per lane of a quad
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* xq = smem;                                            // [groups][MS][32 lanes] uint4: B fragments
     float2* xsc = reinterpret_cast<float2*>(smem + p.xq_bytes);          // [groups][MS * 4 rows] {2^(e-13), sum x}
@@ -165,7 +187,7 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
         for (int pc = blockIdx.x; pc < p.tail_blocks * p.tail_slices; pc += gridDim.x) {
             const int tb = pc / p.tail_slices, sl = pc % p.tail_slices;
             const int r0 = base_rows + tb * kQiRows;
-            const unsigned char* w0p = p.w + (size_t)(r0 + g) * p.row_bytes + t * (W8 ? 16 : 8);
+            const unsigned char* w0p = p.w + (size_t)(r0 + g) * p.row_bytes + t * LB;
             const unsigned char* w1p = w0p + (size_t)8 * p.row_bytes;
             const uint16_t* s0p = reinterpret_cast<const uint16_t*>(p.s + (size_t)(r0 + g) * p.srow_bytes);
             const uint16_t* s1p = reinterpret_cast<const uint16_t*>(p.s + (size_t)(r0 + g + 8) * p.srow_bytes);
@@ -177,7 +199,15 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
             for (int grp = sl * gp; grp < (sl + 1) * gp; grp++) {
                 const int z[4] = {0, 0, 0, 0};
                 uint32_t a[2][4];
-                if (W8) {
+                if (W6) {
+                    const uint32_t* q0 = reinterpret_cast<const uint32_t*>(w0p + grp * GB);
+                    const uint32_t* q1 = reinterpret_cast<const uint32_t*>(w1p + grp * GB);
+                    uint32_t o0[4], o1[4];
+                    unpack6x16(__ldg(q0), __ldg(q0 + 1), __ldg(q0 + 2), o0);
+                    unpack6x16(__ldg(q1), __ldg(q1 + 1), __ldg(q1 + 2), o1);
+                    a[0][0] = o0[0]; a[0][1] = o1[0]; a[0][2] = o0[1]; a[0][3] = o1[1];
+                    a[1][0] = o0[2]; a[1][1] = o1[2]; a[1][2] = o0[3]; a[1][3] = o1[3];
+                } else if (W8) {
                     const uint4 w0 = ldg_nc_u4(w0p + grp * GB), w1 = ldg_nc_u4(w1p + grp * GB);
                     a[0][0] = w0.x; a[0][1] = w1.x; a[0][2] = w0.y; a[0][3] = w1.y;
                     a[1][0] = w0.z; a[1][1] = w1.z; a[1][2] = w0.w; a[1][3] = w1.w;
@@ -371,7 +401,7 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
             for (int c = 0; c < MS; c++) acc0[c] = acc1[c] = 0.f;
             if (ok) {
                 const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
-                const uint32_t wa0 = st + g * p.row_pitch + t * (W8 ? 16 : 8), wa1 = wa0 + 8 * p.row_pitch;
+                const uint32_t wa0 = st + g * p.row_pitch + t * LB, wa1 = wa0 + 8 * p.row_pitch;
                 const uint32_t sa0 = st + codes_bytes + g * p.srow_pitch, sa1 = sa0 + 8 * p.srow_pitch;
 #pragma unroll
                 for (int c4 = 0; c4 < (GW > 0 ? GW : gw); c4 += 4) {
@@ -384,7 +414,14 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
                         const int grp = g0 + c4 + q;
                         const int z[4] = {0, 0, 0, 0};
                         uint32_t a[2][4];  // the A fragments of the group's two MMAs
-                        if (W8) {
+                        if (W6) {
+                            uint32_t o0[4], o1[4];
+                            const uint32_t q0 = wa0 + grp * GB, q1 = wa1 + grp * GB;
+                            unpack6x16(lds32_after(q0, tok), lds32_after(q0 + 4, tok), lds32_after(q0 + 8, tok), o0);
+                            unpack6x16(lds32_after(q1, tok), lds32_after(q1 + 4, tok), lds32_after(q1 + 8, tok), o1);
+                            a[0][0] = o0[0]; a[0][1] = o1[0]; a[0][2] = o0[1]; a[0][3] = o1[1];
+                            a[1][0] = o0[2]; a[1][1] = o1[2]; a[1][2] = o0[3]; a[1][3] = o1[3];
+                        } else if (W8) {
                             const uint4 w0 = lds128_after(wa0 + grp * GB, tok), w1 = lds128_after(wa1 + grp * GB, tok);
                             a[0][0] = w0.x; a[0][1] = w1.x; a[0][2] = w0.y; a[0][3] = w1.y;
                             a[1][0] = w0.z; a[1][1] = w1.z; a[1][2] = w0.w; a[1][3] = w1.w;

@@ -52,8 +52,14 @@ def round_f16(f: np.ndarray) -> np.ndarray:
 
 
 def pack_q(q: np.ndarray, bits: int) -> np.ndarray:
-    """Pack integer codes [..., K] into uint32 [..., K*bits/32]; value j sits in bits [bits*j, bits*j+bits)."""
-    assert 32 % bits == 0
+    """Pack integer codes [..., K] into uint32 [..., K*bits/32]; value j sits in bits [bits*j, bits*j+bits) of the row
+    (for widths that do not divide 32 the row is one little-endian bit stream, Quant.swift:126-136)."""
+    if 32 % bits != 0:
+        q = np.asarray(q, dtype=np.uint8) & np.uint8((1 << bits) - 1)
+        assert (q.shape[-1] * bits) % 32 == 0
+        b = np.unpackbits(q[..., None], axis=-1, bitorder="little")[..., :bits]
+        by = np.packbits(b.reshape(*q.shape[:-1], -1), axis=-1, bitorder="little")
+        return np.ascontiguousarray(by).view(np.uint32)
     per = 32 // bits
     q = np.asarray(q, dtype=np.uint32) & np.uint32((1 << bits) - 1)
     assert q.shape[-1] % per == 0
@@ -64,7 +70,10 @@ def pack_q(q: np.ndarray, bits: int) -> np.ndarray:
 
 def unpack_q(w: np.ndarray, bits: int) -> np.ndarray:
     """uint32 [..., W] -> codes uint32 [..., W*32/bits] (inverse of pack_q)."""
-    assert 32 % bits == 0
+    if 32 % bits != 0:
+        by = np.ascontiguousarray(np.asarray(w, dtype=np.uint32)).view(np.uint8)
+        b = np.unpackbits(by, axis=-1, bitorder="little").reshape(*by.shape[:-1], -1, bits)
+        return np.packbits(b, axis=-1, bitorder="little")[..., 0].astype(np.uint32)
     per = 32 // bits
     w = np.asarray(w, dtype=np.uint32)
     sh = (np.arange(per, dtype=np.uint32) * np.uint32(bits)).astype(np.uint32)
