@@ -457,7 +457,7 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
             __syncwarp();
             if (lane == 0 && ok) mbar_arrive(bar_empty + 8 * s);  // the stage is free once every warp has read its part
 
-            // ---- the eight K slices meet in shared memory; warp 0 adds them in slice order and stores -----------------
+            // ---- the eight K slices meet in shared memory -----------------------------------------------------------------
             float* mine = red + ((it & 1) * ncw + warp) * (64 * MS);
 #pragma unroll
             for (int c = 0; c < MS; c++) {
@@ -465,32 +465,26 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
                 mine[c * 64 + lane * 2 + 1] = acc1[c];
             }
             if (qi_consumer_barrier_or(nct, !ok)) break;  // a wait gave up somewhere: everybody leaves together
-            if (warp != 0) continue;
-#pragma unroll
-            for (int c = 0; c < MS; c++) {
-                const int m = 4 * c + t;
-                if (m >= p.M) continue;
-                float y0 = 0.f, y1 = 0.f;
-                for (int k = 0; k < ncw; k++) {
-                    y0 += red[((it & 1) * ncw + k) * (64 * MS) + c * 64 + lane * 2];
-                    y1 += red[((it & 1) * ncw + k) * (64 * MS) + c * 64 + lane * 2 + 1];
-                }
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int r = g + 8 * h;
-                    if (r >= rows) continue;
-                    const float v = h ? y1 : y0;
-                    const size_t o = (size_t)m * p.ldy + r0 + r;
-                    if (p.y_dtype == kF32) {
-                        float* yp = reinterpret_cast<float*>(p.y) + o;
-                        *yp = p.accumulate ? *yp + v : v;
-                    } else if (p.y_dtype == kF16) {
-                        __half* yp = reinterpret_cast<__half*>(p.y) + o;
-                        *yp = __float2half_rn(p.accumulate ? __half2float(*yp) + v : v);
-                    } else {
-                        uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + o;
-                        *yp = (uint16_t)f32_to_bf16_bits(p.accumulate ? bf16_bits_to_f32(*yp) + v : v);
-                    }
+            // The block's 64 * MS sums, one per thread of the first 2 * MS warps, slices added in slice order; consecutive
+            // lanes take consecutive weight rows, so a row of y is written 64 bytes at a time.
+            if (tid >= 64 * MS) continue;
+            {
+                const int c = tid >> 6, mm = (tid >> 4) & 3, r = tid & 15;
+                const int m = 4 * c + mm;
+                if (m >= p.M || r >= rows) continue;
+                const int slot = c * 64 + (4 * (r & 7) + mm) * 2 + (r >> 3);
+                float v = 0.f;
+                for (int k = 0; k < ncw; k++) v += red[((it & 1) * ncw + k) * (64 * MS) + slot];
+                const size_t o = (size_t)m * p.ldy + r0 + r;
+                if (p.y_dtype == kF32) {
+                    float* yp = reinterpret_cast<float*>(p.y) + o;
+                    *yp = p.accumulate ? *yp + v : v;
+                } else if (p.y_dtype == kF16) {
+                    __half* yp = reinterpret_cast<__half*>(p.y) + o;
+                    *yp = __float2half_rn(p.accumulate ? __half2float(*yp) + v : v);
+                } else {
+                    uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + o;
+                    *yp = (uint16_t)f32_to_bf16_bits(p.accumulate ? bf16_bits_to_f32(*yp) + v : v);
                 }
             }
         }
