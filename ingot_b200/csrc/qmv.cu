@@ -242,17 +242,18 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        // up to four rows and eight groups per warp (K = 4096): the activation fragments stay in registers
-        const bool hoist = ms == 1 && G / ncw == 8;
+        // up to four rows and eight or four groups per warp (K = 4096, 2048): the activation fragments stay in registers
+        const int gwh = ms == 1 ? G / ncw : 0;
         cudaError_t e;
-        if (w6) e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine6, 2, 0>, p)
-                            : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine6, 1, 0>, p);
-        else if (w8) e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 2, 0>, p)
-                            : (hoist ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 1, 8>, p)
-                                     : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine8, 1, 0>, p));
-        else e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 2, 0>, p)
-                         : (hoist ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 1, 8>, p)
-                                  : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 1, 0>, p));
+#define IQ_QI_LAUNCH(F)                                                                             \
+    (ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 2, 0>, p)                                \
+             : gwh == 8 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 1, 8>, p)                     \
+                        : gwh == 4 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 1, 4>, p)          \
+                                   : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 1, 0>, p))
+        if (w6) e = IQ_QI_LAUNCH(kFmtAffine6);
+        else if (w8) e = IQ_QI_LAUNCH(kFmtAffine8);
+        else e = IQ_QI_LAUNCH(kFmtAffine4);
+#undef IQ_QI_LAUNCH
         const int32_t r = check_cuda(ctx, e, "qmv_imma launch");
         if (r != kOk) return r;
     }
@@ -342,15 +343,12 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
 }  // namespace
 
 int32_t gqmv_init(iq_ctx* ctx) {
-    const void* qi[8] = {reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine6, 1, 0>),
-                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine6, 2, 0>),
-                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 1, 0>),
-                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 1, 8>),
-                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 2, 0>),
-                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 1, 0>),
-                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 1, 8>),
-                         reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine8, 2, 0>)};
-    for (int i = 0; i < 8; i++) {
+#define IQ_QI_ALL(F)                                                                                           \
+    reinterpret_cast<const void*>(qmv_imma_kernel<F, 1, 0>), reinterpret_cast<const void*>(qmv_imma_kernel<F, 1, 4>), \
+        reinterpret_cast<const void*>(qmv_imma_kernel<F, 1, 8>), reinterpret_cast<const void*>(qmv_imma_kernel<F, 2, 0>)
+    const void* qi[12] = {IQ_QI_ALL(kFmtAffine4), IQ_QI_ALL(kFmtAffine8), IQ_QI_ALL(kFmtAffine6)};
+#undef IQ_QI_ALL
+    for (int i = 0; i < 12; i++) {
         cudaError_t e = cudaFuncSetAttribute(qi[i], cudaFuncAttributeMaxDynamicSharedMemorySize, kQsSmemMax);
         if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_imma)");
     }

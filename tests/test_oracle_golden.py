@@ -33,11 +33,32 @@ def test_affine_dequant_kat():
     assert (got == np.array(f["expected"], dtype=np.float32)).all()
 
 
-@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("bits", [4, 6, 8])
 def test_pack_unpack_roundtrip(bits):
     rng = np.random.default_rng(bits)
     q = rng.integers(0, 1 << bits, size=(3, 5, 64))
     assert (qref.unpack_q(qref.pack_q(q, bits), bits) == q).all()
+
+
+def test_6bit_stream_matches_the_scalar_rule():
+    """Value j of a 6-bit row sits in bits 6j.. of one little-endian stream, crossing word boundaries
+    (unpackQ, Loader/Quant.swift:126-136; the generator of Tests/IngotTests/KernelHarness.swift:150-172)."""
+    rng = np.random.default_rng(66)
+    q = rng.integers(0, 64, size=128)
+    row = qref.pack_q(q, 6)
+    assert row.shape == (24,)
+    for j in range(128):
+        bit = 6 * j
+        w, o = bit // 32, bit % 32
+        v = int(row[w]) >> o
+        if o + 6 > 32:
+            v |= int(row[w + 1]) << (32 - o)
+        assert v & 63 == q[j]
+    by = row.view(np.uint8)  # the harness sets bit p of byte p / 8
+    for j in (0, 5, 21, 127):
+        for bit in range(6):
+            p_ = 6 * j + bit
+            assert ((int(by[p_ // 8]) >> (p_ % 8)) & 1) == ((int(q[j]) >> bit) & 1)
 
 
 def test_bf16_rne():
