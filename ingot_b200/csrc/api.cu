@@ -95,6 +95,7 @@ extern "C" void iq_ctx_destroy(iq_ctx* ctx) {
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->qmv_tail_scratch) cudaFree(ctx->qmv_tail_scratch);
     if (ctx->qmv_tail_counters) cudaFree(ctx->qmv_tail_counters);
+    delete[] ctx->qmv_maps;
     delete ctx;
 }
 

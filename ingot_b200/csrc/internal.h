@@ -19,6 +19,15 @@ struct iq_ctx {
     float* qmv_tail_scratch = nullptr;
     uint32_t* qmv_tail_counters = nullptr;
     uint32_t qmv_tail_seq = 0;
+    // tensor maps of the GEMV's weight matrices (csrc/qmv.cu), keyed by (base, rows, row bytes): encoding one costs a
+    // driver call, a decode step launches the same matrices over and over
+    struct QmvMap {
+        const void* base = nullptr;
+        int32_t rows = 0, row_bytes = 0;
+        CUtensorMap map;
+    };
+    static constexpr int kQmvMaps = 256;
+    QmvMap* qmv_maps = nullptr;  // host array [kQmvMaps], allocated on first use
     char last_error[256] = {0};
 };
 
@@ -38,6 +47,11 @@ inline int dtype_size(int32_t dt) { return dt == kF32 ? 4 : 2; }
 
 // format id from (bits, group, mode) or -1
 int32_t format_of(const iq_qlinear* m);
+
+// 3-D tensor map over a row-major byte matrix [rows, row_bytes] (row_bytes a multiple of 128) seen as
+// [row_bytes / 128 columns of 128 bytes][rows][128 bytes], box = all columns of 16 rows, 128-byte swizzle: one copy
+// brings a block of 16 rows into shared memory as [column][row][128 bytes] with the rows of a column in different banks.
+int32_t make_map_rows16(iq_ctx* ctx, CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes);
 
 struct Tile;
 // One launch of the gqmv family. mode: 0 plain, 1 gate/up, 2 down. `max_rows` bounds the rows of any tile (<= 16).

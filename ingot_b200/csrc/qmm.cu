@@ -86,6 +86,22 @@ int32_t make_map_2d(iq_ctx* ctx, CUtensorMap* map, const void* base, bool f16, u
     return kOk;
 }
 
+int32_t make_map_rows16(iq_ctx* ctx, CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes) {
+    if (ctx->encode_tiled == nullptr) return fail(ctx, kErrCuda, "cuTensorMapEncodeTiled is not available");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || row_bytes % 128 != 0 || row_bytes / 128 > 256 || rows < 1)
+        return fail(ctx, kErrInvalidArg, "qmv: TMA needs a 16-byte aligned base and rows of 128..32768 bytes in 128-byte steps");
+    const cuuint64_t dims[3] = {128, rows, row_bytes / 128};
+    const cuuint64_t strides[2] = {row_bytes, 128};
+    const cuuint32_t box[3] = {128, 16, (cuuint32_t)(row_bytes / 128)};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
+        map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ctx, kErrCuda, "cuTensorMapEncodeTiled (rows16) failed (%d)", (int)r);
+    return kOk;
+}
+
 int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
     const KernelEntry* ke = find(c.fmt, c.bn, c.epi, c.act);
     if (ke == nullptr) return fail(ctx, kErrNoKernel, "qmm: no kernel for format %d, tile %d, epilogue %d", c.fmt, c.bn, c.epi);

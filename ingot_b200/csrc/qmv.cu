@@ -175,15 +175,18 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     QiParams p;
     memset(&p, 0, sizeof(p));
     p.row_bytes = w8 ? c.K : (w6 ? c.K / 4 * 3 : c.K / 2);
-    // rows land in different banks for the fragment loads: a lane's piece is 16, 12 or 8 bytes, a quad's 64, 48 or 32
-    p.row_pitch = p.row_bytes + (w8 ? 64 : (w6 ? 48 : 32));
+    // 4-bit codes with rows of 1 KB (K = 2048): one swizzled tensor copy per block of 16 rows, no padding (the swizzle
+    // spreads the rows over the banks). Otherwise one bulk copy per row into rows padded by a quad's piece.
+    const bool tm = c.fmt == kFmtAffine4 && p.row_bytes <= 1024 && ctx->encode_tiled != nullptr;
+    p.row_pitch = tm ? p.row_bytes : p.row_bytes + (w8 ? 64 : (w6 ? 48 : 32));
     p.srow_bytes = G * 2;
     p.srow_pitch = p.srow_bytes;
     p.stage_bytes = kQiRows * p.row_pitch + 2 * kQiRows * p.srow_pitch;
     // The path is chosen on what eight rows need, whatever the row count of this call: a row must see the same
     // arithmetic alone and among sixteen.
     const int ncw = 8;  // consumer warps (16 measured slower: 11.3 against 10.0 us on the 14336 x 4096 layer)
-    auto fixed_bytes = [&](int ms) { return G * 512 * ms + G * 32 * ms + 512 * ms * ncw + 256; };
+    // (+ 1024: the stages of the tensor copies start on a 1024-byte boundary)
+    auto fixed_bytes = [&](int ms) { return G * 512 * ms + G * 32 * ms + 512 * ms * ncw + 256 + (tm ? 1024 : 0); };
     if ((kQsSmemMax - fixed_bytes(2)) / p.stage_bytes < 2) return 1;
     p.w = reinterpret_cast<const unsigned char*>(c.w[0]);
     p.s = reinterpret_cast<const unsigned char*>(c.s[0]);
@@ -192,6 +195,22 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     p.x_dtype = c.x_dtype; p.ldx = c.ldx;
     p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
     p.status = ctx->d_status;
+    const CUtensorMap* map = nullptr;
+    static const CUtensorMap no_map = {};
+    if (tm) {
+        // the matrix as the kernel sees it: all rows of W, whatever prefix of them this call computes
+        if (ctx->qmv_maps == nullptr) ctx->qmv_maps = new iq_ctx::QmvMap[iq_ctx::kQmvMaps];
+        const uintptr_t key = reinterpret_cast<uintptr_t>(p.w);
+        iq_ctx::QmvMap& e = ctx->qmv_maps[((key >> 8) ^ (key >> 20) ^ (uintptr_t)c.N) % iq_ctx::kQmvMaps];
+        if (e.base != p.w || e.rows != c.N || e.row_bytes != p.row_bytes) {
+            const int32_t r = make_map_rows16(ctx, &e.map, p.w, (uint64_t)c.N, (uint64_t)p.row_bytes);
+            if (r != kOk) { e.base = nullptr; return r; }
+            e.base = p.w; e.rows = c.N; e.row_bytes = p.row_bytes;
+        }
+        map = &e.map;
+    } else {
+        map = &no_map;
+    }
     const int blocks = c.N / kQiRows;
     // Tail split, decided from the matrix and the GPU alone (not from the row count, so a row sees the same arithmetic
     // in every call): when the blocks do not divide over two CTAs per SM and few are left over, the left-over blocks
@@ -246,11 +265,13 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
         const int gwh = ms == 1 ? G / ncw : 0;
         cudaError_t e;
 #define IQ_QI_LAUNCH(F)                                                                             \
-    (ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 2, 0>, p)                                \
-             : gwh == 8 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 1, 8>, p)                     \
-                        : gwh == 4 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 1, 4>, p)          \
-                                   : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 1, 0>, p))
-        if (w6) e = IQ_QI_LAUNCH(kFmtAffine6);
+    (ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 2, 0>, *map, p)                          \
+             : gwh == 8 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 1, 8>, *map, p)               \
+                        : gwh == 4 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 1, 4>, *map, p)    \
+                                   : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<F, 1, 0>, *map, p))
+        if (tm) e = ms == 2 ? cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 2, 0, true>, *map, p)
+                            : cudaLaunchKernelEx(&cfg, qmv_imma_kernel<kFmtAffine4, 1, 4, true>, *map, p);
+        else if (w6) e = IQ_QI_LAUNCH(kFmtAffine6);
         else if (w8) e = IQ_QI_LAUNCH(kFmtAffine8);
         else e = IQ_QI_LAUNCH(kFmtAffine4);
 #undef IQ_QI_LAUNCH
@@ -346,9 +367,11 @@ int32_t gqmv_init(iq_ctx* ctx) {
 #define IQ_QI_ALL(F)                                                                                           \
     reinterpret_cast<const void*>(qmv_imma_kernel<F, 1, 0>), reinterpret_cast<const void*>(qmv_imma_kernel<F, 1, 4>), \
         reinterpret_cast<const void*>(qmv_imma_kernel<F, 1, 8>), reinterpret_cast<const void*>(qmv_imma_kernel<F, 2, 0>)
-    const void* qi[12] = {IQ_QI_ALL(kFmtAffine4), IQ_QI_ALL(kFmtAffine8), IQ_QI_ALL(kFmtAffine6)};
+    const void* qi[14] = {IQ_QI_ALL(kFmtAffine4), IQ_QI_ALL(kFmtAffine8), IQ_QI_ALL(kFmtAffine6),
+                          reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 1, 4, true>),
+                          reinterpret_cast<const void*>(qmv_imma_kernel<kFmtAffine4, 2, 0, true>)};
 #undef IQ_QI_ALL
-    for (int i = 0; i < 12; i++) {
+    for (int i = 0; i < 14; i++) {
         cudaError_t e = cudaFuncSetAttribute(qi[i], cudaFuncAttributeMaxDynamicSharedMemorySize, kQsSmemMax);
         if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_imma)");
     }

@@ -129,25 +129,37 @@ __device__ __forceinline__ bool qi_consumer_barrier_or(int threads, bool pred) {
 // FMT: kFmtAffine4, kFmtAffine8 or kFmtAffine6; MS: sets of four activation rows (1 or 2); GW: groups of 64 inputs per consumer warp
 // when known at compile time (the activation fragments of the warp's K slice then live in registers across all row
 // blocks), 0 when not.
-template <int FMT, int MS, int GW>
-__global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kernel(const QiParams p) {
+template <int FMT, int MS, int GW, bool TM = false>
+__global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1)
+    qmv_imma_kernel(const __grid_constant__ CUtensorMap wmap, const QiParams p) {
     constexpr bool W6 = FMT == kFmtAffine6;
     // W8: one code per operand byte, lane t of a quad owns inputs 16t..16t+15 of a group (8-bit codes as they are, 6-bit
     // codes after unpacking); otherwise 4-bit codes, two per byte, split by masks
     constexpr bool W8 = FMT == kFmtAffine8 || W6;
     constexpr int GB = W6 ? 48 : (W8 ? 64 : 32);  // code bytes per group of 64 inputs
     constexpr int LB = GB / 4;                    // ... and per lane of a quad
+    // TM: a block of 16 rows arrives as one tensor copy with the 128-byte swizzle, laid out [128-byte column][row][128]:
+    // the byte at offset o of row r sits at (o / 128) * 2048 + r * 128 + ((o / 16 % 8) ^ (r % 8)) * 16 + o % 16, which puts
+    // the eight rows a fragment load touches in eight different bank groups without padding the rows. One copy per block
+    // instead of one per row: with rows of 1 KB (4-bit, K = 2048) the per-row copies' issue rate, about one per 35 ns and
+    // SM, bounds the kernel at 0.6 of the memory roofline, the tensor copy reaches 0.8. With rows of 2 KB and more the
+    // per-row copies already run at the memory's rate and start faster, so they stay.
+    // Not TM: one bulk copy per row into padded rows.
+    static_assert(!TM || FMT == kFmtAffine4, "tensor-copy staging is built for 4-bit codes");
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* xq = smem;                                            // [groups][MS][32 lanes] uint4: B fragments
     float2* xsc = reinterpret_cast<float2*>(smem + p.xq_bytes);          // [groups][MS * 4 rows] {2^(e-13), sum x}
     float* red = reinterpret_cast<float*>(smem + p.xq_bytes + p.xsc_bytes);  // [2][consumer warps][MS][32 lanes][2]
     unsigned char* stages = smem + p.xq_bytes + p.xsc_bytes + p.red_bytes;
+    if (TM) stages += (1024u - (smem_u32(stages) & 1023u)) & 1023u;  // the swizzle pattern is a function of the address
     const int ncw = p.ncw, nct = 32 * p.ncw;  // consumer warps and threads
     uint64_t* bars = reinterpret_cast<uint64_t*>(stages + (size_t)p.nstages * p.stage_bytes);
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * p.nstages;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * p.nstages);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (TM && tid == 32 * p.ncw)  // the descriptor's fetch starts now, not with the first copy
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
     if (tid == 0) {
         for (int s = 0; s < p.nstages; s++) {
             mbar_init(bar_full + 8 * s, 1);
@@ -290,14 +302,19 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
             ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, rows * (p.row_bytes + 2 * p.srow_bytes));
+            // (a tensor copy counts its whole box, rows beyond the matrix arrive as zeros)
+            if (lane == 0)
+                mbar_arrive_expect_tx(bar_full + 8 * s, (TM ? kQiRows : rows) * p.row_bytes + rows * 2 * p.srow_bytes);
             __syncwarp();
             const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
-            if (lane < rows) {  // lanes 0-15: the codes of one row each
+            if (TM) {
+                if (lane == 0) tma_load_3d(st, &wmap, bar_full + 8 * s, 0, r0, 0);
+            } else if (lane < rows) {  // lanes 0-15: the codes of one row each
                 const unsigned char* src = p.w + (size_t)(r0 + lane) * p.row_bytes;
                 for (int off = 0; off < p.row_bytes; off += kQiPiece)
                     bulk_g2s(st + lane * p.row_pitch + off, src + off, min(kQiPiece, p.row_bytes - off), bar_full + 8 * s);
-            } else if (lane == 16) {
+            }
+            if (lane == 16) {
                 bulk_g2s(st + codes_bytes, p.s + (size_t)r0 * p.srow_bytes, rows * p.srow_bytes, bar_full + 8 * s);
             } else if (lane == 17) {
                 bulk_g2s(st + codes_bytes + sc_bytes, p.b + (size_t)r0 * p.srow_bytes, rows * p.srow_bytes, bar_full + 8 * s);
@@ -389,6 +406,12 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
                     xsr[q][c] = lds64f_after(xsc32 + ((g0 + q) * MS + c) * 32, xtok);
                 }
         }
+        // TM: where the lane's piece of group q of a run of four groups sits, relative to row g of the run's first column
+        uint32_t xo[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+            xo[q] = W8 ? (q >> 1) * 2048 + ((((q & 1) * 4 + t) ^ g) << 4)
+                       : (((2 * q + (t >> 1)) ^ g) << 4) + ((t & 1) << 3);
         for (int it = 0; it < items; it++) {
             const int s = it % p.nstages;
             const uint32_t ph = (it / p.nstages) & 1;
@@ -401,7 +424,10 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
             for (int c = 0; c < MS; c++) acc0[c] = acc1[c] = 0.f;
             if (ok) {
                 const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
-                const uint32_t wa0 = st + g * p.row_pitch + t * LB, wa1 = wa0 + 8 * p.row_pitch;
+                // not TM: row g of the padded stage, the lane's piece of group 0. TM: row g of the first 128-byte column
+                // this warp reads (four 4-bit groups or two 8-bit groups per column); xo[] adds the swizzled piece.
+                const uint32_t wa0 = TM ? st + g * 128 + (W8 ? g0 >> 1 : g0 >> 2) * 2048 : st + g * p.row_pitch + t * LB;
+                const uint32_t wa1 = wa0 + (TM ? 1024 : 8 * p.row_pitch);
                 const uint32_t sa0 = st + codes_bytes + g * p.srow_pitch, sa1 = sa0 + 8 * p.srow_pitch;
 #pragma unroll
                 for (int c4 = 0; c4 < (GW > 0 ? GW : gw); c4 += 4) {
@@ -422,11 +448,13 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1) qmv_imma_kerne
                             a[0][0] = o0[0]; a[0][1] = o1[0]; a[0][2] = o0[1]; a[0][3] = o1[1];
                             a[1][0] = o0[2]; a[1][1] = o1[2]; a[1][2] = o0[3]; a[1][3] = o1[3];
                         } else if (W8) {
-                            const uint4 w0 = lds128_after(wa0 + grp * GB, tok), w1 = lds128_after(wa1 + grp * GB, tok);
+                            const uint32_t o = TM ? c4 * 1024 + xo[q] : grp * GB;
+                            const uint4 w0 = lds128_after(wa0 + o, tok), w1 = lds128_after(wa1 + o, tok);
                             a[0][0] = w0.x; a[0][1] = w1.x; a[0][2] = w0.y; a[0][3] = w1.y;
                             a[1][0] = w0.z; a[1][1] = w1.z; a[1][2] = w0.w; a[1][3] = w1.w;
                         } else {
-                            const uint2 w0 = lds64_after(wa0 + grp * GB, tok), w1 = lds64_after(wa1 + grp * GB, tok);
+                            const uint32_t o = TM ? c4 * 512 + xo[q] : grp * GB;
+                            const uint2 w0 = lds64_after(wa0 + o, tok), w1 = lds64_after(wa1 + o, tok);
                             constexpr uint32_t MSK = 0x0F0F0F0Fu;
                             a[0][0] = w0.x & MSK; a[0][1] = w1.x & MSK; a[0][2] = (w0.x >> 4) & MSK; a[0][3] = (w1.x >> 4) & MSK;
                             a[1][0] = w0.y & MSK; a[1][1] = w1.y & MSK; a[1][2] = (w0.y >> 4) & MSK; a[1][3] = (w1.y >> 4) & MSK;
