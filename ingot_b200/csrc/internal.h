@@ -23,7 +23,7 @@ struct iq_ctx {
     // driver call, a decode step launches the same matrices over and over
     struct QmvMap {
         const void* base = nullptr;
-        int32_t rows = 0, row_bytes = 0;
+        int32_t rows = 0, row_bytes = 0, box_rows = 0;
         CUtensorMap map;
     };
     static constexpr int kQmvMaps = 256;
@@ -49,9 +49,12 @@ inline int dtype_size(int32_t dt) { return dt == kF32 ? 4 : 2; }
 int32_t format_of(const iq_qlinear* m);
 
 // 3-D tensor map over a row-major byte matrix [rows, row_bytes] (row_bytes a multiple of 128) seen as
-// [row_bytes / 128 columns of 128 bytes][rows][128 bytes], box = all columns of 16 rows, 128-byte swizzle: one copy
-// brings a block of 16 rows into shared memory as [column][row][128 bytes] with the rows of a column in different banks.
-int32_t make_map_rows16(iq_ctx* ctx, CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes);
+// [row_bytes / 128 columns of 128 bytes][rows][128 bytes], box = all columns of box_rows rows, 128-byte swizzle: one copy
+// brings a block of rows into shared memory as [column][row][128 bytes] with the rows of a column in different banks.
+int32_t make_map_rowblock(iq_ctx* ctx, CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                          uint32_t box_rows);
+// The same through the context's cache; nullptr (with the error recorded) when the encoding fails.
+const CUtensorMap* cached_rowblock_map(iq_ctx* ctx, const void* base, int64_t rows, int32_t row_bytes, int32_t box_rows);
 
 struct Tile;
 // One launch of the gqmv family. mode: 0 plain, 1 gate/up, 2 down. `max_rows` bounds the rows of any tile (<= 16).
@@ -63,6 +66,8 @@ struct GqmvCall {
     const void* s[2] = {nullptr, nullptr};
     const void* b[2] = {nullptr, nullptr};
     int64_t w_estride = 0, s_estride = 0;
+    // which experts the stacked tensors hold (w[] is offset so that a global expert id indexes it); 0 experts: not known
+    int32_t expert_lo = 0, expert_count = 0;
     int32_t N = 0, K = 0;
     const void* x = nullptr;
     int32_t x_dtype = 0;

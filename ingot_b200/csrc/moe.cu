@@ -147,6 +147,7 @@ int32_t run_gateup(iq_moe* l, cudaStream_t cs, const void* x, int32_t x_dtype, i
         c.b[0] = static_cast<const char*>(d.gate.biases) - lo * c.s_estride * 2;
         c.b[1] = static_cast<const char*>(d.up.biases) - lo * c.s_estride * 2;
     }
+    c.expert_lo = d.expert_lo; c.expert_count = d.expert_count;
     c.N = d.d_ff; c.K = d.d_model;
     c.x = x; c.x_dtype = x_dtype; c.ldx = ldx;
     c.row_map = row_map; c.topk = d.top_k;
@@ -176,6 +177,7 @@ int32_t run_down(iq_moe* l, cudaStream_t cs, const __half* h, const Tile* tiles,
     c.w[0] = static_cast<const uint32_t*>(d.down.w) - lo * c.w_estride;
     c.s[0] = static_cast<const char*>(d.down.scales) - lo * c.s_estride * (int64_t)sb;
     if (d.down.biases) c.b[0] = static_cast<const char*>(d.down.biases) - lo * c.s_estride * 2;
+    c.expert_lo = d.expert_lo; c.expert_count = d.expert_count;
     c.N = d.d_model; c.K = d.d_ff;
     c.x = h; c.x_dtype = kF16; c.ldx = d.d_ff;
     c.tiles = tiles; c.ntiles = ntiles; c.grid_tiles = max_tiles;

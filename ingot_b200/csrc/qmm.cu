@@ -86,20 +86,34 @@ int32_t make_map_2d(iq_ctx* ctx, CUtensorMap* map, const void* base, bool f16, u
     return kOk;
 }
 
-int32_t make_map_rows16(iq_ctx* ctx, CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes) {
+int32_t make_map_rowblock(iq_ctx* ctx, CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                          uint32_t box_rows) {
     if (ctx->encode_tiled == nullptr) return fail(ctx, kErrCuda, "cuTensorMapEncodeTiled is not available");
-    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || row_bytes % 128 != 0 || row_bytes / 128 > 256 || rows < 1)
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || row_bytes % 128 != 0 || row_bytes / 128 > 256 || rows < 1 || box_rows < 8 ||
+        box_rows > 256 || box_rows % 8 != 0)
         return fail(ctx, kErrInvalidArg, "qmv: TMA needs a 16-byte aligned base and rows of 128..32768 bytes in 128-byte steps");
     const cuuint64_t dims[3] = {128, rows, row_bytes / 128};
     const cuuint64_t strides[2] = {row_bytes, 128};
-    const cuuint32_t box[3] = {128, 16, (cuuint32_t)(row_bytes / 128)};
+    const cuuint32_t box[3] = {128, box_rows, (cuuint32_t)(row_bytes / 128)};
     const cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
         map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(ctx, kErrCuda, "cuTensorMapEncodeTiled (rows16) failed (%d)", (int)r);
+    if (r != CUDA_SUCCESS) return fail(ctx, kErrCuda, "cuTensorMapEncodeTiled (row block) failed (%d)", (int)r);
     return kOk;
+}
+
+const CUtensorMap* cached_rowblock_map(iq_ctx* ctx, const void* base, int64_t rows, int32_t row_bytes, int32_t box_rows) {
+    if (ctx->qmv_maps == nullptr) ctx->qmv_maps = new iq_ctx::QmvMap[iq_ctx::kQmvMaps];
+    const uintptr_t key = reinterpret_cast<uintptr_t>(base);
+    iq_ctx::QmvMap& e = ctx->qmv_maps[((key >> 8) ^ (key >> 20) ^ (uintptr_t)rows ^ (uintptr_t)box_rows) % iq_ctx::kQmvMaps];
+    if (e.base != base || e.rows != rows || e.row_bytes != row_bytes || e.box_rows != box_rows) {
+        e.base = nullptr;
+        if (make_map_rowblock(ctx, &e.map, base, (uint64_t)rows, (uint64_t)row_bytes, (uint32_t)box_rows) != kOk) return nullptr;
+        e.base = base; e.rows = (int32_t)rows; e.row_bytes = row_bytes; e.box_rows = box_rows;
+    }
+    return &e.map;
 }
 
 int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {

@@ -199,15 +199,8 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     static const CUtensorMap no_map = {};
     if (tm) {
         // the matrix as the kernel sees it: all rows of W, whatever prefix of them this call computes
-        if (ctx->qmv_maps == nullptr) ctx->qmv_maps = new iq_ctx::QmvMap[iq_ctx::kQmvMaps];
-        const uintptr_t key = reinterpret_cast<uintptr_t>(p.w);
-        iq_ctx::QmvMap& e = ctx->qmv_maps[((key >> 8) ^ (key >> 20) ^ (uintptr_t)c.N) % iq_ctx::kQmvMaps];
-        if (e.base != p.w || e.rows != c.N || e.row_bytes != p.row_bytes) {
-            const int32_t r = make_map_rows16(ctx, &e.map, p.w, (uint64_t)c.N, (uint64_t)p.row_bytes);
-            if (r != kOk) { e.base = nullptr; return r; }
-            e.base = p.w; e.rows = c.N; e.row_bytes = p.row_bytes;
-        }
-        map = &e.map;
+        map = cached_rowblock_map(ctx, p.w, c.N, p.row_bytes, kQiRows);
+        if (map == nullptr) return kErrCuda;
     } else {
         map = &no_map;
     }
@@ -282,11 +275,17 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
 }
 
 // ---- int8 tensor-core path for the MoE decode tiles (gate/up + activation, down; affine 4-bit experts) ---------------
-typedef void (*QgKernel)(const QgParams);
-QgKernel qg_pick(int mode, int ms) {
-    if (mode == kModeGateUp) return ms == 4 ? qmv_imma_grouped_kernel<kModeGateUp, 4> : qmv_imma_grouped_kernel<kModeGateUp, 2>;
-    return ms == 4 ? qmv_imma_grouped_kernel<kModeDown, 4> : qmv_imma_grouped_kernel<kModeDown, 2>;
+typedef void (*QgKernel)(const CUtensorMap, const CUtensorMap, const QgParams);
+template <bool TM>
+QgKernel qg_pick_tm(int mode, int ms) {
+    if (mode == kModeGateUp)
+        return ms == 4 ? qmv_imma_grouped_kernel<kModeGateUp, 4, TM> : qmv_imma_grouped_kernel<kModeGateUp, 2, TM>;
+    return ms == 4 ? qmv_imma_grouped_kernel<kModeDown, 4, TM> : qmv_imma_grouped_kernel<kModeDown, 2, TM>;
 }
+QgKernel qg_pick(int mode, int ms, bool tm) { return tm ? qg_pick_tm<true>(mode, ms) : qg_pick_tm<false>(mode, ms); }
+// INGOT_QG_DOWN=1: the down projection (K = d_ff, rows of 384 bytes) on this path too. Off: with tensor copies it
+// measured 9.73 ms against 8.57 ms per 48-layer step of 64 tokens on the fp16 tile kernels.
+int g_qg_down = 0;
 
 // Returns kOk after a launch, 1 when the shape does not fit this path (the caller falls back), or an error.
 int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
@@ -298,19 +297,22 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
             (reinterpret_cast<uintptr_t>(c.b[i]) & 15))
             return 1;
     const int G = c.K / 64;
-    // Short weight rows (the down projection's K = d_ff) stay on the fp16 tile kernels: one bulk copy per 384-byte row
-    // costs more than the arithmetic saves (measured 61.9 against 49.6 us at 64 tokens).
-    if (c.K < 2048) return 1;
-    const int ms = c.max_rows > 8 ? 4 : 2;
     QgParams p;
     memset(&p, 0, sizeof(p));
     p.row_bytes = c.K / 2;
-    p.row_pitch = p.row_bytes + 32;
+    // Tensor-copy staging: the stacked tensors must be known (which experts they hold) and dense, rows whole 128-byte
+    // columns. Short weight rows (the down projection's K = d_ff) stay on the fp16 tile kernels either way: with one
+    // bulk copy per 384-byte row this path measured 61.9 against 49.6 us at 64 tokens, with tensor copies no better.
+    const bool tm = ctx->encode_tiled != nullptr && c.expert_count > 0 && p.row_bytes % 128 == 0 && p.row_bytes / 128 <= 256 &&
+                    c.w_estride * 4 == (int64_t)c.N * p.row_bytes && (c.K >= 2048 || g_qg_down != 0);
+    if (c.K < 2048 && !tm) return 1;
+    const int ms = c.max_rows > 8 ? 4 : 2;
+    p.row_pitch = tm ? p.row_bytes : p.row_bytes + 32;
     p.srow_bytes = G * 2;
     p.xq_bytes = G * ms * 512;
     p.xsc_bytes = G * ms * 32;
     p.red_bytes = 2 * 8 * nw * ms * 64 * 4;
-    const int fixed = p.xq_bytes + p.xsc_bytes + p.red_bytes + 256;
+    const int fixed = p.xq_bytes + p.xsc_bytes + p.red_bytes + 256 + (tm ? 1024 : 0);
     // K slices per block of rows: four (32-row blocks: half as many hand-overs per byte; measured 86 against 100 us on
     // the 64-token layer) when two stages of that size fit, else eight
     int ctas = 1, nstages = 0;
@@ -322,7 +324,7 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
         if ((R * p.srow_bytes) % 16 != 0) continue;
         p.wk = wk; p.rgs = 8 / wk;
         p.NB = (c.N + R - 1) / R;
-        p.mat_bytes = R * p.row_pitch + 2 * R * p.srow_bytes;
+        p.mat_bytes = round_up(R * p.row_pitch + 2 * R * p.srow_bytes, tm ? 1024 : 16);
         p.stage_bytes = nw * p.mat_bytes;
         nstages = (kQsSmemMax - fixed) / p.stage_bytes;
     }
@@ -337,6 +339,16 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
     }
     p.w_ebytes = c.w_estride * 4;
     p.s_ebytes = c.s_estride * 2;
+    p.expert_lo = c.expert_lo;
+    static const CUtensorMap no_map = {};
+    const CUtensorMap* maps[2] = {&no_map, &no_map};
+    if (tm) {
+        for (int i = 0; i < nw; i++) {
+            maps[i] = cached_rowblock_map(ctx, p.w[i] + (int64_t)c.expert_lo * p.w_ebytes, (int64_t)c.expert_count * c.N,
+                                          p.row_bytes, 16 * p.rgs);
+            if (maps[i] == nullptr) return kErrCuda;
+        }
+    }
     p.N = c.N; p.K = c.K;
     p.x = c.x; p.x_dtype = c.x_dtype; p.ldx = c.ldx;
     p.row_map = c.row_map; p.topk = c.topk;
@@ -358,7 +370,7 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return check_cuda(ctx, cudaLaunchKernelEx(&cfg, qg_pick(c.mode, ms), p), "qmv_imma_grouped launch");
+    return check_cuda(ctx, cudaLaunchKernelEx(&cfg, qg_pick(c.mode, ms, tm), *maps[0], *maps[1], p), "qmv_imma_grouped launch");
 }
 
 }  // namespace
@@ -376,8 +388,8 @@ int32_t gqmv_init(iq_ctx* ctx) {
         if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_imma)");
     }
     for (int mode = kModeGateUp; mode <= kModeDown; mode++)
-        for (int ms = 2; ms <= 4; ms += 2) {
-            cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(qg_pick(mode, ms)),
+        for (int v = 0; v < 4; v++) {  // 2 or 4 row sets, bulk copies per row or tensor copies
+            cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(qg_pick(mode, (v & 1) ? 4 : 2, v >= 2)),
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kQsSmemMax);
             if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_imma_grouped)");
         }
@@ -398,6 +410,7 @@ int32_t gqmv_init(iq_ctx* ctx) {
                 if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_stream)");
             }
     if (const char* e2 = getenv("INGOT_QMV_CTAS")) g_qi_ctas = atoi(e2);
+    if (const char* e3 = getenv("INGOT_QG_DOWN")) g_qg_down = atoi(e3);
     const char* env = getenv("INGOT_QMV_PATH");
     g_path = env == nullptr ? 0 : (strcmp(env, "legacy") == 0 ? 1 : (strcmp(env, "stream") == 0 ? 2 : 0));  // both: no int8 path
     return kOk;

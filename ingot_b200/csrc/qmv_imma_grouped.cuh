@@ -45,13 +45,18 @@ struct QgParams {
     int32_t NB;                  // items per tile
     int32_t row_bytes, row_pitch, srow_bytes;
     int32_t mat_bytes, stage_bytes, nstages;
+    int32_t expert_lo;           // tensor-copy staging: the first expert the stacked tensors (and the maps) hold
     int32_t xq_bytes, xsc_bytes, red_bytes;
     int32_t* status;
 };
 
-// MODE: kModeGateUp (two matrices, h = act(gate, up)) or kModeDown; MS: sets of four activation rows per tile (2 or 4)
-template <int MODE, int MS>
-__global__ void __launch_bounds__(kQgThreads, 1) qmv_imma_grouped_kernel(const QgParams p) {
+// MODE: kModeGateUp (two matrices, h = act(gate, up)) or kModeDown; MS: sets of four activation rows per tile (2 or 4).
+// TM: a block of R rows of a matrix arrives as one swizzled tensor copy, laid out [128-byte column][row][128] (see
+// qmv_imma.cuh), instead of one bulk copy per row: expert rows are 384 to 1024 bytes, and copies that short are bound by
+// their issue rate (one producer warp sustains about one per 60 ns), not by their bytes.
+template <int MODE, int MS, bool TM>
+__global__ void __launch_bounds__(kQgThreads, 1)
+    qmv_imma_grouped_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1, const QgParams p) {
     constexpr int NW = MODE == kModeGateUp ? 2 : 1;
     constexpr int GB = 32;  // code bytes per group of 64 inputs (4-bit)
     extern __shared__ __align__(16) unsigned char smem[];
@@ -59,11 +64,16 @@ __global__ void __launch_bounds__(kQgThreads, 1) qmv_imma_grouped_kernel(const Q
     float2* xsc = reinterpret_cast<float2*>(smem + p.xq_bytes);          // [groups][MS * 4 rows] {2^(e-13), sum x}
     float* red = reinterpret_cast<float*>(smem + p.xq_bytes + p.xsc_bytes);  // [2][8 warps][NW * MS][32 lanes][2]
     unsigned char* stages = smem + p.xq_bytes + p.xsc_bytes + p.red_bytes;
+    if (TM) stages += (1024u - (smem_u32(stages) & 1023u)) & 1023u;  // the swizzle pattern is a function of the address
     uint64_t* bars = reinterpret_cast<uint64_t*>(stages + (size_t)p.nstages * p.stage_bytes);
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * p.nstages;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * p.nstages);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (TM && tid == 256) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map0) : "memory");
+        if (NW == 2) asm volatile("prefetch.tensormap [%0];" ::"l"(&map1) : "memory");
+    }
     if (tid == 0) {
         for (int s = 0; s < p.nstages; s++) {
             mbar_init(bar_full + 8 * s, 1);
@@ -98,9 +108,26 @@ __global__ void __launch_bounds__(kQgThreads, 1) qmv_imma_grouped_kernel(const Q
             ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, NW * rows * (p.row_bytes + 2 * p.srow_bytes));
+            // (a tensor copy counts its whole box; rows past the block belong to the next expert or arrive as zeros)
+            if (lane == 0)
+                mbar_arrive_expect_tx(bar_full + 8 * s, NW * ((TM ? R : rows) * p.row_bytes + 2 * rows * p.srow_bytes));
             __syncwarp();
             const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
+            if (TM) {
+                // per matrix: one tensor copy of the codes, one bulk copy of the scales, one of the biases
+                if (lane < NW * 3) {
+                    const int i = lane / 3, q = lane % 3;
+                    const uint32_t dst = st + i * p.mat_bytes;
+                    if (q == 0) {
+                        tma_load_3d(dst, i == 0 ? &map0 : &map1, bar_full + 8 * s, 0,
+                                    (int)(expert - (uint32_t)p.expert_lo) * p.N + r0, 0);
+                    } else {
+                        const unsigned char* src = (q == 1 ? p.s[i] : p.b[i]) + expert * p.s_ebytes + (int64_t)r0 * p.srow_bytes;
+                        bulk_g2s(dst + codes_bytes + (q == 2 ? sc_bytes : 0), src, rows * p.srow_bytes, bar_full + 8 * s);
+                    }
+                }
+                continue;
+            }
             // per matrix: one copy per row of codes (into padded rows), one for the scales, one for the biases
             for (int j = lane; j < NW * (rows + 2); j += 32) {
                 const int i = j / (rows + 2), q = j % (rows + 2);
@@ -216,8 +243,12 @@ __global__ void __launch_bounds__(kQgThreads, 1) qmv_imma_grouped_kernel(const Q
                     }
 #pragma unroll
                     for (int i = 0; i < NW; i++) {
-                        const uint32_t wa0 = st + i * p.mat_bytes + (rb * 16 + g) * p.row_pitch + t * 8 + grp * GB;
-                        const uint32_t wa1 = wa0 + 8 * p.row_pitch;
+                        // TM: column grp / 4 of the block, row rb * 16 + g, 16-byte piece ((grp % 4) * 2 + t / 2) ^ g
+                        const uint32_t wa0 = st + i * p.mat_bytes +
+                                             (TM ? (grp >> 2) * (R * 128) + (rb * 16 + g) * 128 +
+                                                       (((((grp & 3) << 1) + (t >> 1)) ^ g) << 4) + ((t & 1) << 3)
+                                                 : (rb * 16 + g) * p.row_pitch + t * 8 + grp * GB);
+                        const uint32_t wa1 = wa0 + (TM ? 1024 : 8 * p.row_pitch);
                         const uint32_t sa0 = st + i * p.mat_bytes + codes_bytes + (rb * 16 + g) * p.srow_bytes + grp * 2;
                         const uint32_t sa1 = sa0 + 8 * p.srow_bytes;
                         const uint2 w0 = lds64_after(wa0, tok), w1 = lds64_after(wa1, tok);
