@@ -176,12 +176,13 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     memset(&p, 0, sizeof(p));
     p.row_bytes = w8 ? c.K : (w6 ? c.K / 4 * 3 : c.K / 2);
     // 4-bit codes with rows of 1 KB (K = 2048): one swizzled tensor copy per block of 16 rows, no padding (the swizzle
-    // spreads the rows over the banks). Otherwise one bulk copy per row into rows padded by a quad's piece.
+    // spreads the rows over the banks). Otherwise one bulk copy per row (4-bit) or per pair of rows (6- and 8-bit), padded apart by a quad's piece.
     const bool tm = c.fmt == kFmtAffine4 && p.row_bytes <= 1024 && ctx->encode_tiled != nullptr;
-    p.row_pitch = tm ? p.row_bytes : p.row_bytes + (w8 ? 64 : (w6 ? 48 : 32));
+    p.pair = (w8 || w6) ? 1 : 0;  // two rows per bulk copy
+    p.row_pitch = tm ? p.row_bytes : (p.pair ? 2 : 1) * p.row_bytes + (w8 ? 64 : (w6 ? 48 : 32));
     p.srow_bytes = G * 2;
     p.srow_pitch = p.srow_bytes;
-    p.stage_bytes = kQiRows * p.row_pitch + 2 * kQiRows * p.srow_pitch;
+    p.stage_bytes = (tm ? kQiRows * p.row_bytes : (p.pair ? kQiRows / 2 : kQiRows) * p.row_pitch) + 2 * kQiRows * p.srow_pitch;
     // The path is chosen on what eight rows need, whatever the row count of this call: a row must see the same
     // arithmetic alone and among sixteen.
     const int ncw = 8;  // consumer warps (16 measured slower: 11.3 against 10.0 us on the 14336 x 4096 layer)

@@ -16,7 +16,8 @@
 //
 // Structure: persistent CTAs (two per SM up to four rows) each own a contiguous range of 16-row blocks and walk it block
 // by block. Warp 8 streams each 16-row block through a ring of bulk copies (one per
-// row, into rows padded so that the fragment loads are free of bank conflicts, plus scales and biases); the 8 or 16
+// pair of rows, the pairs padded apart so that the fragment loads are free of bank conflicts, plus scales and biases;
+// or one swizzled tensor copy per block where rows are short); the 8
 // consumer warps take one slice of K each, and their partial sums meet in shared memory in a fixed order. Every wait is bounded.
 //
 // Same operator as the reference's vnax_qmv* kernels (Shaders/verify_nax.metal:105-230); taken when K is a multiple
@@ -46,7 +47,8 @@ struct QiParams {
     int64_t ldy;
     int32_t accumulate;
     int32_t row_bytes;    // code bytes per weight row
-    int32_t row_pitch;    // ... and the padded pitch of a row inside a stage
+    int32_t row_pitch;    // the padded pitch of a row, or of a pair of rows (pair != 0), inside a stage
+    int32_t pair;         // rows are staged two per bulk copy
     int32_t srow_bytes;   // scale bytes per weight row (= bias bytes)
     int32_t srow_pitch;   // ... and their padded pitch inside a stage
     int32_t stage_bytes, nstages;
@@ -144,7 +146,10 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1)
     // instead of one per row: with rows of 1 KB (4-bit, K = 2048) the per-row copies' issue rate, about one per 35 ns and
     // SM, bounds the kernel at 0.6 of the memory roofline, the tensor copy reaches 0.8. With rows of 2 KB and more the
     // per-row copies already run at the memory's rate and start faster, so they stay.
-    // Not TM: one bulk copy per row into padded rows.
+    // Not TM: one bulk copy per row into padded rows, or (p.pair) per pair of neighbouring rows, which are one stretch of
+    // memory, the pairs padded apart and the MMA's rows g and g + 8 the two rows of pair g. Pairs measured faster for
+    // 6- and 8-bit rows (44.2 against 47.7 us on a 128000 x 2048 6-bit head), single rows for 4-bit rows of 2 KB (9.0
+    // against 9.6 us on 14336 x 4096, where the first block's arrival counts for more than the copies' number).
     static_assert(!TM || FMT == kFmtAffine4, "tensor-copy staging is built for 4-bit codes");
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* xq = smem;                                            // [groups][MS][32 lanes] uint4: B fragments
@@ -186,7 +191,8 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1)
     }
     const int items = (hi - lo + kQiRows - 1) / kQiRows;
     const int G = p.K / 64;
-    const int codes_bytes = kQiRows * p.row_pitch;
+    const bool pair = !TM && p.pair != 0;
+    const int codes_bytes = TM ? kQiRows * p.row_bytes : (pair ? kQiRows / 2 : kQiRows) * p.row_pitch;
     const int sc_bytes = kQiRows * p.srow_pitch;
 
     // ---- tail pieces: (left-over block, K slice), one warp per piece, weights straight from global memory. Run by a
@@ -309,6 +315,13 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1)
             const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
             if (TM) {
                 if (lane == 0) tma_load_3d(st, &wmap, bar_full + 8 * s, 0, r0, 0);
+            } else if (pair) {
+                if (2 * lane < rows) {  // lanes 0-7: the codes of two neighbouring rows each, one stretch of memory
+                    const unsigned char* src = p.w + (size_t)(r0 + 2 * lane) * p.row_bytes;
+                    const int bytes = min(2, rows - 2 * lane) * p.row_bytes;
+                    for (int off = 0; off < bytes; off += kQiPiece)
+                        bulk_g2s(st + lane * p.row_pitch + off, src + off, min(kQiPiece, bytes - off), bar_full + 8 * s);
+                }
             } else if (lane < rows) {  // lanes 0-15: the codes of one row each
                 const unsigned char* src = p.w + (size_t)(r0 + lane) * p.row_bytes;
                 for (int off = 0; off < p.row_bytes; off += kQiPiece)
@@ -426,9 +439,12 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1)
                 const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
                 // not TM: row g of the padded stage, the lane's piece of group 0. TM: row g of the first 128-byte column
                 // this warp reads (four 4-bit groups or two 8-bit groups per column); xo[] adds the swizzled piece.
+                // Pairs: MMA rows g and g + 8 are the two rows of pair g (rows 2g and 2g + 1 of the block), which arrived as
+                // one copy; rows or pairs are padded apart so that the eight a load touches sit in different banks.
                 const uint32_t wa0 = TM ? st + g * 128 + (W8 ? g0 >> 1 : g0 >> 2) * 2048 : st + g * p.row_pitch + t * LB;
-                const uint32_t wa1 = wa0 + (TM ? 1024 : 8 * p.row_pitch);
-                const uint32_t sa0 = st + codes_bytes + g * p.srow_pitch, sa1 = sa0 + 8 * p.srow_pitch;
+                const uint32_t wa1 = wa0 + (TM ? 1024 : (pair ? p.row_bytes : 8 * p.row_pitch));
+                const uint32_t sa0 = st + codes_bytes + (pair ? 2 * g : g) * p.srow_pitch;
+                const uint32_t sa1 = sa0 + (pair ? 1 : 8) * p.srow_pitch;
 #pragma unroll
                 for (int c4 = 0; c4 < (GW > 0 ? GW : gw); c4 += 4) {
                     // scales and biases of four groups for both rows (bf16 pairs)
@@ -500,7 +516,8 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1)
                 const int c = tid >> 6, mm = (tid >> 4) & 3, r = tid & 15;
                 const int m = 4 * c + mm;
                 if (m >= p.M || r >= rows) continue;
-                const int slot = c * 64 + (4 * (r & 7) + mm) * 2 + (r >> 3);
+                // row r of the block is MMA row r / 2, half r % 2 (row pairs) or MMA row r % 8, half r / 8
+                const int slot = pair ? c * 64 + (4 * (r >> 1) + mm) * 2 + (r & 1) : c * 64 + (4 * (r & 7) + mm) * 2 + (r >> 3);
                 float v = 0.f;
                 for (int k = 0; k < ncw; k++) v += red[((it & 1) * ncw + k) * (64 * MS) + slot];
                 const size_t o = (size_t)m * p.ldy + r0 + r;
