@@ -322,10 +322,13 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1)
                     for (int off = 0; off < bytes; off += kQiPiece)
                         bulk_g2s(st + lane * p.row_pitch + off, src + off, min(kQiPiece, bytes - off), bar_full + 8 * s);
                 }
-            } else if (lane < rows) {  // lanes 0-15: the codes of one row each
-                const unsigned char* src = p.w + (size_t)(r0 + lane) * p.row_bytes;
-                for (int off = 0; off < p.row_bytes; off += kQiPiece)
-                    bulk_g2s(st + lane * p.row_pitch + off, src + off, min(kQiPiece, p.row_bytes - off), bar_full + 8 * s);
+            } else if ((lane & 15) < rows) {
+                // lanes 0-15: the first half of one row each, lanes 16-31: the second half (32 copies in flight at once
+                // bring a 2 KB-row block in sooner than 16: 8.80 against 8.95 us on 14336 x 4096)
+                const int hb = p.row_bytes >> 1, o0 = (lane >> 4) * hb;
+                const unsigned char* src = p.w + (size_t)(r0 + (lane & 15)) * p.row_bytes + o0;
+                for (int off = 0; off < hb; off += kQiPiece)
+                    bulk_g2s(st + (lane & 15) * p.row_pitch + o0 + off, src + off, min(kQiPiece, hb - off), bar_full + 8 * s);
             }
             if (lane == 16) {
                 bulk_g2s(st + codes_bytes, p.s + (size_t)r0 * p.srow_bytes, rows * p.srow_bytes, bar_full + 8 * s);
