@@ -223,7 +223,33 @@ def bench_qmv(torch, dev, peaks):
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(gbs / peaks["hbm_gbs"], 4), "frac_of_8TBs_nominal": round(gbs / 8000.0, 4),
                          "traffic": 33065984, "peak_source": peaks["source"]},  # ncu dram__bytes_read + write of one launch
-            "l2": "8 weight copies in rotation (264 MB > 126 MB L2)", "timing": "CUDA graph of 64 calls, CUDA events"}
+            "l2": "8 weight copies in rotation (264 MB > 126 MB L2)", "timing": "CUDA graph of 64 calls, CUDA events",
+            "lm_head": [{k: r[k] for k in ("workload", "us_per_call", "gbs")} | {"frac": r["roofline"]["frac"]}
+                        for r in (bench_qmv_shape(torch, dev, peaks, 128000, 2048, b) for b in (4, 6, 8))]}
+
+
+def bench_qmv_shape(torch, dev, peaks, N, K, bits, rows=1):
+    """Decode GEMV of another shape (an lm_head: `--only qmv --qmv-shape 128000,2048,4`): enough weight copies in
+    rotation to exceed L2, fp32 logits out."""
+    from ingot_b200 import synth
+    from ingot_b200.linear import VQMV
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(2)
+    one = N * (K * bits // 8 + K // 64 * 4)
+    copies = max(2, -(-300_000_000 // one))
+    ms = [synth.affine_cuda(gen, N, K, bits) for _ in range(copies)]
+    x = synth.activations_cuda(gen, rows, K)
+    y = torch.zeros(rows, N, dtype=torch.float32, device=dev)
+    us = graph_time_us(torch, lambda i: VQMV.encode(x, ms[i % copies], y, rows), 4 * copies)
+    nbytes = ms[0].weight_bytes() + rows * K * 2 + rows * N * 4
+    gbs = nbytes / us / 1e3
+    return {"workload": f"qmv x[{rows},{K}] W[{N},{K}] {bits}-bit g64, bf16 in, fp32 out", "us_per_call": round(us, 3),
+            "bytes_per_call": nbytes, "gbs": round(gbs, 1),
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None, "peak_source": peaks["source"]},
+            "l2": f"{copies} weight copies in rotation ({copies * one // 1000000} MB > 126 MB L2)",
+            "timing": f"CUDA graph of {4 * copies} calls, CUDA events"}
 
 
 def bench_qmm(torch, dev, peaks):
@@ -488,12 +514,17 @@ def main():
     ap.add_argument("--only", choices=["stack", "qmv", "qmm"], default=None,
                     help="run one part alone (small profiling runs): the MoE stack without its side results, or the "
                          "GEMV / GEMM micro-benchmarks")
+    ap.add_argument("--qmv-shape", default=None, help="with --only qmv: N,K,bits of another GEMV (an lm_head) instead of C0")
     args = ap.parse_args()
     claim_stdout()
     if args.only in ("qmv", "qmm"):
         import torch
 
         torch.cuda.set_device(0)
+        if args.only == "qmv" and args.qmv_shape:
+            n, k, bits = (int(v) for v in args.qmv_shape.split(","))
+            emit(bench_qmv_shape(torch, torch.device("cuda", 0), measured_peaks(), n, k, bits))
+            return
         fn = bench_qmv if args.only == "qmv" else bench_qmm
         emit(fn(torch, torch.device("cuda", 0), measured_peaks()))
         return
