@@ -35,7 +35,8 @@ static const float E2M1[16] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, -0.f, -
 
 static inline float e8m0_to_f32(uint8_t s) { return s == 255 ? NAN : ldexpf(1.0f, (int)s - 127); }
 
-/* Dequantises one weight row (K inputs) into out. mode 0: affine (bits 4/8, group), mode 1: mxfp4. */
+/* Dequantises one weight row (K inputs) into out. mode 0: affine (bits 4/8, or 6 as one little-endian bit stream with
+ * value k in bits 6k.. of the row, Loader/Quant.swift:126-136; group 64 or 32), mode 1: mxfp4. */
 static void dequant_row(const uint32_t* w, const void* scales, const uint16_t* biases, int mode, int bits, int group,
                         int K, float* out) {
     if (mode == 1) {
@@ -50,7 +51,15 @@ static void dequant_row(const uint32_t* w, const void* scales, const uint16_t* b
     const int per = 32 / bits;
     const uint32_t mask = (1u << bits) - 1u;
     for (int k = 0; k < K; k++) {
-        const uint32_t q = (w[k / per] >> (bits * (k % per))) & mask;
+        uint32_t q;
+        if (32 % bits != 0) {
+            const int bit = bits * k, wi = bit / 32, o = bit % 32;
+            uint64_t v = (uint64_t)w[wi] >> o;
+            if (o + bits > 32) v |= (uint64_t)w[wi + 1] << (32 - o);
+            q = (uint32_t)v & mask;
+        } else {
+            q = (w[k / per] >> (bits * (k % per))) & mask;
+        }
         out[k] = bf16_to_f32(s[k / group]) * (float)q + bf16_to_f32(biases[k / group]);
     }
 }

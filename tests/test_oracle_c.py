@@ -15,6 +15,16 @@ def test_qmm_affine(bits):
     assert qref.max_rel(y, qref.qmm_affine(x, w[0], s[0], b[0], bits)) <= 1e-5
 
 
+@pytest.mark.parametrize("bits,group", [(4, 32), (6, 64)])
+def test_qmm_affine_other_formats(bits, group):
+    """Groups of 32 and the 6-bit bit stream, the formats of the reference's q4-g32 and lfm-qmv6 kernel cases."""
+    rng = np.random.default_rng(10 * bits + group)
+    w, s, b = synth.affine_np(rng, 48, 256, bits, 1, group)
+    x = synth.activations_np(rng, 3, 256)
+    y, _ = cref.qmm(x, w[0], s[0], b[0], "affine", bits, group)
+    assert qref.max_rel(y, qref.qmm_affine(x, w[0], s[0], b[0], bits, group)) <= 1e-5
+
+
 def test_qmm_mxfp4():
     rng = np.random.default_rng(7)
     w, s = synth.mxfp4_np(rng, 64, 288)
