@@ -14,3 +14,9 @@ def test_dense_q_rejects_cpu_tensors():
 
 def test_vqmv_has_the_reference_row_limit():
     assert VQMV.MAX_ROWS == 16
+
+
+def test_bf16_table_and_embedding_have_no_cpu_path():
+    t = torch.zeros(8, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA"):
+        DenseQ(t, None, None, 8, 64, 16)
