@@ -201,3 +201,30 @@ def test_malformed_files_are_format_errors(tmp_path):
     with pytest.raises(loader.SafetensorsError) as ex:
         loader.SafetensorsStore(str(tmp_path))
     assert ex.value.kind == "io"
+
+
+def test_groups_of_32_and_6_bits_load_as_they_are(tmp_path):
+    """A 4-bit matrix with groups of 32 (from its config entry) and a 6-bit one (bits read off the shapes: 6 K / 32 words
+    per row): the host arrays are the checkpoint's, and dequantise to the same weights. Groups of 32 with 8 bits, which
+    no kernel takes, are refused (Layers/Linear.swift:58-63)."""
+    rng = np.random.default_rng(32)
+    t, raw = {}, {}
+    for name, (N, K, bits, gs) in {"m.q32": (48, 256, 4, 32), "m.head6": (64, 128, 6, 64), "m.bad": (16, 128, 8, 32)}.items():
+        d, r = affine_layer(rng, name, N, K, bits, gs=gs)
+        t.update(d)
+        raw[name] = r
+    write_safetensors(tmp_path / "model.safetensors", t)
+    cfg = loader.ModelConfig({"quantization": {"group_size": 64, "bits": 4, "m.q32": {"group_size": 32, "bits": 4},
+                                               "m.head6": {"group_size": 64, "bits": 6},
+                                               "m.bad": {"group_size": 32, "bits": 8}}})
+    st = loader.SafetensorsStore(str(tmp_path))
+    h = loader.dense_q(st, cfg, ["m.q32"])
+    assert (h.N, h.K, h.bits, h.gs) == (48, 256, 4, 32) and h.s.shape == (48, 8)
+    w, s, b = raw["m.q32"]
+    assert np.array_equal(qref.dequant_affine(h.w, h.s, h.b, 4, 32), qref.dequant_affine(w, s, b, 4, 32))
+    h6 = loader.dense_q(st, cfg, ["m.head6"])
+    assert (h6.N, h6.K, h6.bits, h6.gs) == (64, 128, 6, 64) and h6.w.shape == (64, 24)
+    w, s, b = raw["m.head6"]
+    assert np.array_equal(h6.w, w) and np.array_equal(qref.dequant_affine(h6.w, h6.s, h6.b, 6), qref.dequant_affine(w, s, b, 6))
+    with pytest.raises(loader.SafetensorsError):
+        loader.dense_q(st, cfg, ["m.bad"])
