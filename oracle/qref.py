@@ -338,3 +338,80 @@ def topk64(row: np.ndarray, temperature: float, k: int = 64):
 def argmax_rows(x: np.ndarray) -> np.ndarray:
     """Index of the largest value of each row, ties to the lower index (verify.metal:525-547)."""
     return np.argmax(np.asarray(x, dtype=np.float32), axis=1).astype(np.uint32)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Formats whose kernels are not built yet. PARITY UNPINNED: the reference stores no vectors for them (its tests draw
+# random tensors and compare with the CPU code restated below); what pins these functions is the algebra checked in
+# tests/test_oracle_formats.py (H H = n I, the rotation against an explicit Hadamard matrix, the embedding's inverse).
+
+
+def fwht(v: np.ndarray) -> np.ndarray:
+    """Unnormalised Sylvester Walsh-Hadamard transform over the last axis (a power of two), float32 arithmetic in the
+    order of the reference's butterfly (Tests/IngotTests/KernelHarness.swift:196-210)."""
+    v = np.array(v, dtype=np.float32, copy=True)
+    n = v.shape[-1]
+    assert n & (n - 1) == 0
+    h = 1
+    while h < n:
+        w = v.reshape(*v.shape[:-1], n // (2 * h), 2, h)
+        a, b = w[..., 0, :].copy(), w[..., 1, :].copy()
+        w[..., 0, :] = a + b
+        w[..., 1, :] = a - b
+        h *= 2
+    return v
+
+
+def rotate_input(x: np.ndarray, signs: np.ndarray, block: int = 1024) -> np.ndarray:
+    """The ternary layers' input rotation: x <- H_1024(x * signs) / 32 per block of 1024 inputs, rounded to fp16
+    (had_rows_h, Shaders/xc_tern.metal:29-40; CPU.rotate, KernelHarness.swift:212-224)."""
+    x = np.asarray(x, dtype=np.float32)
+    rows, K = x.shape
+    assert K % block == 0
+    v = (x * np.asarray(signs, dtype=np.float32)[None, :]).reshape(rows, K // block, block)
+    return round_f16((fwht(v) / np.float32(np.sqrt(block))).reshape(rows, K))
+
+
+def dequant_ternary(w: np.ndarray, scales_f16: np.ndarray) -> np.ndarray:
+    """2-bit codes q in {0, 1, 2}, sixteen per word low bits first, w = (q - 1) * s with one fp16 scale per group of 128
+    (Syn.ternary, KernelHarness.swift:125-148; embed_rows_t, xc_tern.metal:56-61). w uint32 [N, K/16], scales float16
+    [N, K/128] -> float32 [N, K]."""
+    q = unpack_q(w, 2).astype(np.float32) - np.float32(1)
+    s = np.repeat(np.asarray(scales_f16, dtype=np.float16).astype(np.float32), 128, axis=-1)
+    assert q.shape == s.shape, (q.shape, s.shape)
+    return q * s
+
+
+def embed_ternary(w: np.ndarray, scales_f16: np.ndarray, signs: np.ndarray, tokens, block: int = 1024) -> np.ndarray:
+    """Rows of a ternary table back in the un-rotated basis: H_1024(row) / 32 * signs per block (embed_rows_t,
+    xc_tern.metal:44-65; the bonsai-embed case, KernelCaseTests.swift:133-155)."""
+    rows = dequant_ternary(w, scales_f16)[np.asarray(tokens, dtype=np.int64)]
+    T, K = rows.shape
+    v = fwht(rows.reshape(T, K // block, block)) / np.float32(np.sqrt(block))
+    return v.reshape(T, K) * np.asarray(signs, dtype=np.float32)[None, :]
+
+
+def quant_i8_rows(a: np.ndarray):
+    """Symmetric int8 per row: scale max|a| / 127 (1 for a zero row), round half to even, clamp to +-127
+    (CPU.quantI8, KernelHarness.swift:250-255). Returns (values as float32, scales)."""
+    a = np.asarray(a, dtype=np.float32)
+    amax = np.abs(a).max(axis=1)
+    sc = np.where(amax > 0, amax / np.float32(127), np.float32(1)).astype(np.float32)
+    q = np.clip(np.rint(a / sc[:, None]), -127, 127).astype(np.float32)
+    return q, sc
+
+
+def w8a8_emulated(x: np.ndarray, wf: np.ndarray, lb: int) -> np.ndarray:
+    """The lossy prefill GEMM of the serving path, emulated: unnormalised Hadamard of n = 32 * 2^lb per contiguous block of
+    x and of W, int8 per row, Y = (Xq Wq^T) sx sw / n (CPU.w8a8, KernelHarness.swift:225-248; the kernel case takes
+    lb = 3 when K / 32 is a multiple of 32, else 0: KernelCaseTests.swift:645)."""
+    x = np.asarray(x, dtype=np.float32)
+    wf = np.asarray(wf, dtype=np.float32)
+    n = 32 << lb
+    K = x.shape[1]
+    assert K % n == 0 and wf.shape[1] == K
+    rot = lambda a: fwht(a.reshape(a.shape[0], K // n, n)).reshape(a.shape[0], K)
+    xq, sx = quant_i8_rows(rot(x))
+    wq, sw = quant_i8_rows(rot(wf))
+    y = (xq.astype(np.float64) @ wq.astype(np.float64).T).astype(np.float32)
+    return y * sx[:, None] * sw[None, :] / np.float32(n)
