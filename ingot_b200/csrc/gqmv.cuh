@@ -193,7 +193,6 @@ __global__ void __launch_bounds__(RG* WK * 32) gqmv_kernel(const GqmvParams p) {
 
     const int row_words = p.K / 32 * (FMT == kFmtAffine8 ? 8 : 4);  // uint32 per weight row
     const int row_groups = p.K / F::GROUP;
-    const int nch_row = row_words / 4;                              // 16-byte chunks per row
 
     const uint4* wrow[NW][2];
     const unsigned char* srow[NW][2];

@@ -433,7 +433,6 @@ int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     const int ck = c.fmt == kFmtAffine8 ? 16 : 32;  // inputs per 16-byte chunk
     const int mh = c.max_rows > 8 ? 2 : 1;
     const int nw = c.mode == kModeGateUp ? 2 : 1;
-    const bool has_bias = c.fmt != kFmtMxfp4;
     // K tile: everything at once when the staged activations fit, else the largest multiple of 1024 that does
     int kt = c.K;
     auto smem_for = [&](int ktile, int* xs_bytes) {

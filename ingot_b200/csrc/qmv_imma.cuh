@@ -425,9 +425,7 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1)
         // TM: where the lane's piece of group q of a run of four groups sits, relative to row g of the run's first column
         uint32_t xo[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++)
-            xo[q] = W8 ? (q >> 1) * 2048 + ((((q & 1) * 4 + t) ^ g) << 4)
-                       : (((2 * q + (t >> 1)) ^ g) << 4) + ((t & 1) << 3);
+        for (int q = 0; q < 4; q++) xo[q] = (((2 * q + (t >> 1)) ^ g) << 4) + ((t & 1) << 3);
         for (int it = 0; it < items; it++) {
             const int s = it % p.nstages;
             const uint32_t ph = (it / p.nstages) & 1;
@@ -441,10 +439,10 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1)
             if (ok) {
                 const uint32_t st = smem_u32(stages + (size_t)s * p.stage_bytes);
                 // not TM: row g of the padded stage, the lane's piece of group 0. TM: row g of the first 128-byte column
-                // this warp reads (four 4-bit groups or two 8-bit groups per column); xo[] adds the swizzled piece.
+                // this warp reads (four 4-bit groups per column); xo[] adds the swizzled piece.
                 // Pairs: MMA rows g and g + 8 are the two rows of pair g (rows 2g and 2g + 1 of the block), which arrived as
                 // one copy; rows or pairs are padded apart so that the eight a load touches sit in different banks.
-                const uint32_t wa0 = TM ? st + g * 128 + (W8 ? g0 >> 1 : g0 >> 2) * 2048 : st + g * p.row_pitch + t * LB;
+                const uint32_t wa0 = TM ? st + g * 128 + (g0 >> 2) * 2048 : st + g * p.row_pitch + t * LB;
                 const uint32_t wa1 = wa0 + (TM ? 1024 : (pair ? p.row_bytes : 8 * p.row_pitch));
                 const uint32_t sa0 = st + codes_bytes + (pair ? 2 * g : g) * p.srow_pitch;
                 const uint32_t sa1 = sa0 + (pair ? 1 : 8) * p.srow_pitch;
@@ -467,8 +465,7 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1)
                             a[0][0] = o0[0]; a[0][1] = o1[0]; a[0][2] = o0[1]; a[0][3] = o1[1];
                             a[1][0] = o0[2]; a[1][1] = o1[2]; a[1][2] = o0[3]; a[1][3] = o1[3];
                         } else if (W8) {
-                            const uint32_t o = TM ? c4 * 1024 + xo[q] : grp * GB;
-                            const uint4 w0 = lds128_after(wa0 + o, tok), w1 = lds128_after(wa1 + o, tok);
+                            const uint4 w0 = lds128_after(wa0 + grp * GB, tok), w1 = lds128_after(wa1 + grp * GB, tok);
                             a[0][0] = w0.x; a[0][1] = w1.x; a[0][2] = w0.y; a[0][3] = w1.y;
                             a[1][0] = w0.z; a[1][1] = w1.z; a[1][2] = w0.w; a[1][3] = w1.w;
                         } else {

@@ -126,21 +126,21 @@ __global__ void __launch_bounds__(kQgThreads, 1)
                         bulk_g2s(dst + codes_bytes + (q == 2 ? sc_bytes : 0), src, rows * p.srow_bytes, bar_full + 8 * s);
                     }
                 }
-                continue;
-            }
-            // per matrix: one copy per row of codes (into padded rows), one for the scales, one for the biases
-            for (int j = lane; j < NW * (rows + 2); j += 32) {
-                const int i = j / (rows + 2), q = j % (rows + 2);
-                const uint32_t dst = st + i * p.mat_bytes;
-                if (q < rows) {
-                    bulk_g2s(dst + q * p.row_pitch, p.w[i] + expert * p.w_ebytes + (int64_t)(r0 + q) * p.row_bytes, p.row_bytes,
-                             bar_full + 8 * s);
-                } else if (q == rows) {
-                    bulk_g2s(dst + codes_bytes, p.s[i] + expert * p.s_ebytes + (int64_t)r0 * p.srow_bytes, rows * p.srow_bytes,
-                             bar_full + 8 * s);
-                } else {
-                    bulk_g2s(dst + codes_bytes + sc_bytes, p.b[i] + expert * p.s_ebytes + (int64_t)r0 * p.srow_bytes,
-                             rows * p.srow_bytes, bar_full + 8 * s);
+            } else {
+                // per matrix: one copy per row of codes (into padded rows), one for the scales, one for the biases
+                for (int j = lane; j < NW * (rows + 2); j += 32) {
+                    const int i = j / (rows + 2), q = j % (rows + 2);
+                    const uint32_t dst = st + i * p.mat_bytes;
+                    if (q < rows) {
+                        bulk_g2s(dst + q * p.row_pitch, p.w[i] + expert * p.w_ebytes + (int64_t)(r0 + q) * p.row_bytes, p.row_bytes,
+                                 bar_full + 8 * s);
+                    } else if (q == rows) {
+                        bulk_g2s(dst + codes_bytes, p.s[i] + expert * p.s_ebytes + (int64_t)r0 * p.srow_bytes, rows * p.srow_bytes,
+                                 bar_full + 8 * s);
+                    } else {
+                        bulk_g2s(dst + codes_bytes + sc_bytes, p.b[i] + expert * p.s_ebytes + (int64_t)r0 * p.srow_bytes,
+                                 rows * p.srow_bytes, bar_full + 8 * s);
+                    }
                 }
             }
         }
