@@ -5,6 +5,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "../../include/ingot_qmm.h"
 #include "common.cuh"
 
@@ -18,7 +21,7 @@ struct iq_ctx {
     // scratch of the GEMV's tail split (csrc/qmv_imma.cuh): a ring of kQmvTailSlots slots, one per launch in turn
     float* qmv_tail_scratch = nullptr;
     uint32_t* qmv_tail_counters = nullptr;
-    uint32_t qmv_tail_seq = 0;
+    std::atomic<uint32_t> qmv_tail_seq{0};
     // tensor maps of the GEMV's weight matrices (csrc/qmv.cu), keyed by (base, rows, row bytes): encoding one costs a
     // driver call, a decode step launches the same matrices over and over
     struct QmvMap {
@@ -28,6 +31,7 @@ struct iq_ctx {
     };
     static constexpr int kQmvMaps = 256;
     QmvMap* qmv_maps = nullptr;  // host array [kQmvMaps], allocated on first use
+    std::mutex qmv_maps_lock;    // several host threads may launch on one context
     char last_error[256] = {0};
 };
 
@@ -53,8 +57,8 @@ int32_t format_of(const iq_qlinear* m);
 // brings a block of rows into shared memory as [column][row][128 bytes] with the rows of a column in different banks.
 int32_t make_map_rowblock(iq_ctx* ctx, CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                           uint32_t box_rows);
-// The same through the context's cache; nullptr (with the error recorded) when the encoding fails.
-const CUtensorMap* cached_rowblock_map(iq_ctx* ctx, const void* base, int64_t rows, int32_t row_bytes, int32_t box_rows);
+// The same through the context's cache, copied into *out; an error code (with the message recorded) when the encoding fails.
+int32_t cached_rowblock_map(iq_ctx* ctx, const void* base, int64_t rows, int32_t row_bytes, int32_t box_rows, CUtensorMap* out);
 
 struct Tile;
 // One launch of the gqmv family. mode: 0 plain, 1 gate/up, 2 down. `max_rows` bounds the rows of any tile (<= 16).

@@ -104,16 +104,19 @@ int32_t make_map_rowblock(iq_ctx* ctx, CUtensorMap* map, const void* base, uint6
     return kOk;
 }
 
-const CUtensorMap* cached_rowblock_map(iq_ctx* ctx, const void* base, int64_t rows, int32_t row_bytes, int32_t box_rows) {
+int32_t cached_rowblock_map(iq_ctx* ctx, const void* base, int64_t rows, int32_t row_bytes, int32_t box_rows, CUtensorMap* out) {
+    std::lock_guard<std::mutex> hold(ctx->qmv_maps_lock);
     if (ctx->qmv_maps == nullptr) ctx->qmv_maps = new iq_ctx::QmvMap[iq_ctx::kQmvMaps];
     const uintptr_t key = reinterpret_cast<uintptr_t>(base);
     iq_ctx::QmvMap& e = ctx->qmv_maps[((key >> 8) ^ (key >> 20) ^ (uintptr_t)rows ^ (uintptr_t)box_rows) % iq_ctx::kQmvMaps];
     if (e.base != base || e.rows != rows || e.row_bytes != row_bytes || e.box_rows != box_rows) {
         e.base = nullptr;
-        if (make_map_rowblock(ctx, &e.map, base, (uint64_t)rows, (uint64_t)row_bytes, (uint32_t)box_rows) != kOk) return nullptr;
+        const int32_t r = make_map_rowblock(ctx, &e.map, base, (uint64_t)rows, (uint64_t)row_bytes, (uint32_t)box_rows);
+        if (r != kOk) return r;
         e.base = base; e.rows = (int32_t)rows; e.row_bytes = row_bytes; e.box_rows = box_rows;
     }
-    return &e.map;
+    *out = e.map;
+    return kOk;
 }
 
 int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {

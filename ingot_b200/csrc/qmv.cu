@@ -196,14 +196,12 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     p.x_dtype = c.x_dtype; p.ldx = c.ldx;
     p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
     p.status = ctx->d_status;
-    const CUtensorMap* map = nullptr;
-    static const CUtensorMap no_map = {};
+    CUtensorMap wmap = {};
+    const CUtensorMap* map = &wmap;
     if (tm) {
         // the matrix as the kernel sees it: all rows of W, whatever prefix of them this call computes
-        map = cached_rowblock_map(ctx, p.w, c.N, p.row_bytes, kQiRows);
-        if (map == nullptr) return kErrCuda;
-    } else {
-        map = &no_map;
+        const int32_t r = cached_rowblock_map(ctx, p.w, c.N, p.row_bytes, kQiRows, &wmap);
+        if (r != kOk) return r;
     }
     const int blocks = c.N / kQiRows;
     // Tail split, decided from the matrix and the GPU alone (not from the row count, so a row sees the same arithmetic
@@ -239,7 +237,7 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
         cfg.gridDim = dim3(blocks < ctx->sms * ctas ? blocks : ctx->sms * ctas, 1, 1);
         p.tail_blocks = 0;
         if (tail_slices > 0) {
-            const uint32_t slot = ctx->qmv_tail_seq++ % kQmvTailSlots;
+            const uint32_t slot = ctx->qmv_tail_seq.fetch_add(1) % kQmvTailSlots;
             p.tail_blocks = tail;
             p.tail_slices = tail_slices;
             p.blocks_per_cta = per2 * (2 / ctas);
@@ -341,13 +339,13 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
     p.w_ebytes = c.w_estride * 4;
     p.s_ebytes = c.s_estride * 2;
     p.expert_lo = c.expert_lo;
-    static const CUtensorMap no_map = {};
-    const CUtensorMap* maps[2] = {&no_map, &no_map};
+    CUtensorMap wmaps[2] = {};
+    const CUtensorMap* maps[2] = {&wmaps[0], &wmaps[1]};
     if (tm) {
         for (int i = 0; i < nw; i++) {
-            maps[i] = cached_rowblock_map(ctx, p.w[i] + (int64_t)c.expert_lo * p.w_ebytes, (int64_t)c.expert_count * c.N,
-                                          p.row_bytes, 16 * p.rgs);
-            if (maps[i] == nullptr) return kErrCuda;
+            const int32_t r = cached_rowblock_map(ctx, p.w[i] + (int64_t)c.expert_lo * p.w_ebytes, (int64_t)c.expert_count * c.N,
+                                                  p.row_bytes, 16 * p.rgs, &wmaps[i]);
+            if (r != kOk) return r;
         }
     }
     p.N = c.N; p.K = c.K;
