@@ -47,6 +47,21 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def profiled_traffic(filename: str):
+    """DRAM bytes (read + write) of one launch as an ncu capture recorded them: the `traffic_bytes_per_launch:` line of a
+    summary under profiles/. Returns (bytes or None, "profiles/<file>" or None); a missing file or line gives None, so a
+    number never outlives the summary it came from."""
+    import re
+
+    path = os.path.join(ROOT, "profiles", filename)
+    try:
+        with open(path) as f:
+            m = re.search(r"traffic_bytes_per_launch:\s*(\d+)", f.read())
+    except OSError:
+        return None, None
+    return (int(m.group(1)), "profiles/" + filename) if m else (None, None)
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -163,14 +178,17 @@ def time_steps(torch, dist, world, fn, steps, warmup):
     return ms
 
 
-def graph_time_us(torch, fn, n_in_graph: int, reps: int = 20) -> float:
+def graph_time_us(torch, fn, n_in_graph: int, reps: int = 20, dist=None, world: int = 1) -> float:
     """Average device time of one call of fn(i): n_in_graph calls captured into a CUDA graph and replayed, which takes
-    the host's launch cost out of a microsecond-scale kernel's timing."""
+    the host's launch cost out of a microsecond-scale kernel's timing. With world > 1 every rank makes the same calls
+    (kernels that meet at a barrier included) and the result is the maximum over the ranks."""
     s = torch.cuda.Stream()
     with torch.cuda.stream(s):
         for i in range(3):
             fn(i)
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=s):
             for i in range(n_in_graph):
@@ -178,17 +196,54 @@ def graph_time_us(torch, fn, n_in_graph: int, reps: int = 20) -> float:
         for _ in range(3):
             g.replay()
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(reps):
             g.replay()
         e1.record()
         torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / (reps * n_in_graph) * 1e3
+    us = e0.elapsed_time(e1) / (reps * n_in_graph) * 1e3
+    if world > 1:
+        t = torch.tensor([us], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item())
+    return us
+
+
+def count_own_kernels(graph):
+    """Kernel nodes of a captured CUDA graph that are this library's kernels (namespace iq): the launches one replay
+    makes. Returns (own, all kernel nodes), or (None, None) when the graph cannot be inspected."""
+    try:
+        from cuda.bindings import runtime as rt
+
+        raw = graph.raw_cuda_graph()
+        raw = raw if isinstance(raw, rt.cudaGraph_t) else rt.cudaGraph_t(int(raw))
+        err, _, n = rt.cudaGraphGetNodes(raw, 0)
+        if int(err) != 0 or n == 0:
+            return None, None
+        err, nodes, n = rt.cudaGraphGetNodes(raw, n)
+        own = total = 0
+        for node in nodes[:n]:
+            err, ty = rt.cudaGraphNodeGetType(node)
+            if int(err) != 0 or ty != rt.cudaGraphNodeType.cudaGraphNodeTypeKernel:
+                continue
+            total += 1
+            err, prm = rt.cudaGraphKernelNodeGetParams(node)
+            name = b""
+            if int(err) == 0:
+                err, name = rt.cudaFuncGetName(prm.func)
+                name = name if int(err) == 0 and name else b""
+            if b"iq" in name:
+                own += 1
+        return own, total
+    except Exception:
+        return None, None
 
 
 def capture(torch, fn):
-    """Captures fn() (kernel launches only, no host synchronisation) into a CUDA graph and returns its replay: the step
+    """Captures fn() (kernel launches only, no host synchronisation) into a CUDA graph and returns the graph: the step
     then costs one launch on the host, which is what a serving loop does with a fixed-shape step."""
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
@@ -196,12 +251,19 @@ def capture(torch, fn):
         for _ in range(2):
             fn()
         torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
+        try:
+            g = torch.cuda.CUDAGraph(keep_graph=True)  # the graph stays inspectable (launch count)
+        except TypeError:
+            g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=s):
             fn()
+        try:
+            g.instantiate()
+        except Exception:
+            pass  # already instantiated at the end of the capture
     torch.cuda.current_stream().wait_stream(s)
     torch.cuda.synchronize()
-    return g.replay
+    return g
 
 
 def bench_qmv(torch, dev, peaks):
@@ -218,11 +280,12 @@ def bench_qmv(torch, dev, peaks):
     us = graph_time_us(torch, lambda i: VQMV.encode(x, ms[i % 8], y, 1), 64)
     nbytes = ms[0].weight_bytes() + K * 2 + N * 2  # codes + scales + biases + x + y = 33,067,008 B
     gbs = nbytes / us / 1e3
+    qmv_traffic, qmv_traffic_src = profiled_traffic("qmv_imma_c0_14336x4096.md")
     return {"workload": "qmv x[1,4096] W[14336,4096] 4-bit g64, bf16 in/out", "us_per_call": round(us, 3),
             "bytes_per_call": nbytes, "gbs": round(gbs, 1),
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(gbs / peaks["hbm_gbs"], 4), "frac_of_8TBs_nominal": round(gbs / 8000.0, 4),
-                         "traffic": 33065984, "peak_source": peaks["source"]},  # ncu dram__bytes_read + write of one launch
+                         "traffic": qmv_traffic, "traffic_source": qmv_traffic_src, "peak_source": peaks["source"]},
             "l2": "8 weight copies in rotation (264 MB > 126 MB L2)", "timing": "CUDA graph of 64 calls, CUDA events",
             "lm_head": [{k: r[k] for k in ("workload", "us_per_call", "gbs")} | {"frac": r["roofline"]["frac"]}
                         for r in (bench_qmv_shape(torch, dev, peaks, 128000, 2048, b) for b in (4, 6, 8))]}
@@ -278,6 +341,150 @@ def bench_qmm(torch, dev, peaks):
             "cases": res}
 
 
+def layer0_host_weights(torch, dev):
+    """The first layer's full tensors (all 128 experts) as the stack draws them (seed 0), on the host, for the checker."""
+    import numpy as np
+
+    from ingot_b200 import synth
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0)
+    router = synth.router_cuda(gen, E, D).float().cpu().numpy()
+    mats = []
+    for (n, k) in ((I, D), (I, D), (D, I)):
+        full = synth.affine_cuda(gen, n, k, 4, E)
+        mats.append((full.w.cpu().numpy().view(np.uint32), full.s.view(torch.int16).cpu().numpy().view(np.uint16),
+                     full.b.view(torch.int16).cpu().numpy().view(np.uint16)))
+        del full
+    return router, mats
+
+
+def parity_check(torch, dist, dev, stack, r0_dev, t_n, world, return_dtype):
+    """Before anything is timed: the stack's first layer on this rank's tokens against the CPU oracle (the checker, never
+    the thing measured). Routing indices of every token bit for bit against oracle.qref.route; the layer's update on
+    32 sampled tokens against the C oracle's MoE FFN within 1e-3 (max|d| / max|ref|). Worst rank reported."""
+    import numpy as np
+
+    from ingot_b200 import ep
+    from oracle import cref, qref
+
+    l0 = stack.layers[0]
+    r = r0_dev.clone()
+    before = r.cpu().numpy().copy()
+    ep.rmsnorm(r, stack.xn, t_n)
+    l0.encode(stack.xn, r, t_n, accumulate=True)
+    torch.cuda.synchronize()
+    xn = stack.xn[:t_n].float().cpu().numpy()
+    got_inds = l0.layer.views(t_n)["inds"].cpu().numpy().astype(np.uint32)
+    upd = r.cpu().numpy() - before
+    router, mats = layer0_host_weights(torch, dev)
+    inds, wts = qref.route(qref.router_logits(xn, router), TOPK)
+    inds_exact = bool(np.array_equal(got_inds, inds))
+    rng = np.random.default_rng(99)
+    sel = np.sort(rng.choice(t_n, size=min(32, t_n), replace=False))
+    cref.set_threads(max(1, cref.host_threads() // max(world, 1)))
+    ref, _ = cref.moe_ffn(xn[sel], inds[sel], wts[sel], mats[0], mats[1], mats[2], "affine")
+    max_rel = float(qref.max_rel(upd[sel], ref))
+    if world > 1:
+        t = torch.tensor([max_rel, 0.0 if inds_exact else 1.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        max_rel, inds_exact = float(t[0].item()), bool(t[1].item() == 0.0)
+    return {"max_rel": round(max_rel, 7), "tolerance": 1e-3, "inds_exact": inds_exact, "sampled_tokens_per_rank": int(len(sel)),
+            "layer": "first layer of the stack, this rank's tokens, against oracle/ (C + numpy restatement)",
+            "return_dtype": {torch.float16: "f16", torch.float32: "f32"}[return_dtype] if world > 1 else "n/a"}
+
+
+def piece_times(torch, dist, world, stack, r, t_n):
+    """Device time of every piece of one layer (the first), each captured eight times in a CUDA graph of its own and
+    replayed, max over ranks; the pieces run on the state a full forward pass left behind."""
+    l0 = stack.layers[0]
+    L, xn = l0.layer, stack.xn
+    from ingot_b200 import ep
+
+    stack.forward(r.clone(), t_n)
+    torch.cuda.synchronize()
+    tm = lambda fn: round(graph_time_us(torch, lambda i: fn(), 8, reps=5, dist=dist, world=world), 2)
+    out = {"norm": tm(lambda: ep.rmsnorm(r, xn, t_n)),
+           "router": tm(lambda: L.encode(xn, r, t_n, only="router")),
+           "route": tm(lambda: L.encode(xn, r, t_n, only="route")),
+           "group": tm(lambda: L.encode(xn, r, t_n, only="group"))}
+    if world == 1:
+        out["gateup"] = tm(lambda: L.encode(xn, r, t_n, only="gateup"))
+        out["down"] = tm(lambda: L.encode(xn, r, t_n, only="down"))
+        out["combine"] = tm(lambda: L.encode(xn, r, t_n, only="combine"))
+        return out
+    dx, b, k = l0.dx, l0.buf, L.router.top_k
+    v = L.views(t_n)
+    out["pack_push"] = tm(lambda: dx.pack_push(xn, t_n, k, v["inds"], v["pos"], v["offsets"]))
+    out["barrier_plan"] = tm(lambda: dx.barrier(then_plan=True))
+    merged = [None]
+
+    def compact():
+        merged[0] = dx.compact(b["xc_dx"], b["rows_dx"])
+
+    out["compact"] = tm(compact)
+    out["experts_gateup_down_return"] = tm(lambda: L.experts(b["xc_dx"], min(t_n * k, dx.max_rows), merged[0], 1, b["yd_dx"],
+                                                            b["ws_dx"], yd_rows=b["rows_dx"]))
+    out["barrier"] = tm(lambda: dx.barrier())
+    out["combine"] = tm(lambda: L.combine_rows(dx.back, r, t_n, accumulate=True))
+    return out
+
+
+def bench_colsplit(torch, dist, dev, rank, world, peaks):
+    """The column-split dense linear over the ranks: x[1, 4096] . W[14336, 4096]^T 4-bit (us per call, whole y on every
+    rank) and x[2048, 4096] (TFLOP/s per GPU and in total), with the library's own peer-store exchange (calls captured
+    in a CUDA graph), and the same kernels with a host-launched NCCL all-gather for comparison. Every rank draws its own
+    shard; enough shard copies rotate to exceed L2."""
+    from ingot_b200 import ep, synth
+
+    N, K = 14336, 4096
+    lo, per = ep.column_shard(rank, world, N)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(100 + rank)
+    one = per * (K // 2 + K // 64 * 4)
+    copies = max(2, -(-300_000_000 // one))
+    shards = [synth.affine_cuda(gen, per, K, 4) for _ in range(copies)]
+    res = {"workload": f"W[14336,4096] 4-bit g64 split {world} ways by output features ({per} per GPU), y fp32 on every rank",
+           "l2": f"{copies} shard copies in rotation ({copies * one // 1000000} MB per GPU)"}
+    for tag, M in (("decode", 1), ("prefill", 2048)):
+        x = synth.activations_cuda(gen, M, K)
+        entry = {"rows": M}
+        for exchange in ("device", "nccl"):
+            try:
+                lin = ep.ColumnSplitLinear(shards[0], N, None, M, exchange=exchange)
+
+                def call(i):
+                    lin.shard = shards[i % copies]
+                    lin.encode(x, M)
+
+                if exchange == "device":
+                    n_graph = 4 * copies if M == 1 else 4
+                    us = graph_time_us(torch, call, n_graph, reps=5 if M == 1 else 3, dist=dist, world=world)
+                else:  # the library collective is launched by the host, call by call, as a caller would
+                    n_calls = 50 if M == 1 else 8
+                    us = time_steps(torch, dist, world, lambda: [call(i) for i in range(n_calls)], 3, 1) * 1e3 / n_calls
+                entry[exchange + "_us"] = round(us, 2)
+                lin.close()
+                del lin
+            except Exception as exc:  # the comparison arm must not take the bench down
+                entry[exchange + "_us"] = None
+                entry[exchange + "_error"] = repr(exc)[:200]
+        us = entry.get("device_us")
+        if us:
+            if M == 1:
+                gb = (one + K * 2 + N * 4) / us / 1e3  # per GPU: its shard + x in, the whole y out
+                entry["gbs_per_gpu"] = round(gb, 1)
+                entry["frac_hbm_per_gpu"] = round(gb / peaks["hbm_gbs"], 4)
+            else:
+                tf = 2.0 * M * N * K / us / 1e6
+                entry["tflops_total"] = round(tf, 1)
+                entry["tflops_per_gpu"] = round(tf / world, 1)
+                entry["frac_burst_per_gpu"] = round(tf / world / peaks["bf16_tflops"], 4)
+                entry["allgather_bytes_per_gpu"] = int(M * per * 4 * (world - 1))
+        res[tag] = entry
+    return res
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -307,32 +514,32 @@ def run_ours(args):
     r = torch.empty_like(r0_dev)
     out_pinned = torch.empty_like(r0_pinned).pin_memory()
 
-    def step():
+    # parity first: nothing below is worth a number if the layer differs from the oracle
+    parity = None
+    if args.layers > 0 and not args.no_parity:
+        if world > 1:
+            dist.barrier()
+        parity = parity_check(torch, dist, dev, stack, r0_dev, t_n, world, RETURN_DTYPE(torch))
+
+    def step_eager():
         r.copy_(r0_dev)
         stack.forward(r, t_n)
 
+    # no host synchronisation inside a step, on one GPU or many: one CUDA graph per step
+    if world > 1:
+        dist.barrier()
+    step_graph = capture(torch, step_eager)
+    fwd_graph = capture(torch, lambda: stack.forward(r, t_n))
+    own_launches, all_launches = count_own_kernels(step_graph)
+
+    def step():
+        step_graph.replay()
+
     def step_e2e():  # host buffers in, host buffer out: the public API a caller drives
         r.copy_(r0_pinned, non_blocking=True)
-        stack.forward(r, t_n)
+        fwd_graph.replay()
         out_pinned.copy_(r, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-
-    graphed = True  # no host synchronisation inside a step, on one GPU or many
-    if graphed:
-        if world > 1:
-            dist.barrier()
-        step_graph = capture(torch, step)
-        fwd_graph = capture(torch, lambda: stack.forward(r, t_n))
-        step_eager = step
-
-        def step():
-            step_graph()
-
-        def step_e2e():  # noqa: F811
-            r.copy_(r0_pinned, non_blocking=True)
-            fwd_graph()
-            out_pinned.copy_(r, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
 
     sampler = ClockSampler(local)
     if rank == 0:
@@ -352,18 +559,22 @@ def run_ours(args):
             rd.copy_(rd0)
             stack.forward(rd, d_n)
 
-        if graphed:
-            step_dec = capture(torch, step_dec)
-        ms_dec = time_steps(torch, dist, world, step_dec, max(args.steps, 3), args.warmup)
+        dec_graph = capture(torch, step_dec)
+        ms_dec = time_steps(torch, dist, world, dec_graph.replay, max(args.steps, 3), args.warmup)
         dec = {"tokens": DECODE_TOKENS, "ms_per_step": round(ms_dec, 3), "tokens_per_s": round(DECODE_TOKENS / ms_dec * 1e3, 1)}
+        if world == 1:
+            # HBM floor of one decode layer: the weights of the experts 64 tokens touch (about 126 of 128) + the router
+            floor_us = (126 * 2654208 + 524288) / (peaks["hbm_gbs"] * 1e3)
+            dec["us_per_layer"] = round(ms_dec * 1e3 / max(args.layers, 1), 2)
+            dec["hbm_floor_us_per_layer"] = round(floor_us, 2)
+            dec["frac_of_hbm_floor"] = round(floor_us / (ms_dec * 1e3 / max(args.layers, 1)), 4)
 
-    # the dominant kernel of the prefill stack: the experts' gate+up GEMM; timed alone over the layers (rank 0's share)
+    # per-piece device times of one layer (every rank takes part: the exchange pieces meet at barriers)
+    pieces = piece_times(torch, dist, world, stack, r, t_n) if args.layers > 0 else None
+
+    # the dominant kernel of the prefill stack: the experts' gate+up GEMM, timed alone over the layers at N = 1
     roof = None
-    # kernels per layer: norm, router, top-k, histogram, scan, place, pack, gate/up, down, combine; expert-parallel: norm,
-    # router, top-k, histogram, scan, place, pack+push, barrier(+plan), compact, tile list, gate/up, down, return, barrier,
-    # combine
-    launches_per_layer = 10 if world == 1 else 15
-    if world == 1:
+    if world == 1 and args.layers > 0:
         xn = stack.xn
 
         def gateup_all():
@@ -374,11 +585,17 @@ def run_ours(args):
         ms_gu = time_steps(torch, dist, 1, gateup_all, max(2, args.steps // 2), 1) / len(stack.layers)
         flops = 2.0 * t_n * TOPK * (2 * I) * D
         tf = flops / (ms_gu * 1e-3) / 1e12
+        traffic, traffic_src = profiled_traffic("qmm_tc_grouped_gateup_down_prefill4096.md") if t_n == PREFILL_TOKENS else (None, None)
         roof = {"kernel": "experts gate+up+SwiGLU (grouped)", "bound": "tensor", "achieved": round(tf, 2),
                 "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": round(tf / peaks["bf16_tflops_sustained"], 4),
-                "traffic": 405289472 if (t_n == PREFILL_TOKENS and args.layers > 0) else None,  # ncu DRAM read + write per launch
+                "traffic": traffic, "traffic_source": traffic_src,
+                "algorithmic_bytes": int(E * 2 * I * (D // 2 + D // 64 * 4) + t_n * D * 2 + t_n * TOPK * I * 2),
                 "ms_per_launch": round(ms_gu, 4), "flops_per_launch": flops,
                 "peak_source": peaks["source"] + " (sustained: the kernel runs inside a long step)"}
+
+    colsplit = None
+    if world > 1 and args.only is None:
+        colsplit = bench_colsplit(torch, dist, dev, rank, world, peaks)
 
     line = None
     if rank == 0:
@@ -386,6 +603,14 @@ def run_ours(args):
         qmm = bench_qmm(torch, dev, peaks) if args.only is None else None
         from ingot_b200 import capi
         status = capi.context(local).device_status()
+        if own_launches is not None:
+            launches = {"gpu_launches": own_launches * args.steps,
+                        "gpu_launches_source": f"{own_launches} kernel nodes of this library ({all_launches} kernel nodes in all) "
+                                               "counted in the step's CUDA graph, times the timed steps"}
+        else:
+            per_layer = 10 if world == 1 else 15
+            launches = {"gpu_launches": per_layer * args.layers * args.steps,
+                        "gpu_launches_source": "graph not inspectable: kernels per layer by the launch list x layers x steps"}
         line = {
             "metric": "moe_ffn_tokens_per_s", "value": round(T / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True,
@@ -398,12 +623,12 @@ def run_ours(args):
                        "launch": "one CUDA graph per step", "exchange": "peer stores + flag barrier (own kernels)" if world > 1 else "none"},
             "e2e": {"value": round(T / ms_e2e * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 3),
                     "h2d_bytes_per_step": int(t_n * D * 4), "d2h_bytes_per_step": int(t_n * D * 4)},
-            "gpu_launches": launches_per_layer * args.layers * args.steps,
-            "clocks": clocks, "finite": finite, "device_status": status,
+            **launches,
+            "clocks": clocks, "finite": finite, "device_status": status, "parity": parity,
             "roofline": roof if roof is not None else {"bound": "tensor", "achieved": None, "peak": peaks["bf16_tflops_sustained"],
                                                         "unit": "TFLOP/s", "frac": None, "traffic": None,
-                                                        "note": "per-kernel timing is taken at N=1"},
-            "decode": dec, "qmv": qmv, "qmm": qmm,
+                                                        "note": "the dominant kernel is timed alone at N=1; see pieces_us"},
+            "pieces_us": pieces, "decode": dec, "qmv": qmv, "qmm": qmm, "colsplit": colsplit,
         }
         if world == 1 and args.only is None:
             line["cpu_baseline"] = cpu_baseline(sample_tokens=args.cpu_tokens, reps=1)
@@ -418,19 +643,33 @@ def run_ours(args):
 # CPU arm: the C restatement of the reference's fp32 semantics, all host threads
 
 
-def cpu_layer_once(sample_tokens: int, seed: int = 0):
-    """One layer of the stack on the CPU (router logits, top-k, gate/up/SwiGLU, down, combine; dequantisation inside the
-    timed region). Returns (seconds, threads)."""
+_CPU_CASE = {}
+
+
+def cpu_layer_inputs(sample_tokens: int, seed: int = 0):
+    """Weights and activations of one layer on the host (drawn once, outside any timed region)."""
     import numpy as np
 
     from ingot_b200 import synth
+
+    key = (sample_tokens, seed)
+    if key not in _CPU_CASE:
+        rng = np.random.default_rng(seed)
+        g, u, d = synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, D, I, 4, E)
+        _CPU_CASE[key] = (g, u, d, synth.router_np(rng, E, D), synth.activations_np(rng, sample_tokens, D))
+    return _CPU_CASE[key]
+
+
+def cpu_layer_once(sample_tokens: int, seed: int = 0):
+    """One layer of the stack on the CPU (router logits, top-k, gate/up/SwiGLU, down, combine; dequantisation inside the
+    timed region) on every hardware thread of the host, whatever OMP_NUM_THREADS the launcher exported. Returns
+    (seconds, threads)."""
+    import numpy as np
+
     from oracle import cref, qref
 
-    rng = np.random.default_rng(seed)
-    g, u, d = synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, I, D, 4, E), synth.affine_np(rng, D, I, 4, E)
-    wr = synth.router_np(rng, E, D)
-    x = synth.activations_np(rng, sample_tokens, D)
-    cref.lib()
+    g, u, d, wr, x = cpu_layer_inputs(sample_tokens, seed)
+    cref.set_threads(0)
     t0 = time.perf_counter()
     logits = qref.router_logits(x, wr)
     inds, wts = cref.route(logits, E, TOPK)
@@ -446,18 +685,21 @@ def cpu_baseline(sample_tokens: int, reps: int = 1):
         dt, threads = cpu_layer_once(sample_tokens)
         best = dt if best is None else min(best, dt)
     return {"value": round(sample_tokens / (best * LAYERS), 2), "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": f"one layer of the 48 at {sample_tokens} tokens on the host ({best:.2f} s), scaled to 48 layers; "
-                      "C restatement under oracle/, OpenMP"}
+            "sample": f"one whole layer of the 48 at {sample_tokens} tokens on the host ({best:.2f} s, {threads} threads), "
+                      "scaled by 48 layers; C restatement under oracle/, OpenMP"}
 
 
 def run_reference(args):
     """The reference's CPU implementation of the path. ingot itself is Metal-only (no CPU or CUDA path to install), so
-    this is the oracle port; one step = one layer of the stack at `--cpu-tokens` tokens, scaled to 48 layers."""
+    this is the oracle port. One timed step = ONE layer of the stack at the full token count (a bounded sample: the 48
+    layers are the same work 48 times); `ms_per_step` is that step as measured, `value` the tokens/s of the 48-layer job
+    it implies (tokens / (48 x step time))."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     n = args.cpu_tokens
+    cpu_layer_inputs(n)
     for _ in range(min(args.warmup, 1)):
         cpu_layer_once(n)
     times, threads = [], 1
@@ -466,14 +708,17 @@ def run_reference(args):
         times.append(dt)
     sec = sum(times) / len(times)
     value = round(n / (sec * LAYERS), 2)
+    sample = (f"each step is one layer of the {LAYERS} at {n} tokens ({sec:.2f} s on {threads} threads); value = tokens / "
+              f"({LAYERS} x step time)")
     line = {
         "impl": "reference", "metric": "moe_ffn_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3 * LAYERS * (args.tokens / n), 1),
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": round(sec * 1e3, 1),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{LAYERS}-layer MoE FFN stack, prefill {args.tokens} tokens: 128 experts top-8 d_model 2048 "
-                               "d_ff 768 4-bit g64, r += MoE(RMSNorm(r))", "tokens": args.tokens, "layers": LAYERS},
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": f"one layer at {n} tokens per step, scaled to {LAYERS} layers"},
+                               "d_ff 768 4-bit g64, r += MoE(RMSNorm(r))", "tokens": args.tokens, "layers": LAYERS,
+                   "layers_per_timed_step": 1, "step_scaling": f"value = tokens / ({LAYERS} x ms_per_step)",
+                   "sample_tokens": n},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "ingot has no CPU or CUDA implementation to install (Swift + Metal only); this arm runs the C restatement "
                 "of its fp32 semantics kept under oracle/",
@@ -510,7 +755,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS)
     ap.add_argument("--layers", type=int, default=LAYERS)
-    ap.add_argument("--cpu-tokens", type=int, default=1024, help="tokens of the bounded CPU sample")
+    ap.add_argument("--cpu-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the CPU sample (one layer per step)")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check before the timing (profiling runs)")
     ap.add_argument("--only", choices=["stack", "qmv", "qmm"], default=None,
                     help="run one part alone (small profiling runs): the MoE stack without its side results, or the "
                          "GEMV / GEMM micro-benchmarks")

@@ -13,7 +13,7 @@
  *     [experts, n, k/group] (affine, w = scale*q + bias) or `scales` uint8 e8m0 [experts, n, k/32] and no biases (mxfp4);
  *   - every pointer is a device pointer owned by the caller; nothing is allocated, freed or synchronised in a call that
  *     takes a stream: work is enqueued on `stream` (a cudaStream_t passed as void*) and the call returns;
- *   - scratch memory is the caller's: ask for the size once (…_workspace_bytes), allocate it at layer construction
+ *   - scratch memory is the caller's (one exception: the decode GEMV's tail scratch, see iq_qmv): ask for the size once (…_workspace_bytes), allocate it at layer construction
  *     (the reference allocates its scratch at construction too, Layers/MoE.swift:220-241), pass it to every call;
  *   - every function returns 0 or a negative iq_status; iq_last_error(ctx) gives the message. Shapes the reference's
  *     launchers reject with a precondition (rows > 16 in qmv, M % 64 != 0 in qmm, …) come back as IQ_ERR_INVALID_ARG;
@@ -61,7 +61,10 @@ typedef enum iq_router_score { IQ_SCORE_SOFTMAX = 0, IQ_SCORE_SIGMOID = 1 } iq_r
 /* Shared expert: none, with a sigmoid gate per token, or with weight 1 (LAB_MOE_SHARED 0 / 1 / 2, verify.metal:165). */
 typedef enum iq_shared_kind { IQ_SHARED_NONE = 0, IQ_SHARED_GATED = 1, IQ_SHARED_UNGATED = 2 } iq_shared_kind;
 
-enum { IQ_FLAG_ACCUMULATE = 1 }; /* y += result (VQMV.encode accumulate:, encodeQmmF32 accumulate:) */
+enum {
+    IQ_FLAG_ACCUMULATE = 1, /* y += result (VQMV.encode accumulate:, encodeQmmF32 accumulate:) */
+    IQ_FLAG_NO_BARRIER = 2  /* iq_linear_colsplit: leave the flag barriers out (the host orders the ranks itself) */
+};
 
 /* A quantized matrix on the device. Replaces DenseQ (Sources/Ingot/Layers/Linear.swift:17-33) and
  * DeviceQuantizedLinear (Sources/Ingot/Loader/Quant.swift:205-231): three buffers plus N, K, bits, group size.
@@ -89,6 +92,11 @@ const char* iq_last_error(const iq_ctx* ctx);
  * (0 = none did; the word is cleared when read). The reference surfaces GPU errors at waitUntilCompleted
  * (Sources/Ingot/GPU.swift:164-167); this is the equivalent place. Not for the enqueue path. */
 int32_t iq_ctx_status(iq_ctx* ctx, int32_t* device_status);
+/* Bound, in SM clock cycles, of the waits on another GPU (the flag barriers of the expert-parallel exchange and of the
+ * column-split linear). The default, 4e9 cycles, is about two seconds; a host that watches its peers itself (a
+ * heartbeat) can shorten it so that a rank whose peer has gone comes back within milliseconds with IQ_ERR_TIMEOUT in
+ * iq_ctx_status. The reference has no counterpart (one GPU, no peer to wait for). Applies to calls enqueued afterwards. */
+int32_t iq_ctx_set_wait_cycles(iq_ctx* ctx, uint64_t cycles);
 /* ABI version of this header (bumped on incompatible changes). */
 int32_t iq_abi_version(void);
 
@@ -99,7 +107,13 @@ int32_t iq_abi_version(void);
  * x: [rows, ldx] of x_dtype (the reference takes half or float; bf16 is added because the checkpoints' activations
  * are bf16); y: [rows, ldy] of y_dtype (the reference writes float). n_prefix > 0 computes only the first n_prefix
  * output features (a multiple of 16). Requires n % 16 == 0, k % 64 == 0, ldx % 8 == 0, 16-byte aligned x.
- * The bits of row i do not depend on `rows` or on the other rows. */
+ * The bits of activation row i do not depend on `rows` or on the other rows (for a given n_prefix: a call over a prefix
+ * of the output features may sum an output feature's K slices in another order than a call over all of them).
+ * Scratch: matrices whose 16-row blocks do not divide over the GPU's CTAs sum a few left-over blocks through a small
+ * scratch area that the context owns (the one exception to "scratch is the caller's": a few hundred KB allocated at
+ * iq_ctx_create). Each stream that makes such calls holds one of 16 slots of it for the life of the context; a 17th
+ * stream is refused with IQ_ERR_INVALID_ARG. A CUDA graph keeps the slot of the stream it was captured on: two graphs
+ * captured on the same stream must not be replayed at the same time. */
 int32_t iq_qmv(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx, const iq_qlinear* m, void* y,
                int32_t y_dtype, int64_t ldy, int32_t rows, uint32_t flags, int32_t n_prefix);
 
@@ -297,6 +311,28 @@ int32_t iq_ep_return_rows(iq_ep* ep, void* stream, int32_t yd_dtype, int32_t d_m
  * with sources = 1, region_rows = 0. After iq_ep_barrier(then_plan = 1). */
 int32_t iq_ep_compact(iq_ep* ep, void* stream, const void* recv_rows, int32_t d_model, int32_t yd_dtype, void* rows_out,
                       void** table, const uint32_t** merged_counts);
+
+/* ---- column-split dense linear ---------------------------------------------------------------------------------------
+ * One dense quantized linear over the GPUs of one box: rank r holds output features [r*n/G, (r+1)*n/G) (rows of w /
+ * scales / biases: one contiguous byte range of each tensor), x is replicated, every rank ends up with the whole y.
+ * The reference runs on one GPU and has no counterpart; a shard is what its row concatenation and nPrefix calls address
+ * (Layers/Linear.swift:107-183, 350-366). The host allocates, once, on every rank, y ([max_rows, n] of y_dtype, row
+ * pitch n) and flags (uint32 [world], zeroed) in memory every peer can address and passes all ranks' addresses.
+ * iq_linear_colsplit, on every rank, in stream order: this rank's slice goes straight into its columns of its own y
+ * (iq_qmv for rows <= 16, iq_qmm for larger multiples of 64, with their preconditions and workspace); then all ranks meet
+ * (none of them still reads the previous call's y), each stores its slice into the same columns of every peer's y with
+ * 16-byte peer stores, and they meet again: when the call's kernels have run, y holds all n output features on every
+ * rank. For one to sixteen rows the exchange is one small kernel. The waits are bounded (iq_ctx_set_wait_cycles;
+ * IQ_ERR_TIMEOUT in iq_ctx_status when a peer never arrives). n a multiple of 16 * world; at most 8 ranks. With
+ * IQ_FLAG_NO_BARRIER the barriers are left out and the host must order the ranks (and the reuse of y) itself. */
+typedef struct iq_colsplit iq_colsplit;
+int32_t iq_colsplit_create(iq_ctx* ctx, int32_t rank, int32_t world, int32_t n_total, int32_t max_rows, int32_t y_dtype,
+                           void* const* peer_y, void* const* peer_flags, iq_colsplit** out);
+void iq_colsplit_destroy(iq_colsplit* cs);
+int32_t iq_linear_colsplit_workspace_bytes(iq_colsplit* cs, const iq_qlinear* shard, int32_t rows, int32_t x_dtype,
+                                           size_t* bytes);
+int32_t iq_linear_colsplit(iq_colsplit* cs, void* stream, const void* x, int32_t x_dtype, int64_t ldx,
+                           const iq_qlinear* shard, int32_t rows, uint32_t flags, void* workspace, size_t workspace_bytes);
 
 /* ---- before the first layer -------------------------------------------------------------------------------------------
  * Embedding gather: row tokens[r] of the table, dequantised as float(scale) * code + float(bias) in fp32, into out_f32

@@ -14,6 +14,7 @@ IQ_ROUTER_BF16, IQ_ROUTER_Q8 = 0, 1
 IQ_SCORE_SOFTMAX, IQ_SCORE_SIGMOID = 0, 1
 IQ_SHARED_NONE, IQ_SHARED_GATED, IQ_SHARED_UNGATED = 0, 1, 2
 IQ_FLAG_ACCUMULATE = 1
+IQ_FLAG_NO_BARRIER = 2
 IQ_PIECE_ROUTER, IQ_PIECE_ROUTE, IQ_PIECE_GROUP, IQ_PIECE_GATEUP, IQ_PIECE_DOWN, IQ_PIECE_COMBINE = 1, 2, 4, 8, 16, 32
 IQ_PIECE_ALL = 63
 
@@ -27,6 +28,8 @@ SYMBOLS = [
     "iq_ep_pack_push", "iq_ep_return_push", "iq_ep_return_rows", "iq_ep_compact",
     "iq_st_open", "iq_st_close", "iq_st_count", "iq_st_entry", "iq_st_find", "iq_st_last_error", "iq_widen4to8_words",
     "iq_scales_div16_bf16", "iq_argmax_rows", "iq_topk64_scratch_bytes", "iq_topk64", "iq_embed_rows",
+    "iq_ctx_set_wait_cycles", "iq_colsplit_create", "iq_colsplit_destroy", "iq_linear_colsplit_workspace_bytes",
+    "iq_linear_colsplit",
 ]
 
 
@@ -136,6 +139,15 @@ def lib() -> C.CDLL:
         for name in ("iq_ep_create", "iq_ep_share_counts", "iq_ep_barrier", "iq_ep_plan", "iq_ep_pack_push",
                      "iq_ep_return_push", "iq_ep_return_rows", "iq_ep_compact"):
             getattr(l, name).restype = i32
+        l.iq_ctx_set_wait_cycles.argtypes = [vp, C.c_uint64]
+        l.iq_colsplit_create.argtypes = [vp, i32, i32, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]
+        l.iq_colsplit_destroy.argtypes = [vp]
+        l.iq_colsplit_destroy.restype = None
+        l.iq_linear_colsplit_workspace_bytes.argtypes = [vp, C.POINTER(QLinear), i32, i32, C.POINTER(sz)]
+        l.iq_linear_colsplit.argtypes = [vp, vp, vp, i32, i64, C.POINTER(QLinear), i32, u32, vp, sz]
+        for name in ("iq_ctx_set_wait_cycles", "iq_colsplit_create", "iq_linear_colsplit_workspace_bytes",
+                     "iq_linear_colsplit"):
+            getattr(l, name).restype = i32
         l.iq_moe_pack_rows.argtypes = [vp, vp, vp, i32, i64, i32, vp, sz, vp]
         l.iq_moe_experts_workspace_bytes.argtypes = [vp, i32, i32, C.POINTER(sz)]
         l.iq_moe_experts.argtypes = [vp, vp, vp, i32, i32, vp, i32, i32, vp, i32, vp, vp, sz]
@@ -175,6 +187,10 @@ class Context:
         v = C.c_int32(0)
         self.check(lib().iq_ctx_status(self._h, C.byref(v)))
         return v.value
+
+    def set_wait_cycles(self, cycles: int):
+        """Bound of the waits on another GPU, in SM clock cycles (iq_ctx_set_wait_cycles)."""
+        self.check(lib().iq_ctx_set_wait_cycles(self._h, cycles))
 
     def close(self):
         if self._h:

@@ -40,6 +40,9 @@ extern "C" const char* iq_strerror(int32_t status) {
         case kErrNoKernel: return "no kernel for this configuration";
         case kErrTimeout: return "device-side wait timed out";
         case kErrComm: return "communication error";
+        case IQ_ERR_IO: return "file could not be opened, mapped or read";
+        case IQ_ERR_FORMAT: return "not a safetensors file or inconsistent header";
+        case IQ_ERR_MISSING: return "no such tensor";
         default: return "unknown status";
     }
 }
@@ -97,6 +100,13 @@ extern "C" void iq_ctx_destroy(iq_ctx* ctx) {
     if (ctx->qmv_tail_counters) cudaFree(ctx->qmv_tail_counters);
     delete[] ctx->qmv_maps;
     delete ctx;
+}
+
+extern "C" int32_t iq_ctx_set_wait_cycles(iq_ctx* ctx, uint64_t cycles) {
+    if (ctx == nullptr) return kErrInvalidArg;
+    if (cycles < 1000) return fail(ctx, kErrInvalidArg, "wait bound of %llu cycles (at least 1000)", (unsigned long long)cycles);
+    ctx->wait_cycles = cycles;
+    return kOk;
 }
 
 extern "C" int32_t iq_ctx_status(iq_ctx* ctx, int32_t* device_status) {

@@ -10,13 +10,13 @@
 #include <new>
 
 #include "internal.h"
+#include "peer.cuh"
 #include "ptx.cuh"
 
 namespace iq {
 
 namespace {
 
-constexpr int kMaxRanks = 8;
 constexpr int kMaxSegs = kMaxRanks * 512;
 
 // Receive-buffer layout: every source rank owns a fixed region of region_rows rows in each peer's receive buffer, so a
@@ -74,10 +74,6 @@ __global__ void __launch_bounds__(32) ep_plan_kernel(const uint32_t* __restrict_
                                                      uint32_t region_rows, EpPlan* __restrict__ plan) {
     ep_plan_body(counts, rank, world, E, region_rows, plan);
 }
-
-struct PeerPtrs {
-    void* p[kMaxRanks];
-};
 
 // Rows of this rank, packed as fp16 in expert order, written straight into region `rank` of the owners' receive
 // buffers; the first `world` blocks also write this rank's per-expert counts into row `rank` of every peer's count
@@ -207,30 +203,15 @@ __global__ void ep_share_counts_kernel(const uint32_t* __restrict__ offsets, Pee
 // replayed from a CUDA graph. The wait is bounded: on a timeout the status word is set and the kernel returns.
 // With plan != nullptr the kernel goes on to derive this rank's plan from the count matrix the peers have just completed.
 __global__ void ep_barrier_kernel(PeerPtrs flags, uint32_t* epoch, int rank, int world, int32_t* status,
-                                  const uint32_t* counts, int E, uint32_t region_rows, EpPlan* plan) {
+                                  const uint32_t* counts, int E, uint32_t region_rows, EpPlan* plan,
+                                  unsigned long long wait_cycles) {
     __shared__ uint32_t e;
     if (threadIdx.x == 0) {
         e = *epoch + 1;
         *epoch = e;
-        __threadfence_system();  // everything this rank wrote to its peers before the barrier is ordered before the flag
     }
     __syncthreads();
-    if ((int)threadIdx.x < world) {
-        volatile uint32_t* remote = static_cast<volatile uint32_t*>(flags.p[threadIdx.x]) + rank;
-        *remote = e;
-    }
-    if ((int)threadIdx.x < world) {
-        volatile uint32_t* mine = static_cast<volatile uint32_t*>(flags.p[rank]) + threadIdx.x;
-        const long long t0 = clock64();
-        while ((int32_t)(*mine - e) < 0) {
-            if ((unsigned long long)(clock64() - t0) > kWaitCycles) {
-                atomicExch(status, kErrTimeout);
-                break;
-            }
-        }
-    }
-    __syncthreads();
-    __threadfence_system();
+    peer_flag_barrier(flags, e, rank, world, status, wait_cycles);
     if (plan != nullptr) ep_plan_body(counts, rank, world, E, region_rows, plan);
 }
 
@@ -305,7 +286,7 @@ extern "C" int32_t iq_ep_barrier(iq_ep* ep, void* stream, int32_t then_plan) {
     if (ep == nullptr) return kErrInvalidArg;
     ep_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         ep->flags, ep->epoch, ep->rank, ep->world, ep->ctx->d_status, static_cast<const uint32_t*>(ep->counts.p[ep->rank]),
-        ep->experts, (uint32_t)ep->region_rows, then_plan ? ep->plan : nullptr);
+        ep->experts, (uint32_t)ep->region_rows, then_plan ? ep->plan : nullptr, ep->ctx->wait_cycles);
     return check_cuda(ep->ctx, cudaGetLastError(), "ep_barrier launch");
 }
 

@@ -18,10 +18,18 @@ struct iq_ctx {
     // cuTensorMapEncodeTiled, resolved through the runtime so that the library does not link libcuda directly
     void* encode_tiled = nullptr;
     int32_t* d_status = nullptr;  // device status word written by kernels whose bounded waits gave up
-    // scratch of the GEMV's tail split (csrc/qmv_imma.cuh): a ring of kQmvTailSlots slots, one per launch in turn
+    // bound, in SM clock cycles, of the waits on another GPU (the flag barrier of the expert-parallel exchange and of the
+    // column-split linear); iq_ctx_set_wait_cycles changes it
+    unsigned long long wait_cycles = 4000000000ull;
+    // scratch of the GEMV's tail split (csrc/qmv_imma.cuh): kQmvTailSlots slots
     float* qmv_tail_scratch = nullptr;
     uint32_t* qmv_tail_counters = nullptr;
-    std::atomic<uint32_t> qmv_tail_seq{0};
+    // one slot of the ring per stream that has launched a tail-split GEMV (launches of one stream run in series, so they
+    // can share a slot; different streams may overlap and must not)
+    static constexpr int kTailSlots = 16;
+    void* qmv_tail_streams[kTailSlots] = {nullptr};
+    int qmv_tail_stream_count = 0;
+    std::mutex qmv_tail_lock;
     // tensor maps of the GEMV's weight matrices (csrc/qmv.cu), keyed by (base, rows, row bytes): encoding one costs a
     // driver call, a decode step launches the same matrices over and over
     struct QmvMap {
@@ -37,7 +45,7 @@ struct iq_ctx {
 
 namespace iq {
 
-constexpr int kQmvTailSlots = 16;         // launches whose tail scratch may be live at once (different streams)
+constexpr int kQmvTailSlots = iq_ctx::kTailSlots;  // streams whose tail-split launches may overlap
 constexpr int kQmvTailPieces = 512;       // at most this many (block, K slice) pieces per launch
 constexpr int kQmvTailBlocks = 64;        // ... over at most this many 16-row blocks
 
@@ -73,6 +81,7 @@ struct GqmvCall {
     // which experts the stacked tensors hold (w[] is offset so that a global expert id indexes it); 0 experts: not known
     int32_t expert_lo = 0, expert_count = 0;
     int32_t N = 0, K = 0;
+    int32_t n_full = 0;  // rows of the whole matrix when N is a prefix of it (0: N)
     const void* x = nullptr;
     int32_t x_dtype = 0;
     int64_t ldx = 0;

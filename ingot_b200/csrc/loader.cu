@@ -211,9 +211,15 @@ extern "C" int32_t iq_st_open(const char* path, iq_st** out) {
                     iq_st_close(f);
                     return st_fail(IQ_ERR_FORMAT, "format: malformed entry: %s", nm.c_str());
                 }
+                // element count times element size, refused when the product leaves 64 bits (the reference's Swift
+                // multiplication traps there): a wrapped product must not pass the size check below
                 uint64_t count = 1;
-                for (int64_t d : en.shape) count *= (uint64_t)d;
-                if (en.end < en.begin || en.end - en.begin != count * (uint64_t)esz || f->data_start + en.end > f->file_size) {
+                bool overflow = false;
+                for (int64_t d : en.shape)
+                    overflow = overflow || d < 0 || __builtin_mul_overflow(count, (uint64_t)d, &count);
+                uint64_t want_bytes = 0;
+                overflow = overflow || __builtin_mul_overflow(count, (uint64_t)esz, &want_bytes);
+                if (overflow || en.end < en.begin || en.end - en.begin != want_bytes || f->data_start + en.end > f->file_size) {
                     const std::string nm = en.name;
                     iq_st_close(f);
                     return st_fail(IQ_ERR_FORMAT, "format: inconsistent size in %s", nm.c_str());

@@ -521,7 +521,7 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
             const int tiles = ((tokens + bm - 1) / bm) * ((d.experts + kRtBN - 1) / kRtBN);
             const int nchunks = d.d_model / kRtBK;
             int S = 1;
-            while (tiles * S < 4 * 148 && S < 8 && nchunks / (2 * S) >= 2) S *= 2;
+            while (tiles * S < 4 * ctx->sms && S < 8 && nchunks / (2 * S) >= 2) S *= 2;
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((tokens + bm - 1) / bm, (d.experts + kRtBN - 1) / kRtBN, S);
             cfg.blockDim = dim3(128);
@@ -669,7 +669,7 @@ ExpertsWs carve_experts(const iq_moe* l, void* base, int max_rows, int sources) 
 }  // namespace
 
 extern "C" int32_t iq_moe_experts_workspace_bytes(const iq_moe* l, int32_t max_rows, int32_t sources, size_t* bytes) {
-    if (l == nullptr || bytes == nullptr || max_rows < 1 || sources < 1) return kErrInvalidArg;
+    if (l == nullptr || bytes == nullptr || max_rows < 1 || sources < 1 || sources > kMaxEpSources) return kErrInvalidArg;
     *bytes = carve_experts(l, nullptr, max_rows, sources).bytes;
     return kOk;
 }
@@ -680,7 +680,8 @@ extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16,
     if (l == nullptr) return kErrInvalidArg;
     iq_ctx* ctx = l->ctx;
     const iq_moe_desc& d = l->d;
-    if (rows_f16 == nullptr || counts == nullptr || yd == nullptr || sources < 1 || sources * d.expert_count > 4096 ||
+    if (rows_f16 == nullptr || counts == nullptr || yd == nullptr || sources < 1 || sources > kMaxEpSources ||
+        sources * d.expert_count > 4096 ||
         total_rows < 0 || total_rows > max_rows || (yd_dtype != kF32 && yd_dtype != kF16) || region_rows < 0 ||
         (int64_t)region_rows * sources > max_rows ||
         (reinterpret_cast<uintptr_t>(rows_f16) & 15) != 0)

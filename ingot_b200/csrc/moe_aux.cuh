@@ -676,11 +676,13 @@ __global__ void __launch_bounds__(256) moe_pack_rows_kernel(const void* __restri
 // Tile list of the rows a rank received, by source then by local expert; counts[s * E + e] rows from source s for
 // expert e. region_rows == 0: the sources' rows follow each other (packed); region_rows > 0: the rows of source s start
 // at s * region_rows (every source owns a fixed region of the receive buffer). One block; at most 4096 entries.
+constexpr int kMaxEpSources = 16;  // source ranks of one tile list (the per-source totals live in shared memory)
+
 __global__ void __launch_bounds__(512) ep_tiles_kernel(const uint32_t* __restrict__ counts, int sources, int E, int e_lo,
                                                        int e_cnt, int bm, uint32_t region_rows, Tile* __restrict__ tiles,
                                                        uint32_t* __restrict__ ntiles) {
     __shared__ uint32_t rstart[4096];
-    __shared__ uint32_t stot[16];
+    __shared__ uint32_t stot[kMaxEpSources];
     __shared__ uint32_t stiles[512];
     const int n = sources * e_cnt;
     if ((int)threadIdx.x < sources) {

@@ -225,7 +225,7 @@ static __device__ __align__(256) unsigned char g_qmm_noalloc_scratch[kNoAllocByt
 
 namespace {
 constexpr int kMaxDevices = 64;
-void* g_noalloc_ptr[kMaxDevices] = {nullptr};  // device address of the array, per device, resolved on first use
+std::atomic<void*> g_noalloc_ptr[kMaxDevices];  // device address of the array, per device, resolved on first use (zero-initialised)
 }  // namespace
 
 extern "C" int32_t iq_qmm_noalloc(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx,
@@ -241,7 +241,8 @@ extern "C" int32_t iq_qmm_noalloc(iq_ctx* ctx, void* stream, const void* x, int3
                     "caller-provided workspace", (size_t)rows * (size_t)m->k, kNoAllocBytes / 2);
     const int dev = ctx->device;
     if (dev < 0 || dev >= kMaxDevices) return fail(ctx, kErrInvalidArg, "qmm_noalloc: device %d", dev);
-    if (g_noalloc_ptr[dev] == nullptr) {
+    void* scratch = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+    if (scratch == nullptr) {
         // The array's name is only a host-side handle here; the kernels need its address on this device. Resolved once
         // per device with that device current (it is: the context selected it, and the caller runs on it).
         int cur = -1;
@@ -251,9 +252,10 @@ extern "C" int32_t iq_qmm_noalloc(iq_ctx* ctx, void* stream, const void* x, int3
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_qmm_noalloc_scratch);
         if (e != cudaSuccess) return check_cuda(ctx, e, "cudaGetSymbolAddress(scratch)");
-        g_noalloc_ptr[dev] = p;
+        g_noalloc_ptr[dev].store(p, std::memory_order_release);  // two first callers store the same address
+        scratch = p;
     }
     // Every byte the GEMM reads from the scratch is written by this call's own conversion pass first, so nothing has
     // to be cleared; what the previous call left behind is simply overwritten.
-    return iq_qmm(ctx, stream, x, x_dtype, ldx, m, y, y_dtype, ldy, rows, flags, g_noalloc_ptr[dev], kNoAllocBytes);
+    return iq_qmm(ctx, stream, x, x_dtype, ldx, m, y, y_dtype, ldy, rows, flags, scratch, kNoAllocBytes);
 }

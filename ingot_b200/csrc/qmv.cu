@@ -79,9 +79,7 @@ QsKernel qs_pick(int32_t fmt, int mh, int mode) {
 }
 constexpr int kQsSmemMax = 226 * 1024;
 
-// 0: choose per shape; 1: always the register-staged kernel; 2: the streaming kernel wherever it applies
-int g_path = 0;
-int g_qi_ctas = 2;  // INGOT_QMV_CTAS=1: one CTA per SM with a deeper ring (measured 10.7 against 10.0 us)
+constexpr int kQiCtasPerSm = 2;  // up to four rows: two CTAs per SM (one CTA with a deeper ring measured 10.7 against 10.0 us)
 
 // Returns kOk after a launch, 1 when the shape does not fit this path (the caller falls back), or an error.
 int32_t launch_qmv_stream(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
@@ -161,6 +159,18 @@ int32_t launch_qmv_stream(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     return check_cuda(ctx, cudaLaunchKernelEx(&cfg, k, p), "qmv_stream launch");
 }
 
+// The tail split's scratch slot of a stream: launches of one stream run in series (a dependent launch waits for its
+// predecessor before it touches the scratch), so a stream keeps one slot for good; streams may overlap, so each gets its
+// own, and a context serves at most kQmvTailSlots of them. -1 when they are used up.
+int tail_slot_of(iq_ctx* ctx, cudaStream_t st) {
+    std::lock_guard<std::mutex> hold(ctx->qmv_tail_lock);
+    for (int i = 0; i < ctx->qmv_tail_stream_count; i++)
+        if (ctx->qmv_tail_streams[i] == static_cast<void*>(st)) return i;
+    if (ctx->qmv_tail_stream_count >= kQmvTailSlots) return -1;
+    ctx->qmv_tail_streams[ctx->qmv_tail_stream_count] = static_cast<void*>(st);
+    return ctx->qmv_tail_stream_count++;
+}
+
 // ---- int8 tensor-core path (decode, up to four rows, affine codes) -----------------------------------------------
 // Returns kOk after a launch, 1 when the shape does not fit this path (the caller falls back), or an error.
 int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
@@ -199,14 +209,16 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     CUtensorMap wmap = {};
     const CUtensorMap* map = &wmap;
     if (tm) {
-        // the matrix as the kernel sees it: all rows of W, whatever prefix of them this call computes
-        const int32_t r = cached_rowblock_map(ctx, p.w, c.N, p.row_bytes, kQiRows, &wmap);
+        // the matrix as the kernel sees it: all rows of W, whatever prefix of them this call computes (one cached map
+        // per matrix, not one per prefix)
+        const int32_t r = cached_rowblock_map(ctx, p.w, c.n_full > c.N ? c.n_full : c.N, p.row_bytes, kQiRows, &wmap);
         if (r != kOk) return r;
     }
     const int blocks = c.N / kQiRows;
-    // Tail split, decided from the matrix and the GPU alone (not from the row count, so a row sees the same arithmetic
-    // in every call): when the blocks do not divide over two CTAs per SM and few are left over, the left-over blocks
-    // are cut into K slices and dealt out one piece per CTA.
+    // Tail split, decided from the output features this call computes and the GPU alone (not from the activation row
+    // count, so an activation row sees the same arithmetic alone and among sixteen; a call with n_prefix may split
+    // differently from a call over the whole matrix): when the blocks do not divide over two CTAs per SM and few are
+    // left over, the left-over blocks are cut into K slices and dealt out one piece per CTA.
     const int slots = 2 * ctx->sms;
     const int per2 = blocks / slots, tail = blocks - per2 * slots;
     int tail_slices = 0;
@@ -228,7 +240,7 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
         p.ncw = ncw;
         // up to four rows: two CTAs per SM when each still gets two stages (twice the warps to hide latencies behind)
         int ctas = 1;
-        if (ms == 1 && g_qi_ctas == 2 && (kQsSmemMax / 2 - 1024 - fixed_bytes(ms)) / p.stage_bytes >= 2) ctas = 2;
+        if (ms == 1 && kQiCtasPerSm == 2 && (kQsSmemMax / 2 - 1024 - fixed_bytes(ms)) / p.stage_bytes >= 2) ctas = 2;
         int nstages = ((ctas == 2 ? kQsSmemMax / 2 - 1024 : kQsSmemMax) - fixed_bytes(ms)) / p.stage_bytes;
         if (nstages > 8) nstages = 8;
         p.nstages = nstages;
@@ -237,7 +249,10 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
         cfg.gridDim = dim3(blocks < ctx->sms * ctas ? blocks : ctx->sms * ctas, 1, 1);
         p.tail_blocks = 0;
         if (tail_slices > 0) {
-            const uint32_t slot = ctx->qmv_tail_seq.fetch_add(1) % kQmvTailSlots;
+            const int slot = tail_slot_of(ctx, st);
+            if (slot < 0)
+                return fail(ctx, kErrInvalidArg, "qmv: more than %d streams launch GEMVs with a tail split on this context",
+                            kQmvTailSlots);
             p.tail_blocks = tail;
             p.tail_slices = tail_slices;
             p.blocks_per_cta = per2 * (2 / ctas);
@@ -282,9 +297,9 @@ QgKernel qg_pick_tm(int mode, int ms) {
     return ms == 4 ? qmv_imma_grouped_kernel<kModeDown, 4, TM> : qmv_imma_grouped_kernel<kModeDown, 2, TM>;
 }
 QgKernel qg_pick(int mode, int ms, bool tm) { return tm ? qg_pick_tm<true>(mode, ms) : qg_pick_tm<false>(mode, ms); }
-// INGOT_QG_DOWN=1: the down projection (K = d_ff, rows of 384 bytes) on this path too. Off: with tensor copies it
-// measured 9.73 ms against 8.57 ms per 48-layer step of 64 tokens on the fp16 tile kernels.
-int g_qg_down = 0;
+// The down projection (K = d_ff, rows of 384 bytes) stays off this path: with tensor copies it measured 9.73 ms against
+// 8.57 ms per 48-layer step of 64 tokens on the fp16 tile kernels.
+constexpr bool kQgDown = false;
 
 // Returns kOk after a launch, 1 when the shape does not fit this path (the caller falls back), or an error.
 int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
@@ -303,7 +318,7 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
     // columns. Short weight rows (the down projection's K = d_ff) stay on the fp16 tile kernels either way: with one
     // bulk copy per 384-byte row this path measured 61.9 against 49.6 us at 64 tokens, with tensor copies no better.
     const bool tm = ctx->encode_tiled != nullptr && c.expert_count > 0 && p.row_bytes % 128 == 0 && p.row_bytes / 128 <= 256 &&
-                    c.w_estride * 4 == (int64_t)c.N * p.row_bytes && (c.K >= 2048 || g_qg_down != 0);
+                    c.w_estride * 4 == (int64_t)c.N * p.row_bytes && (c.K >= 2048 || kQgDown);
     if (c.K < 2048 && !tm) return 1;
     const int ms = c.max_rows > 8 ? 4 : 2;
     p.row_pitch = tm ? p.row_bytes : p.row_bytes + 32;
@@ -408,24 +423,19 @@ int32_t gqmv_init(iq_ctx* ctx) {
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kQsSmemMax);
                 if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_stream)");
             }
-    if (const char* e2 = getenv("INGOT_QMV_CTAS")) g_qi_ctas = atoi(e2);
-    if (const char* e3 = getenv("INGOT_QG_DOWN")) g_qg_down = atoi(e3);
-    const char* env = getenv("INGOT_QMV_PATH");
-    g_path = env == nullptr ? 0 : (strcmp(env, "legacy") == 0 ? 1 : (strcmp(env, "stream") == 0 ? 2 : 0));  // both: no int8 path
     return kOk;
 }
 
 int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
-    if (g_path == 0) {
-        int32_t r = launch_qmv_imma(ctx, st, c);
-        if (r != 1) return r;
-        r = launch_qmv_imma_grouped(ctx, st, c);
-        if (r != 1) return r;
-    }
-    if (g_path != 1) {
-        const int32_t r = launch_qmv_stream(ctx, st, c);
-        if (r != 1) return r;
-    }
+    // One kernel per (format, shape), chosen from the matrix alone: the int8 tensor-core kernels for affine codes whose
+    // K fits their staging, the streaming fp16 kernel for MXFP4 and the remaining affine shapes, the register-staged
+    // fp16 kernel where a 16-row block over the whole K does not fit a stage.
+    int32_t r = launch_qmv_imma(ctx, st, c);
+    if (r != 1) return r;
+    r = launch_qmv_imma_grouped(ctx, st, c);
+    if (r != 1) return r;
+    r = launch_qmv_stream(ctx, st, c);
+    if (r != 1) return r;
     if (c.fmt == kFmtAffine6)
         return fail(ctx, kErrUnsupported, "qmv: 6-bit weights run on the int8 kernel only (a plain GEMV, k a multiple of 2048, n >= 16)");
     const int ck = c.fmt == kFmtAffine8 ? 16 : 32;  // inputs per 16-byte chunk
@@ -524,6 +534,7 @@ extern "C" int32_t iq_qmv(iq_ctx* ctx, void* stream, const void* x, int32_t x_dt
     c.s[0] = m->scales;
     c.b[0] = m->biases;
     c.N = n;
+    c.n_full = m->n;
     c.K = m->k;
     c.x = x; c.x_dtype = x_dtype; c.ldx = ldx;
     c.rows = rows; c.max_rows = rows; c.grid_tiles = 1;

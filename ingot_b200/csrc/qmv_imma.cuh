@@ -112,6 +112,28 @@ __device__ __forceinline__ void unpack6x16(uint32_t w0, uint32_t w1, uint32_t w2
     o[3] = spread6(w2 >> 8);
 }
 
+// Block fixed point of one group of 64 activations: from the group's largest magnitude and its sum, the power of two
+// 2^(e-13) the digits are counted in (2^e > amax >= 2^(e-1)) and its inverse. A group that holds a NaN or an infinity
+// (amax or the sum not finite; fmaxf drops a NaN, the sum keeps it) gets a NaN scale and a NaN sum, so that every output
+// it feeds comes out NaN, where the fp16 kernels and an fp32 matrix product give NaN or an infinity: a non-finite input
+// must not turn into a finite output. Groups whose largest magnitude is below 2^-100 count as zero.
+__device__ __forceinline__ void qi_group_scale(float amax, float& sum, float& scale, float& inv) {
+    scale = 0.f;
+    inv = 0.f;
+    if (!(amax <= 3.4028235e38f) || !(fabsf(sum) <= 3.4028235e38f)) {
+        scale = __uint_as_float(0x7FC00000u);
+        sum = scale;
+        return;
+    }
+    if (amax > 0.f) {
+        const int e = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 126;
+        if (e > -100) {
+            scale = __uint_as_float((uint32_t)(e - 13 + 127) << 23);
+            inv = __uint_as_float((uint32_t)(13 - e + 127) << 23);
+        }
+    }
+}
+
 // Barrier over the consumer warps; the value it returns (zero) is a token for loads that must stay behind it.
 __device__ __forceinline__ uint32_t qi_consumer_barrier(int threads) {
     uint32_t t;
@@ -378,15 +400,8 @@ __global__ void __launch_bounds__(kQiMaxThreads, MS == 1 ? 2 : 1)
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
                 sum += __shfl_xor_sync(0xffffffffu, sum, o);
             }
-            float scale = 0.f, inv = 0.f;
-            if (amax > 0.f && amax < 3.0e38f) {
-                // 2^e > amax >= 2^(e-1): e from the exponent field (subnormal groups are treated as zero)
-                const int e = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 126;
-                if (e > -100) {
-                    scale = __uint_as_float((uint32_t)(e - 13 + 127) << 23);
-                    inv = __uint_as_float((uint32_t)(13 - e + 127) << 23);
-                }
-            }
+            float scale, inv;
+            qi_group_scale(amax, sum, scale, inv);
             if (w8 == 0) xsc[j * 4 * MS + m] = make_float2(scale, sum);
             uint32_t hi_w[2] = {0, 0}, lo_w[2] = {0, 0};  // [b0 / b1 half] bytes i = 0..3
 #pragma unroll

@@ -194,14 +194,8 @@ __global__ void __launch_bounds__(kQgThreads, 1)
                         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
                         sum += __shfl_xor_sync(0xffffffffu, sum, o);
                     }
-                    float scale = 0.f, inv = 0.f;
-                    if (amax > 0.f && amax < 3.0e38f) {
-                        const int e = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 126;
-                        if (e > -100) {
-                            scale = __uint_as_float((uint32_t)(e - 13 + 127) << 23);
-                            inv = __uint_as_float((uint32_t)(13 - e + 127) << 23);
-                        }
-                    }
+                    float scale, inv;
+                    qi_group_scale(amax, sum, scale, inv);
                     if (!live) continue;
                     if (w8 == 0) xsc[j * 4 * MS + m] = make_float2(scale, sum);
                     uint32_t hi_w[2] = {0, 0}, lo_w[2] = {0, 0};

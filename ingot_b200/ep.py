@@ -19,7 +19,7 @@ import torch
 import torch.distributed as dist
 
 from . import capi
-from .linear import DenseQ, VQMV, _stream_ptr
+from .linear import DenseQ, VQMV, _dtype_id, _stream_ptr
 from .moe import MoELayer
 
 
@@ -241,23 +241,106 @@ class MoEStack:
         return r
 
 
+def column_shard(rank: int, world: int, n: int) -> Tuple[int, int]:
+    """Output features [lo, lo + count) held by `rank` of a linear with n output features split by columns; every shard is
+    a whole number of 16-row blocks (the GEMV's unit), so n must be a multiple of 16 * world."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} of {world}")
+    if n % (16 * world) != 0:
+        raise ValueError(f"{n} output features do not split into {world} shards of whole 16-row blocks")
+    per = n // world
+    return rank * per, per
+
+
+def shard_rows(full: DenseQ, rank: int, world: int) -> DenseQ:
+    """The shard of `rank`: rows [lo, lo + count) of w / scales / biases — one contiguous byte range of each tensor, the
+    layout being row-major by output feature (the reference addresses such a range with nPrefix and its row
+    concatenation, Layers/Linear.swift:107-183, 350-366)."""
+    if full.experts != 1:
+        raise ValueError("a column-split linear is one matrix, not a stack of experts")
+    w, sc, b = shard_tensors(full.w, full.s, full.b, rank, world, full.N)
+    return DenseQ(w, sc, b, full.N // world, full.K, full.bits, full.gs, full.mode)
+
+
+def shard_tensors(w, scales, biases, rank: int, world: int, n: int):
+    """Rows [lo, lo + count) of the three tensors of a matrix with n output features (torch tensors or numpy arrays,
+    on any device; biases may be None): what `shard_rows` cuts, usable on the host before anything is uploaded."""
+    lo, per = column_shard(rank, world, n)
+    cut = lambda t: None if t is None else t.reshape(n, -1)[lo:lo + per]
+    return cut(w), cut(scales), cut(biases)
+
+
+def assemble_columns(y_all: torch.Tensor, rows: int) -> torch.Tensor:
+    """y [rows, n] from the all-gathered slices y_all [world, max_rows, n / world] (slice r = output features of rank r)."""
+    world, _, per = y_all.shape
+    return y_all[:, :rows].permute(1, 0, 2).reshape(rows, world * per)
+
+
 class ColumnSplitLinear:
-    """A dense quantized linear split by output features: rank r holds rows [r·N/G, (r+1)·N/G) of w/scales/biases (a
-    contiguous byte range of each tensor, the layout being row-major by output feature), x is replicated, and the
-    slices of y are all-gathered. Decode (rows ≤ 16) uses the GEMV kernel, larger row counts the GEMM kernel."""
+    """A dense quantized linear split by output features over the GPUs of one box: rank r holds rows [r*N/G, (r+1)*N/G) of
+    w / scales / biases, x is replicated, and every rank ends up with the whole y [rows, N]. Decode (rows <= 16) runs the
+    GEMV kernel, larger row counts the tcgen05 GEMM.
 
-    def __init__(self, shard: DenseQ, group: Optional[dist.ProcessGroup], max_rows: int):
-        self.shard, self.group = shard, group
+    exchange="device" (default on GPUs): iq_linear_colsplit — the slice is computed straight into this rank's y, stored
+    into every peer's y by the library's own kernel over peer memory and fenced by its flag barrier; no host
+    synchronisation, graph-capturable. y and the flags live in torch symmetric memory (plain peer pointers, multicast off).
+    exchange="nccl": the kernels write a local slice and `all_gather_into_tensor` assembles them (the baseline)."""
+
+    def __init__(self, shard: DenseQ, n_total: int, group: Optional[dist.ProcessGroup], max_rows: int,
+                 y_dtype: torch.dtype = torch.float32, exchange: str = "device", x_dtype: torch.dtype = torch.bfloat16):
+        if exchange not in ("device", "nccl"):
+            raise ValueError("exchange is 'device' or 'nccl'")
+        self.shard, self.group, self.exchange = shard, group, exchange
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        lo, per = column_shard(self.rank, self.world, n_total)
+        if shard.N != per:
+            raise ValueError(f"the shard has {shard.N} output features, {n_total} / {self.world} = {per} expected")
+        self.n_total, self.max_rows, self.y_dtype = n_total, max_rows, y_dtype
         dev = shard.w.device
-        self.y_local = torch.empty(max_rows, shard.N, dtype=torch.float32, device=dev)
-        self.y_all = torch.empty(self.world, max_rows, shard.N, dtype=torch.float32, device=dev)
-        self.ws = torch.empty(max(shard.qmm_workspace_bytes(max(max_rows, 64), torch.bfloat16), 256), dtype=torch.uint8,
-                              device=dev)
-        self.max_rows = max_rows
+        self.ctx = capi.context(dev.index or 0)
+        self.ws = torch.empty(max(shard.qmm_workspace_bytes(max(max_rows, 64), x_dtype), 256), dtype=torch.uint8, device=dev)
+        self._h = C.c_void_p()
+        if exchange == "nccl":
+            self.y_local = torch.empty(max_rows, per, dtype=y_dtype, device=dev)
+            self.y_all = torch.empty(self.world, max_rows, per, dtype=y_dtype, device=dev)
+            return
+        esz = torch.empty((), dtype=y_dtype).element_size()
+        if self.world > 1:
+            import os
 
-    def encode(self, x: torch.Tensor, rows: int) -> torch.Tensor:
-        """Returns y_all [G, max_rows, N/G]: slice r holds output features [r·N/G, (r+1)·N/G) of the first `rows` rows."""
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+
+            g = group if group is not None else dist.group.WORLD
+            self._bufs, ptrs = [], []
+            for nbytes in (max_rows * n_total * esz, 256):
+                t = symm_mem.empty((nbytes + 255) // 256 * 256, dtype=torch.uint8, device=dev)
+                t.zero_()
+                h = symm_mem.rendezvous(t, g)
+                self._bufs.append((t, h))
+                ptrs.append([int(p) for p in h.buffer_ptrs])
+            torch.cuda.synchronize(dev)
+            dist.barrier(g)
+            ybuf = self._bufs[0][0]
+        else:
+            ybuf = torch.zeros(max_rows * n_total * esz, dtype=torch.uint8, device=dev)
+            self._flags = torch.zeros(64, dtype=torch.int32, device=dev)
+            ptrs = [[ybuf.data_ptr()], [self._flags.data_ptr()]]
+        self.y = ybuf[: max_rows * n_total * esz].view(y_dtype).view(max_rows, n_total)
+        arr = lambda v: (C.c_void_p * self.world)(*v)
+        self.ctx.check(capi.lib().iq_colsplit_create(self.ctx.handle, self.rank, self.world, n_total, max_rows,
+                                                     _dtype_id(self.y), arr(ptrs[0]), arr(ptrs[1]), C.byref(self._h)))
+
+    def encode(self, x: torch.Tensor, rows: int, stream=None) -> torch.Tensor:
+        """Enqueues y[:rows] = x[:rows] W^T on every rank and returns y [max_rows, N] (valid in stream order)."""
+        if rows > self.max_rows:
+            raise ValueError(f"rows = {rows} exceeds the {self.max_rows} reserved")
+        if self.exchange == "device":
+            q = self.shard.qlinear()
+            self.ctx.check(capi.lib().iq_linear_colsplit(self._h, _stream_ptr(stream), x.data_ptr(), _dtype_id(x), x.stride(0),
+                                                         C.byref(q), rows, 0, self.ws.data_ptr(), self.ws.numel()))
+            return self.y
         if rows <= VQMV.MAX_ROWS:
             VQMV.encode(x, self.shard, self.y_local, rows)
         else:
@@ -265,5 +348,10 @@ class ColumnSplitLinear:
         if self.world == 1:
             self.y_all[0].copy_(self.y_local)
         else:
-            dist.all_gather_into_tensor(self.y_all, self.y_local, group=self.group)
-        return self.y_all
+            dist.all_gather_into_tensor(self.y_all.view(-1, self.y_all.shape[2]), self.y_local, group=self.group)
+        return assemble_columns(self.y_all, self.max_rows)
+
+    def close(self):
+        if self._h:
+            capi.lib().iq_colsplit_destroy(self._h)
+            self._h = C.c_void_p()

@@ -18,6 +18,18 @@
 #include <omp.h>
 #endif
 
+/* Number of OpenMP threads the following calls use (launchers such as torch.distributed.run export OMP_NUM_THREADS=1,
+ * which would otherwise turn the timed baseline into a one-core run). Returns the count now in force. */
+int qo_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 static inline float bf16_to_f32(uint16_t v) {
     uint32_t u = (uint32_t)v << 16;
     float f;

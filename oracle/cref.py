@@ -28,6 +28,21 @@ def lib():
     return _lib
 
 
+def host_threads() -> int:
+    """Hardware threads this process may run on."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def set_threads(n: int = 0) -> int:
+    """Sets the OpenMP thread count of the C oracle (n <= 0: every hardware thread of the host) and returns it. Needed
+    under launchers that export OMP_NUM_THREADS=1."""
+    lib().qo_set_threads.restype = C.c_int
+    return int(lib().qo_set_threads(C.c_int(n if n > 0 else host_threads())))
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 

@@ -87,6 +87,61 @@ def test_exchange_plan_two_ranks():
     assert sorted(res) == [(0, "ok"), (1, "ok")], res
 
 
+def colsplit_worker(rank, world, port, q):
+    """The column-split linear's host logic: every rank cuts its shard of the same seeded matrix, computes its slice of y
+    (with the CPU oracle standing in for the kernels), the slices are all-gathered and assembled."""
+    from ingot_b200 import synth
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(5)  # the same tensors on every rank
+        N, Kin, rows, max_rows = 96, 128, 3, 4
+        w, s, b = synth.affine_np(rng, N, Kin, 4)
+        x = synth.activations_np(rng, rows, Kin)
+        lo, per = ep.column_shard(rank, world, N)
+        assert (lo, per) == (rank * N // world, N // world)
+        ws, ss, bs = ep.shard_tensors(w[0], s[0], b[0], rank, world, N)
+        assert ws.shape == (per, Kin // 8) and ss.shape == (per, Kin // 64)
+        # a shard is one contiguous byte range of each tensor
+        assert ws.tobytes() == w[0].tobytes()[lo * Kin // 2:(lo + per) * Kin // 2]
+        y_local = torch.zeros(max_rows, per)
+        y_local[:rows] = torch.from_numpy(qref.matmul_t(x, qref.dequant_affine(ws, ss, bs, 4)))
+        y_all = torch.zeros(world, max_rows, per)
+        dist.all_gather_into_tensor(y_all.view(world * max_rows, per), y_local)
+        y = ep.assemble_columns(y_all, rows)
+        ref = qref.matmul_t(x, qref.dequant_affine(w[0], s[0], b[0], 4))
+        assert y.shape == (rows, N) and np.array_equal(y.numpy(), ref)
+        q.put((rank, "ok"))
+    except Exception as exc:  # pragma: no cover
+        q.put((rank, repr(exc)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_column_split_two_ranks():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=colsplit_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(res) == [(0, "ok"), (1, "ok")], res
+
+
+def test_column_shard_guards():
+    assert ep.column_shard(3, 8, 14336) == (5376, 1792)
+    with pytest.raises(ValueError):
+        ep.column_shard(0, 3, 64)      # 64 features do not make three shards of whole 16-row blocks
+    with pytest.raises(ValueError):
+        ep.column_shard(2, 2, 64)
+
+
 def test_plan_exchange_and_slices():
     ca = np.arange(4 * 8).reshape(4, 8)
     send, recv = ep.plan_exchange(ca, 1)

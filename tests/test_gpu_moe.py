@@ -99,6 +99,34 @@ def test_moe_c2_configuration(cuda_device, T):
     check_layer(layer, host, synth.activations_np(rng, T, 2048), T, "silu")
 
 
+def test_moe_c2_layer_at_the_benchmarked_size(cuda_device):
+    """The layer the 48-layer stack is made of, at the benchmark's 4096 prefill tokens (32,768 routed rows: the chunked
+    counting sort, 256-row tiles, the single-accumulator gate/up path): logits, indices, weights and the whole permutation
+    against the oracle in full, the outputs on 32 sampled tokens."""
+    rng = np.random.default_rng(4096)
+    T, E, K, D, I = 4096, 128, 8, 2048, 768
+    layer, host = build_layer(rng, cuda_device, E, K, D, I, max_tokens=T)
+    x = synth.activations_np(rng, T, D)
+    out = torch.zeros(T, D, dtype=torch.float32, device=cuda_device)
+    layer.encode(x_tensor(x, cuda_device), out, T)
+    assert capi.context(0).device_status() == 0
+    v = layer.views(T)
+    logits = qref.router_logits(x, host["router"])
+    inds, wts = qref.route(logits, K)
+    assert np.array_equal(v["inds"].cpu().numpy().astype(np.uint32), inds), "routing indices differ"
+    assert qref.max_rel(v["wts"].cpu().numpy(), wts) <= 1e-5
+    offsets, row_map, pos = qref.group_pairs(inds, E)
+    assert np.array_equal(v["offsets"].cpu().numpy().astype(np.uint32), offsets)
+    assert np.array_equal(v["row_map"].cpu().numpy().astype(np.uint32), row_map)
+    assert np.array_equal(v["pos"].cpu().numpy().astype(np.uint32), pos)
+    sel = np.sort(rng.choice(T, size=32, replace=False))
+    ref = qref.moe_ffn(x[sel], inds[sel], wts[sel], host["weights"])
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    err = qref.max_rel(got[sel], ref)
+    assert err <= TOL, err
+
+
 @pytest.mark.parametrize("T", [1, 256])
 def test_moe_c3_configuration(cuda_device, T):
     """32 experts, top-4, d_model = d_ff = 2880, MXFP4, expert biases, clamped SwiGLU."""

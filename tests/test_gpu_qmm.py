@@ -64,7 +64,7 @@ def test_qmm_mxfp4(cuda_device):
 
 
 @pytest.mark.parametrize("bits", [4, 8])
-@pytest.mark.parametrize("M,N,K", [(512, 14336, 4096), (2048, 14336, 4096), (512, 4096, 14336)])
+@pytest.mark.parametrize("M,N,K", [(512, 14336, 4096), (2048, 14336, 4096), (512, 4096, 14336), (2048, 4096, 14336)])
 def test_qmm_prefill_configuration(cuda_device, bits, M, N, K):
     """The prefill configuration at full size: the oracle on 192 sampled output features, and agreement with the decode
     GEMV kernel (itself checked against the oracle) on 16 sampled token rows over every output feature."""

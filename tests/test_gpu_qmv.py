@@ -182,3 +182,56 @@ def test_qmv_negative_control(cuda_device):
     ref_bad = qref.matmul_t(x, qref.dequant_affine(w2[0], host[1][0], host[2][0], 4))
     y = run(m, x_tensor(x, cuda_device), 1)
     assert qref.max_rel(y.cpu().numpy(), ref_bad) > TOL
+
+
+def int8_path_case(rng, device, N=256, K=2048, bits=4):
+    """A matrix the int8 tensor-core GEMV takes (K a multiple of 2048): its activations go through 14-bit block fixed
+    point per group of 64, which the cases below stress."""
+    m, host = affine_case(rng, N, K, bits, device)
+    return m, qref.dequant_affine(host[0][0], host[1][0], host[2][0], bits)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_qmv_int8_path_outlier_per_group(cuda_device, bits):
+    """One activation of about 1e3 in every group of 64 among values ~ N(0, 1): the group's fixed-point step follows the
+    outlier. The result stays inside the bound against the fp32 oracle."""
+    rng = np.random.default_rng(31 + bits)
+    m, wf = int8_path_case(rng, cuda_device, bits=bits)
+    x = synth.activations_np(rng, 3, 2048)
+    for g in range(2048 // 64):
+        x[:, g * 64 + rng.integers(0, 64)] = np.float32(1000.0) * rng.choice([-1.0, 1.0])
+    x = synth.round_bf16(x)
+    y = run(m, x_tensor(x, cuda_device), 3)
+    assert qref.max_rel(y.cpu().numpy(), qref.matmul_t(x, wf)) <= TOL
+
+
+def test_qmv_int8_path_wide_dynamic_range_fp32(cuda_device):
+    """fp32 activations whose groups span 2^-20 .. 2^20 in magnitude (each group at its own scale), and one group of
+    values that are subnormal in half precision: the per-group exponent carries the range."""
+    rng = np.random.default_rng(33)
+    m, wf = int8_path_case(rng, cuda_device)
+    x = rng.normal(0, 1, size=(2, 2048)).astype(np.float32)
+    for g in range(32):
+        x[:, g * 64:(g + 1) * 64] *= np.float32(2.0) ** rng.integers(-20, 21)
+    x[:, 5 * 64:6 * 64] = rng.normal(0, 1, size=(2, 64)).astype(np.float32) * np.float32(3e-8)  # below fp16's normal range
+    y = run(m, torch.from_numpy(x).to(cuda_device), 2)
+    assert qref.max_rel(y.cpu().numpy(), qref.matmul_t(x, wf)) <= TOL
+    # a row that is tiny everywhere keeps its relative accuracy (nothing is flushed at these magnitudes)
+    xs = (rng.normal(0, 1, size=(1, 2048)) * 1e-6).astype(np.float32)
+    ys = run(m, torch.from_numpy(xs).to(cuda_device), 1)
+    assert qref.max_rel(ys.cpu().numpy(), qref.matmul_t(xs, wf)) <= TOL
+
+
+@pytest.mark.parametrize("bad", [float("nan"), float("inf"), -float("inf")])
+@pytest.mark.parametrize("K", [2048, 512])
+def test_qmv_non_finite_activations_propagate(cuda_device, bad, K):
+    """A NaN or an infinity in x must not come out as a finite number, on the int8 path (K = 2048) as on the fp16 one
+    (K = 512), as in the reference's fp32 product; rows without one are untouched."""
+    rng = np.random.default_rng(35)
+    m, host = affine_case(rng, 64, K, 4, cuda_device)
+    x = synth.activations_np(rng, 3, K)
+    x[1, 77] = bad
+    y = run(m, x_tensor(x, cuda_device), 3).cpu().numpy()
+    ref = qref.matmul_t(x[[0, 2]], deq(host, 4))
+    assert not np.isfinite(y[1]).any()
+    assert qref.max_rel(y[[0, 2]], ref) <= TOL
