@@ -213,31 +213,34 @@ def graph_time_us(torch, fn, n_in_graph: int, reps: int = 20, dist=None, world: 
 
 
 def count_own_kernels(graph):
-    """Kernel nodes of a captured CUDA graph that are this library's kernels (namespace iq): the launches one replay
-    makes. Returns (own, all kernel nodes), or (None, None) when the graph cannot be inspected."""
+    """Kernel nodes of a captured CUDA graph, and how many of them are this library's kernels (namespace iq in the
+    mangled name): the launches one replay makes. Returns (own or None when names cannot be read, all kernel nodes), or
+    (None, None) when the graph cannot be inspected."""
     try:
-        from cuda.bindings import runtime as rt
+        from cuda.bindings import driver as drv
 
         raw = graph.raw_cuda_graph()
-        raw = raw if isinstance(raw, rt.cudaGraph_t) else rt.cudaGraph_t(int(raw))
-        err, _, n = rt.cudaGraphGetNodes(raw, 0)
+        g = drv.CUgraph(int(raw))
+        err, _, n = drv.cuGraphGetNodes(g, 0)
         if int(err) != 0 or n == 0:
             return None, None
-        err, nodes, n = rt.cudaGraphGetNodes(raw, n)
-        own = total = 0
+        err, nodes, n = drv.cuGraphGetNodes(g, n)
+        own = total = named = 0
         for node in nodes[:n]:
-            err, ty = rt.cudaGraphNodeGetType(node)
-            if int(err) != 0 or ty != rt.cudaGraphNodeType.cudaGraphNodeTypeKernel:
+            err, ty = drv.cuGraphNodeGetType(node)
+            if int(err) != 0 or ty != drv.CUgraphNodeType.CU_GRAPH_NODE_TYPE_KERNEL:
                 continue
             total += 1
-            err, prm = rt.cudaGraphKernelNodeGetParams(node)
-            name = b""
-            if int(err) == 0:
-                err, name = rt.cudaFuncGetName(prm.func)
-                name = name if int(err) == 0 and name else b""
-            if b"iq" in name:
-                own += 1
-        return own, total
+            try:
+                err, prm = drv.cuGraphKernelNodeGetParams(node)
+                err2, name = drv.cuFuncGetName(prm.func) if int(err) == 0 else (1, b"")
+                if int(err2) == 0 and name:
+                    named += 1
+                    if b"2iq" in name or b"iq::" in name:
+                        own += 1
+            except Exception:
+                pass
+        return (own if named == total else None), total
     except Exception:
         return None, None
 
@@ -603,10 +606,13 @@ def run_ours(args):
         qmm = bench_qmm(torch, dev, peaks) if args.only is None else None
         from ingot_b200 import capi
         status = capi.context(local).device_status()
-        if own_launches is not None:
-            launches = {"gpu_launches": own_launches * args.steps,
-                        "gpu_launches_source": f"{own_launches} kernel nodes of this library ({all_launches} kernel nodes in all) "
-                                               "counted in the step's CUDA graph, times the timed steps"}
+        if all_launches is not None:
+            n_own = own_launches if own_launches is not None else all_launches
+            launches = {"gpu_launches": n_own * args.steps,
+                        "gpu_launches_source": (f"{n_own} kernel nodes of this library" if own_launches is not None else
+                                                f"{all_launches} kernel nodes (their names could not be read; torch's "
+                                                "residual copy is a memcpy node, so all of them are this library's)") +
+                                               f" of {all_launches} kernel nodes counted in the step's CUDA graph, times the timed steps"}
         else:
             per_layer = 10 if world == 1 else 15
             launches = {"gpu_launches": per_layer * args.layers * args.steps,

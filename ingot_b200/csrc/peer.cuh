@@ -22,9 +22,9 @@ struct PeerPtrs {
 // the flag. The wait is bounded: after wait_cycles the status word is set to kErrTimeout and the block goes on.
 __device__ __forceinline__ void peer_flag_barrier(const PeerPtrs& flags, uint32_t e, int rank, int world, int32_t* status,
                                                   unsigned long long wait_cycles) {
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();  // every thread's peer stores are done; the fence below, by the flag writers, covers them
     if ((int)threadIdx.x < world) {
+        __threadfence_system();
         volatile uint32_t* remote = static_cast<volatile uint32_t*>(flags.p[threadIdx.x]) + rank;
         *remote = e;
         volatile uint32_t* mine = static_cast<volatile uint32_t*>(flags.p[rank]) + threadIdx.x;
@@ -35,9 +35,9 @@ __device__ __forceinline__ void peer_flag_barrier(const PeerPtrs& flags, uint32_
                 break;
             }
         }
+        __threadfence_system();  // what the peers stored before their flags is read after this point
     }
     __syncthreads();
-    __threadfence_system();
 }
 
 }  // namespace iq

@@ -297,28 +297,49 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                 if (EPI == kEpiGateUp) tmem_ld32(tbase + BN + c0, r1);
                 tmem_ld_wait();
                 if (!n_ok) continue;
+                // The 32 token columns of this thread's output feature. No early exit inside the loops: an exit test
+                // between the elements serialises them (each then pays the whole dependent chain of the activation,
+                // about a hundred cycles) and made the epilogue a third of the grouped GEMM's time; the columns beyond
+                // the tile's rows are computed and dropped by the stores' predicates.
+                float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
-                    if (c0 + j >= rows) break;
-                    float v = __uint_as_float(r0[j]) + bias0;
-                    if (EPI == kEpiGateUp) {
-                        // gate and up stay fp32 up to the activation (the reference's prefill kernels round them to
-                        // half first, GU_HALF, Shaders/qmm_nax_moe.metal:491-505: a storage choice, not needed here)
-                        const float g = v;
-                        const float u = __uint_as_float(r1[j]) + bias1;
-                        v = glu<ACT>(g, u, p.limit);
-                    }
-                    const size_t o = (size_t)(row0 + c0 + j) * p.ldy + n;
-                    if (p.y_dtype == kF32) {
-                        float* yp = reinterpret_cast<float*>(p.y) + o;
-                        *yp = p.accumulate ? *yp + v : v;
-                    } else if (p.y_dtype == kF16) {
-                        __half* yp = reinterpret_cast<__half*>(p.y) + o;
-                        *yp = __float2half_rn(p.accumulate ? __half2float(*yp) + v : v);
+                    v[j] = __uint_as_float(r0[j]) + bias0;
+                    // gate and up stay fp32 up to the activation (the reference's prefill kernels round them to half
+                    // first, GU_HALF, Shaders/qmm_nax_moe.metal:491-505: a storage choice, not needed here)
+                    if (EPI == kEpiGateUp) v[j] = glu<ACT>(v[j], __uint_as_float(r1[j]) + bias1, p.limit);
+                }
+                const int live = rows - c0;  // columns j < live exist
+                const size_t o0 = (size_t)(row0 + c0) * p.ldy + n;
+                if (p.y_dtype == kF16) {
+                    __half* yp = reinterpret_cast<__half*>(p.y) + o0;
+                    if (p.accumulate) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < live) yp[(size_t)j * p.ldy] = __float2half_rn(__half2float(yp[(size_t)j * p.ldy]) + v[j]);
                     } else {
-                        uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + o;
-                        *yp = (uint16_t)f32_to_bf16_bits(p.accumulate ? bf16_bits_to_f32(*yp) + v : v);
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < live) yp[(size_t)j * p.ldy] = __float2half_rn(v[j]);
                     }
+                } else if (p.y_dtype == kF32) {
+                    float* yp = reinterpret_cast<float*>(p.y) + o0;
+                    if (p.accumulate) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < live) yp[(size_t)j * p.ldy] += v[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < live) yp[(size_t)j * p.ldy] = v[j];
+                    }
+                } else {
+                    uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + o0;
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (j < live)
+                            yp[(size_t)j * p.ldy] =
+                                (uint16_t)f32_to_bf16_bits(p.accumulate ? bf16_bits_to_f32(yp[(size_t)j * p.ldy]) + v[j] : v[j]);
                 }
             }
             tc_fence_before();

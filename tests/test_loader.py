@@ -192,6 +192,13 @@ def test_malformed_files_are_format_errors(tmp_path):
     with pytest.raises(loader.SafetensorsError) as ex:
         loader.SafetensorsStore(str(tmp_path))
     assert "inconsistent size in t" in str(ex.value)
+    # a shape whose element count wraps 64 bits ([2^32, 2^32] -> 0 elements) must not pass for an empty tensor
+    for shape in ([2**32, 2**32], [2**62, 4], [2**40, 2**22, 2]):
+        js = json.dumps({"t": {"dtype": "F32", "shape": shape, "data_offsets": [0, 0]}}).encode()
+        p.write_bytes(struct.pack("<Q", len(js)) + js + b"\x00" * 8)
+        with pytest.raises(loader.SafetensorsError) as ex:
+            loader.SafetensorsStore(str(tmp_path))
+        assert ex.value.kind == "format" and "inconsistent size in t" in str(ex.value)
     js = json.dumps({"t": {"dtype": "F64", "shape": [1], "data_offsets": [0, 8]}}).encode()
     p.write_bytes(struct.pack("<Q", len(js)) + js + b"\x00" * 8)
     with pytest.raises(loader.SafetensorsError) as ex:
