@@ -1,4 +1,6 @@
 // MoE layer and dense gated FFN entry points.
+#include <string.h>
+
 #include <new>
 
 #include "internal.h"
@@ -11,6 +13,8 @@ struct iq_moe {
     int32_t ld = 0;  // logits row stride
     const uint32_t* ext_inds = nullptr;
     const float* ext_wts = nullptr;
+    // largest row norm of a bf16 router (0: not computed), for the error bound of the tensor-core logits
+    float router_wnorm_max = 0.f;
 };
 
 namespace iq {
@@ -98,22 +102,47 @@ MoeWs carve(const iq_moe* l, void* base, int tokens) {
 }
 
 typedef void (*RouteKernel)(const RouteParams);
-RouteKernel route_kernel_for(int experts) {
+template <bool REFINE>
+RouteKernel route_kernel_of(int experts) {
     switch ((experts + 31) / 32) {
-        case 1: return route_topk_kernel<1>;
-        case 2: return route_topk_kernel<2>;
-        case 3: return route_topk_kernel<3>;
-        case 4: return route_topk_kernel<4>;
-        case 5: case 6: return route_topk_kernel<6>;
-        case 7: case 8: return route_topk_kernel<8>;
-        case 9: case 10: case 11: case 12: return route_topk_kernel<12>;
-        default: return route_topk_kernel<16>;
+        case 1: return route_topk_kernel<1, REFINE>;
+        case 2: return route_topk_kernel<2, REFINE>;
+        case 3: return route_topk_kernel<3, REFINE>;
+        case 4: return route_topk_kernel<4, REFINE>;
+        case 5: case 6: return route_topk_kernel<6, REFINE>;
+        case 7: case 8: return route_topk_kernel<8, REFINE>;
+        case 9: case 10: case 11: case 12: return route_topk_kernel<12, REFINE>;
+        default: return route_topk_kernel<16, REFINE>;
     }
 }
+RouteKernel route_kernel_for(int experts, bool refine) {
+    return refine ? route_kernel_of<true>(experts) : route_kernel_of<false>(experts);
+}
 
-int32_t launch_route(iq_moe* l, cudaStream_t st, const float* logits, int ld, int tokens, uint32_t* inds, float* wts) {
+// Many tokens with a bf16 router and bf16 activations: the logits come from the tensor cores (bf16 products are exact,
+// the fp32 accumulation is not), and the route kernel recomputes exactly, in float64, the few logits per token that
+// can still be among the k largest. Indices and weights are then the same bits as with float64 logits throughout, at
+// a fifth of the time: the float64 GEMM was 135 us of a 4096-token layer.
+// Error bound of an approximate logit: K accumulations, each assumed to lose at most 2^-21 of the running magnitude
+// (eight times what round-to-nearest fp32 would), over sum_k |x_k w_k| <= ||x||_2 ||w||_2.
+bool tensor_router(const iq_moe* l, int tokens, int32_t x_dtype) {
+    const iq_moe_desc& d = l->d;
+    return l->router_wnorm_max > 0.f && l->ext_inds == nullptr && d.router_kind == IQ_ROUTER_BF16 &&
+           d.router_score == IQ_SCORE_SOFTMAX && x_dtype == kBF16 && tokens > kRouterTiledMinTokens && d.experts % 64 == 0 &&
+           d.d_model % 64 == 0;
+}
+float router_err_coef(const iq_moe* l) { return (float)l->d.d_model * 4.76837158e-7f * 1.05f * l->router_wnorm_max; }
+
+int32_t launch_route(iq_moe* l, cudaStream_t st, const float* logits, int ld, int tokens, uint32_t* inds, float* wts,
+                     const void* refine_x = nullptr, int64_t ldx = 0) {
     RouteParams rp;
     rp.logits = logits;
+    rp.logits_rw = const_cast<float*>(logits);
+    rp.x = static_cast<const uint16_t*>(refine_x);
+    rp.ldx = ldx;
+    rp.wr = static_cast<const uint16_t*>(l->d.router_w);
+    rp.D = l->d.d_model;
+    rp.err_coef = router_err_coef(l);
     rp.logit_bias = l->d.router_logit_bias;
     rp.pes = l->d.per_expert_scale;
     rp.inds = inds;
@@ -123,7 +152,7 @@ int32_t launch_route(iq_moe* l, cudaStream_t st, const float* logits, int ld, in
     rp.sigmoid = l->d.router_score == IQ_SCORE_SIGMOID ? 1 : 0;
     rp.select_bias = l->d.router_select_bias;
     rp.eps = l->d.route_eps;
-    route_kernel_for(l->d.experts)<<<(tokens + 3) / 4, 128, 0, st>>>(rp);
+    route_kernel_for(l->d.experts, refine_x != nullptr)<<<(tokens + 3) / 4, 128, 0, st>>>(rp);
     return check_cuda(l->ctx, cudaGetLastError(), "route_topk launch");
 }
 
@@ -453,6 +482,27 @@ extern "C" int32_t iq_moe_create(iq_ctx* ctx, const iq_moe_desc* d, iq_moe** out
     l->d = *d;
     l->fmt = fg;
     l->ld = round_up(d->experts, 64);
+    if (d->router_kind == IQ_ROUTER_BF16 && d->router_score == IQ_SCORE_SOFTMAX && d->experts % 64 == 0) {
+        // set-up time (this call takes no stream): the largest row norm of the router, for the error bound of the
+        // tensor-core logits. The router tensor must be complete on the device when the layer is created.
+        uint32_t* dmax = nullptr;
+        cudaError_t e = cudaMalloc(&dmax, 4);
+        if (e == cudaSuccess) e = cudaMemset(dmax, 0, 4);
+        if (e == cudaSuccess) {
+            router_wnorm_max_kernel<<<d->experts, 256>>>(static_cast<const uint16_t*>(d->router_w), d->d_model, dmax);
+            e = cudaGetLastError();
+        }
+        uint32_t bits = 0;
+        if (e == cudaSuccess) e = cudaMemcpy(&bits, dmax, 4, cudaMemcpyDeviceToHost);
+        if (dmax) cudaFree(dmax);
+        if (e != cudaSuccess) {
+            delete l;
+            return check_cuda(ctx, e, "moe: router norm");
+        }
+        float f;
+        memcpy(&f, &bits, 4);
+        if (f > 0.f && f < 3.0e38f) l->router_wnorm_max = f;  // otherwise (zero or non-finite router): the float64 path
+    }
     *out = l;
     return kOk;
 }
@@ -499,7 +549,7 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
     const iq_moe_desc& d = l->d;
     if (tokens < 1) return fail(ctx, kErrInvalidArg, "moe: tokens = %d", tokens);
     if (x_dtype < 0 || x_dtype > 2 || out_dtype < 0 || out_dtype > 2) return fail(ctx, kErrInvalidArg, "moe: dtype");
-    if ((pieces & (IQ_PIECE_ROUTER | IQ_PIECE_GATEUP)) &&
+    if ((pieces & (IQ_PIECE_ROUTER | IQ_PIECE_ROUTE | IQ_PIECE_GATEUP)) && (x != nullptr || (pieces & (IQ_PIECE_ROUTER | IQ_PIECE_GATEUP))) &&
         (x == nullptr || ldx < d.d_model || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0))
         return fail(ctx, kErrInvalidArg, "moe: x must be 16-byte aligned with ldx >= d_model and ldx %% 8 == 0");
     if ((pieces & IQ_PIECE_COMBINE) && (out == nullptr || ldo < d.d_model || ldo % 4 != 0))
@@ -513,7 +563,18 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
     const float* wts = l->ext_wts ? l->ext_wts : w.wts;
     int32_t st;
 
-    if ((pieces & IQ_PIECE_ROUTER) && l->ext_inds == nullptr) {
+    const bool fast_router = tensor_router(l, tokens, x_dtype);
+    if ((pieces & IQ_PIECE_ROUTER) && fast_router) {
+        QmmCall c;
+        c.fmt = kFmtBf16Plain; c.epi = 0; c.bn = 128;
+        c.x16 = x; c.ldx = ldx; c.x_rows = tokens;
+        c.w[0] = d.router_w;
+        c.experts = 1;
+        c.N = d.experts; c.K = d.d_model; c.M = tokens;
+        c.y = w.logits; c.y_dtype = kF32; c.ldy = l->ld;
+        st = launch_qmm(ctx, cs, c);
+        if (st != kOk) return st;
+    } else if ((pieces & IQ_PIECE_ROUTER) && l->ext_inds == nullptr) {
         if (tokens > kRouterTiledMinTokens && d.d_model % 64 == 0) {
             // register-tiled float64 GEMM; the K range is split over a cluster until the grid fills the GPU several
             // times over (the blocks of one SM share its float64 pipe, so balance comes from many small blocks)
@@ -563,7 +624,8 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
         if (st != kOk) return st;
     }
     if ((pieces & IQ_PIECE_ROUTE) && l->ext_inds == nullptr) {
-        st = launch_route(l, cs, w.logits, l->ld, tokens, w.inds, w.wts);
+        if (fast_router && x == nullptr) return fail(ctx, kErrInvalidArg, "moe: the route piece needs x (it recomputes logits)");
+        st = launch_route(l, cs, w.logits, l->ld, tokens, w.inds, w.wts, fast_router ? x : nullptr, ldx);
         if (st != kOk) return st;
     }
     const int bm = decode_tile_rows(l, tokens);

@@ -280,6 +280,27 @@ __global__ void __launch_bounds__(128) router_logits_tiled_kernel(const void* __
     }
 }
 
+// Largest Euclidean norm of a router row (bf16 [E, D]), rounded up a little: one block per expert, the maximum taken
+// over the bit patterns (positive floats order like their bits). Feeds the error bound of the approximate logits.
+__global__ void __launch_bounds__(256) router_wnorm_max_kernel(const uint16_t* __restrict__ wr, int D, uint32_t* __restrict__ out) {
+    __shared__ float wsum[8];
+    const uint16_t* row = wr + (size_t)blockIdx.x * D;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < D; i += 256) {
+        const float f = bf16_bits_to_f32(row[i]);
+        s = fmaf(f, f, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int i = 0; i < 8; i++) tot += wsum[i];
+        atomicMax(out, __float_as_uint(sqrtf(tot) * 1.001f));
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Top-k routing of softmax-family routers. One warp per token. The rule (KernelCaseRouter.swift:57-80 of the
 // reference): add the router bias to the logits, NaN counts as -inf, pick the maximum k times with ties going to the
@@ -287,6 +308,15 @@ __global__ void __launch_bounds__(128) router_logits_tiled_kernel(const void* __
 // k order, then x routed scale and x the per-expert scale of the chosen expert.
 struct RouteParams {
     const float* logits;       // [T, ld]
+    // Refinement (route_topk_kernel<VPL, true>): `logits` then holds approximate values, each within
+    // err_coef * ||x_t||_2 of the exact one. The kernel recomputes, exactly (float64 sums of exact products, rounded once
+    // to fp32), every logit that could still belong to the top k, writes them back and selects among those.
+    float* logits_rw;          // the same array, writable
+    const uint16_t* x;         // bf16 activations [T, ldx]
+    int64_t ldx;
+    const uint16_t* wr;        // bf16 router [E, D]
+    int32_t D;
+    float err_coef;
     const float* logit_bias;   // [E] or null
     const float* pes;          // per-expert scale [E] or null
     uint32_t* inds;            // [T, topk]
@@ -298,7 +328,29 @@ struct RouteParams {
     float eps;                 // sigmoid: added to the sum of the chosen scores
 };
 
-template <int VPL>
+// One exact logit: sum_k x[k] * w[k] over bf16 inputs. Every product is exact in fp32 (two 8-bit significands); the sum
+// runs in float64 in a fixed order (lane-strided chunks, then a butterfly over the lanes), so its fp32 rounding is the
+// correctly rounded dot product whatever the order. All lanes get the result.
+__device__ __forceinline__ float exact_dot_bf16(const uint16_t* __restrict__ xrow, const uint16_t* __restrict__ wrow, int D,
+                                                int lane) {
+    double a4[4] = {0.0, 0.0, 0.0, 0.0};  // four independent chains (the float64 adds would otherwise wait for each other)
+    for (int u = lane; u < D / 8; u += 32) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(xrow + u * 8);
+        const uint4 wv = ldg_nc_u4(wrow + u * 8);
+        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            a4[j] += (double)(__uint_as_float(xw[j] << 16) * __uint_as_float(ww[j] << 16));
+            a4[j] += (double)(__uint_as_float(xw[j] & 0xFFFF0000u) * __uint_as_float(ww[j] & 0xFFFF0000u));
+        }
+    }
+    double acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    return (float)acc;
+}
+
+template <int VPL, bool REFINE = false>
 __global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -323,6 +375,65 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
         if (f != f) f = -INFINITY;
         v[j] = f;
         if (e >= p.E) taken |= 1u << j;
+    }
+    if (REFINE) {
+        // ---- which experts can still be among the k largest? Those within 2 eps of the k-th largest approximate value:
+        // with |approx - exact| <= eps everywhere, at least k experts have an exact value >= kth - eps, so a true member of
+        // the top k has exact >= kth - eps and approx >= kth - 2 eps. The exact values of these candidates decide.
+        uint32_t tk = taken;
+        float kth = -INFINITY;
+        for (int k = 0; k < p.topk; k++) {
+            float bv = -INFINITY;
+            int bj = -1;
+#pragma unroll
+            for (int j = 0; j < VPL; j++)
+                if (!((tk >> j) & 1u) && (bj < 0 || v[j] > bv)) { bv = v[j]; bj = j; }
+            float gv = bj >= 0 ? bv : -INFINITY;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, o));
+            // one holder of the maximum drops out (the lowest lane; which one is irrelevant for the k-th value)
+            const uint32_t holders = __ballot_sync(0xffffffffu, bj >= 0 && bv == gv);
+            if (holders == 0u) { gv = -INFINITY; }
+            else if (lane == __ffs(holders) - 1) tk |= 1u << bj;
+            kth = gv;
+        }
+        const uint16_t* xrow = p.x + (size_t)t * p.ldx;
+        float ss = 0.f;
+        for (int u = lane; u < p.D / 8; u += 32) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xrow + u * 8);
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float a = __uint_as_float(xw[j] << 16), b = __uint_as_float(xw[j] & 0xFFFF0000u);
+                ss = fmaf(a, a, ss);
+                ss = fmaf(b, b, ss);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float eps = p.err_coef * sqrtf(ss) * 1.001f;
+        // anything not finite (an infinity or NaN among the inputs): every expert is recomputed
+        float thr = kth - 2.f * eps;
+        if (!(fabsf(kth) <= 3.0e38f) || !(eps <= 3.0e38f)) thr = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < VPL; j++) {
+            const bool mine = !((taken >> j) & 1u) && v[j] >= thr;
+            uint32_t bal = __ballot_sync(0xffffffffu, mine);
+            while (bal != 0u) {
+                const int src = __ffs(bal) - 1;
+                bal &= bal - 1u;
+                const int e = j * 32 + src;
+                const float exact = exact_dot_bf16(xrow, p.wr + (size_t)e * p.D, p.D, lane);
+                if (lane == src) {
+                    p.logits_rw[(size_t)t * p.ld + e] = exact;
+                    float f = exact;
+                    if (p.logit_bias != nullptr) f += p.logit_bias[e];
+                    if (f != f) f = -INFINITY;
+                    v[j] = f;
+                }
+            }
+            if (!mine) taken |= 1u << j;  // out of the running
+        }
     }
     float myv = -INFINITY, myp = 0.f;
     uint32_t myi = 0;

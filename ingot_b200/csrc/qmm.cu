@@ -40,6 +40,7 @@ const KernelEntry* table(int* n) {
         entry<kFmtAffine4, 128, kEpiGateUp, kActRelu2>(), entry<kFmtAffine4, 256, kEpiGateUp, kActRelu2>(),
         entry<kFmtMxfp4, 128, kEpiGateUp, kActGelu>(), entry<kFmtMxfp4, 256, kEpiGateUp, kActGelu>(),
         entry<kFmtMxfp4, 128, kEpiGateUp, kActRelu2>(), entry<kFmtMxfp4, 256, kEpiGateUp, kActRelu2>(),
+        entry<kFmtBf16Plain, 128, kEpiStore>(),  // bf16 x bf16 (the router's approximate logits)
     };
     *n = (int)(sizeof(t) / sizeof(t[0]));
     return t;
@@ -68,7 +69,8 @@ int32_t qmm_init(iq_ctx* ctx) {
 }
 
 // 2-D tensor map over a row-major matrix: `inner` elements per row, `rows` rows, `row_bytes` between rows.
-int32_t make_map_2d(iq_ctx* ctx, CUtensorMap* map, const void* base, bool f16, uint64_t inner, uint64_t rows,
+// elem: 0 = bytes, 1 = fp16, 2 = bf16 elements
+int32_t make_map_2d(iq_ctx* ctx, CUtensorMap* map, const void* base, int elem, uint64_t inner, uint64_t rows,
                     uint64_t row_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128) {
     if (ctx->encode_tiled == nullptr) return fail(ctx, kErrCuda, "cuTensorMapEncodeTiled is not available");
     if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || row_bytes % 16 != 0)
@@ -78,7 +80,8 @@ int32_t make_map_2d(iq_ctx* ctx, CUtensorMap* map, const void* base, bool f16, u
     const cuuint32_t box[2] = {box_inner, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
-        map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+        map, elem == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : (elem == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8),
+        2, const_cast<void*>(base), dims,
         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -122,15 +125,21 @@ int32_t cached_rowblock_map(iq_ctx* ctx, const void* base, int64_t rows, int32_t
 int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
     const KernelEntry* ke = find(c.fmt, c.bn, c.epi, c.act);
     if (ke == nullptr) return fail(ctx, kErrNoKernel, "qmm: no kernel for format %d, tile %d, epilogue %d", c.fmt, c.bn, c.epi);
+    const bool plain = c.fmt == kFmtBf16Plain;  // bf16 activations and bf16 weights, both copied as they are
     const int pack_row = c.fmt == kFmtAffine8 ? 64 : 32;
     const uint64_t row_bytes = (uint64_t)c.K / kBK * pack_row;
     CUtensorMap mx, mw0, mw1;
-    int32_t r = make_map_2d(ctx, &mx, c.x16, true, (uint64_t)c.K, (uint64_t)c.x_rows, (uint64_t)c.ldx * 2, kBK, c.bn, true);
+    int32_t r = make_map_2d(ctx, &mx, c.x16, plain ? 2 : 1, (uint64_t)c.K, (uint64_t)c.x_rows, (uint64_t)c.ldx * 2, kBK, c.bn, true);
     if (r != kOk) return r;
-    r = make_map_2d(ctx, &mw0, c.w[0], false, row_bytes, (uint64_t)c.experts * c.N, row_bytes, pack_row, kWRows, false);
-    if (r != kOk) return r;
-    r = make_map_2d(ctx, &mw1, c.w[1] ? c.w[1] : c.w[0], false, row_bytes, (uint64_t)c.experts * c.N, row_bytes, pack_row,
-                    kWRows, false);
+    if (plain) {
+        r = make_map_2d(ctx, &mw0, c.w[0], 2, (uint64_t)c.K, (uint64_t)c.experts * c.N, (uint64_t)c.K * 2, kBK, kWRows, true);
+        mw1 = mw0;
+    } else {
+        r = make_map_2d(ctx, &mw0, c.w[0], 0, row_bytes, (uint64_t)c.experts * c.N, row_bytes, pack_row, kWRows, false);
+        if (r != kOk) return r;
+        r = make_map_2d(ctx, &mw1, c.w[1] ? c.w[1] : c.w[0], 0, row_bytes, (uint64_t)c.experts * c.N, row_bytes, pack_row,
+                        kWRows, false);
+    }
     if (r != kOk) return r;
     QmmParams p;
     for (int i = 0; i < 2; i++) {

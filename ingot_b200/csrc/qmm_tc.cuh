@@ -66,9 +66,9 @@ __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr) {
     d |= (uint64_t)2 << 61;              // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor, kind::f16: D = f32, A = B = f16, both K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t make_idesc(int n) {
-    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kWRows >> 4) << 24);
+// Instruction descriptor, kind::f16: D = f32, A = B = f16 (or both bf16), both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc(int n, bool bf16 = false) {
+    return (1u << 4) | (bf16 ? (1u << 7) | (1u << 10) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kWRows >> 4) << 24);
 }
 
 // ---- dequantisation of 32 consecutive inputs of one weight row into four 16-byte chunks --------------------------
@@ -129,7 +129,8 @@ __device__ __forceinline__ void dequant32(uint32_t packed_row_half, uint32_t sc_
 template <int FMT, int BN, int EPI>
 struct QmmSmem {
     static constexpr int NWT = EPI == kEpiGateUp ? 2 : 1;                 // weight tiles per stage
-    static constexpr int PACK_ROW = FMT == kFmtAffine8 ? 64 : 32;         // packed bytes per row per K step
+    static constexpr bool PLAIN = FMT == kFmtBf16Plain;                   // bf16 weights used as they are: no packed tile
+    static constexpr int PACK_ROW = PLAIN ? 0 : (FMT == kFmtAffine8 ? 64 : 32);  // packed bytes per row per K step
     static constexpr int X_BYTES = BN * 128;
     static constexpr int WD_BYTES = kWRows * 128;
     static constexpr int WP_BYTES = kWRows * PACK_ROW;
@@ -227,6 +228,12 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!(ok = mbar_wait_relaxed(bar_empty + 8 * s, ph ^ 1, abort_flag))) break;
                     unsigned char* st = smem + s * S::STAGE_BYTES;
+                    if (S::PLAIN) {  // the bf16 weight tile goes straight where the MMA reads it (128-byte swizzle)
+                        mbar_arrive_expect_tx(bar_full + 8 * s, S::X_BYTES + S::WD_BYTES);
+                        tma_load_2d(smem_u32(st), &map_x, bar_full + 8 * s, ks * kBK, row0);
+                        tma_load_2d(smem_u32(st + S::X_BYTES), &map_w0, bar_full + 8 * s, ks * kBK, (int)expert * p.N + n0);
+                        continue;
+                    }
                     mbar_arrive_expect_tx(bar_full + 8 * s, S::X_BYTES + NWT * S::WP_BYTES);
                     tma_load_2d(smem_u32(st), &map_x, bar_full + 8 * s, ks * kBK, row0);
                     const int wrow = (int)expert * p.N + n0;
@@ -247,7 +254,7 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                 uint32_t expert; int row0, rows, n0;
                 decode(wi, expert, row0, rows, n0);
                 const int nmma = min(BN, (rows + 15) & ~15);
-                const uint32_t idesc = make_idesc(nmma);
+                const uint32_t idesc = make_idesc(nmma, S::PLAIN);
                 const int a = tcount % S::NACC;
                 const uint32_t aph = (tcount / S::NACC) & 1;
                 if (!(ok = mbar_wait(bar_tempty + 8 * a, aph ^ 1, abort_flag))) break;
@@ -257,7 +264,7 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag))) break;
-                    if (!(ok = mbar_wait(bar_ready + 8 * s, ph, abort_flag))) break;
+                    if (!S::PLAIN && !(ok = mbar_wait(bar_ready + 8 * s, ph, abort_flag))) break;
                     tc_fence_after();
                     unsigned char* st = smem + s * S::STAGE_BYTES;
                     const uint64_t bdesc = make_sw128_desc(smem_u32(st));
@@ -346,7 +353,7 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * a);
         }
-    } else {
+    } else if (!S::PLAIN) {
         // ================= dequantisers (256 threads, two groups of four warps) =================
         // Group g takes the K steps with (global step index) % 2 == g: one thread per weight row, both halves of the
         // step. While one group waits for its stage, converts and publishes it, the other is half a period ahead, so the
