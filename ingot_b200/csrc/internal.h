@@ -102,7 +102,7 @@ struct GqmvCall {
 };
 int32_t launch_gqmv(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c);
 
-// One launch of the tensor-core GEMM (csrc/qmm.cu). x16: fp16 activations [x_rows, ldx]; w[i]: stacked
+// One launch of the tensor-core GEMM (csrc/qmm.cu). x16: fp16 activations [x_rows, ldx] (bf16 with the plain bf16 format); w[i]: stacked
 // [experts * N, K] codes (w[1]: the up matrix of the gate/up epilogue). tiles == nullptr: dense tiling over M x N.
 struct QmmCall {
     int32_t fmt = 0;
@@ -111,6 +111,9 @@ struct QmmCall {
     const void* x16 = nullptr;
     int64_t ldx = 0;
     int64_t x_rows = 0;
+    // gathered activation rows (grouped gate/up): row r of a tile is row gather_map[tile.start + r] / gather_div of x16
+    const uint32_t* gather_map = nullptr;
+    uint32_t gather_div = 1;
     const void* w[2] = {nullptr, nullptr};
     const void* s[2] = {nullptr, nullptr};
     const void* b[2] = {nullptr, nullptr};

@@ -223,12 +223,16 @@ int tensor_tile_rows(int64_t rows, int64_t expert_slots) {
     return rows >= expert_slots * kBigTileRowsPerExpert ? kPrefillTileRowsBig : kPrefillTileRows;
 }
 
+// rows16: fp16 rows [n_rows, ld16] in tile order, or (gather_map given) the tokens' rows in place, fetched through
+// gather_map[sorted position] / gather_div.
 int32_t run_gateup_tc(iq_moe* l, cudaStream_t cs, const __half* rows16, int64_t n_rows, const Tile* tiles,
-                      const uint32_t* ntiles, __half* h, int bn) {
+                      const uint32_t* ntiles, __half* h, int bn, const uint32_t* gather_map = nullptr, uint32_t gather_div = 1,
+                      int64_t ld16 = 0, int64_t x_rows = 0) {
     const iq_moe_desc& d = l->d;
     QmmCall c;
     c.fmt = l->fmt; c.epi = 1; c.bn = bn;
-    c.x16 = rows16; c.ldx = d.d_model; c.x_rows = n_rows;
+    c.x16 = rows16; c.ldx = ld16 > 0 ? ld16 : d.d_model; c.x_rows = x_rows > 0 ? x_rows : n_rows;
+    c.gather_map = gather_map; c.gather_div = gather_div;
     c.w[0] = d.gate.w; c.w[1] = d.up.w;
     c.s[0] = d.gate.scales; c.s[1] = d.up.scales;
     c.b[0] = d.gate.biases; c.b[1] = d.up.biases;
@@ -656,9 +660,22 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
     const bool tc = use_tensor_path(P, d.expert_count);
     if (pieces & IQ_PIECE_GATEUP) {
         if (tc) {
-            moe_pack_rows_kernel<<<P, 256, 0, cs>>>(x, x_dtype, ldx, w.pos, w.xs, P, d.d_model, d.top_k);
-            st = check_cuda(ctx, cudaGetLastError(), "moe_pack_rows launch");
-            if (st == kOk) st = run_gateup_tc(l, cs, w.xs, P, w.tiles_b, w.ntiles + 1, w.h, tensor_tile_rows(P, d.expert_count));
+            // The GEMM's producer fetches each tile's token rows through row_map (the reference gathers through rowMap
+            // too, Shaders/qmm_nax_moe.metal:512-586): nothing is packed in expert order. It needs fp16 rows: fp16
+            // activations are used in place, others are converted once per token (not once per routed pair).
+            const __half* x16 = static_cast<const __half*>(x);
+            int64_t ld16 = ldx;
+            st = kOk;
+            if (x_dtype != kF16) {
+                const size_t units = (size_t)tokens * d.d_model / 8;
+                rows_to_f16_kernel<<<(unsigned)((units + 255) / 256), 256, 0, cs>>>(x, x_dtype, ldx, w.xs, tokens, d.d_model);
+                st = check_cuda(ctx, cudaGetLastError(), "rows_to_f16 launch");
+                x16 = w.xs;
+                ld16 = d.d_model;
+            }
+            if (st == kOk)
+                st = run_gateup_tc(l, cs, x16, P, w.tiles_b, w.ntiles + 1, w.h, tensor_tile_rows(P, d.expert_count), w.row_map,
+                                   (uint32_t)d.top_k, ld16, tokens);
         } else {
             st = run_gateup(l, cs, x, x_dtype, ldx, w.row_map, w.tiles_a, w.ntiles, max_tiles, bm, w.h);
         }

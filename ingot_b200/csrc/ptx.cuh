@@ -128,6 +128,15 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  : "memory");
 }
 
+// 16-byte asynchronous copy global -> shared memory (bypassing L1), and the arrival that an mbarrier receives once all
+// of this thread's copies issued so far have landed (.noinc: it counts as one of the barrier's expected arrivals).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // Programmatic dependent launch: let the next kernel in the stream start its independent prologue, and wait for the
 // previous kernel's results before touching anything it may have written. Both are no-ops without the launch attribute.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -17,17 +17,24 @@ struct KernelEntry {
     int bn;
     int epi;
     int act;
+    bool gather;
     QmmKernel fn;
     int smem;
 };
 
-template <int FMT, int BN, int EPI, int ACT = kActSilu>
+template <int FMT, int BN, int EPI, int ACT = kActSilu, bool GATHER = false>
 KernelEntry entry() {
-    return KernelEntry{FMT, BN, EPI, ACT, qmm_tc_kernel<FMT, BN, EPI, ACT>, QmmSmem<FMT, BN, EPI>::TOTAL};
+    return KernelEntry{FMT, BN, EPI, ACT, GATHER, qmm_tc_kernel<FMT, BN, EPI, ACT, GATHER>, QmmSmem<FMT, BN, EPI>::TOTAL};
+}
+// gate/up with the activation rows gathered by row index, both tile heights
+template <int FMT, int ACT>
+void gather_entries(KernelEntry* t, int* n) {
+    t[(*n)++] = entry<FMT, 128, kEpiGateUp, ACT, true>();
+    t[(*n)++] = entry<FMT, 256, kEpiGateUp, ACT, true>();
 }
 
 const KernelEntry* table(int* n) {
-    static const KernelEntry t[] = {
+    static const KernelEntry fixed[] = {
         entry<kFmtAffine4, 256, kEpiStore>(), entry<kFmtAffine4, 128, kEpiStore>(),
         entry<kFmtAffine8, 256, kEpiStore>(), entry<kFmtAffine8, 128, kEpiStore>(),
         entry<kFmtMxfp4, 256, kEpiStore>(),   entry<kFmtMxfp4, 128, kEpiStore>(),
@@ -42,16 +49,31 @@ const KernelEntry* table(int* n) {
         entry<kFmtMxfp4, 128, kEpiGateUp, kActRelu2>(), entry<kFmtMxfp4, 256, kEpiGateUp, kActRelu2>(),
         entry<kFmtBf16Plain, 128, kEpiStore>(),  // bf16 x bf16 (the router's approximate logits)
     };
-    *n = (int)(sizeof(t) / sizeof(t[0]));
+    constexpr int kFixed = (int)(sizeof(fixed) / sizeof(fixed[0]));
+    static KernelEntry t[kFixed + 16];
+    static int count = 0;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        for (int i = 0; i < kFixed; i++) t[count++] = fixed[i];
+        gather_entries<kFmtAffine4, kActSilu>(t, &count);
+        gather_entries<kFmtAffine4, kActGelu>(t, &count);
+        gather_entries<kFmtAffine4, kActSwigluOai>(t, &count);
+        gather_entries<kFmtAffine4, kActRelu2>(t, &count);
+        gather_entries<kFmtMxfp4, kActSilu>(t, &count);
+        gather_entries<kFmtMxfp4, kActGelu>(t, &count);
+        gather_entries<kFmtMxfp4, kActSwigluOai>(t, &count);
+        gather_entries<kFmtMxfp4, kActRelu2>(t, &count);
+    });
+    *n = count;
     return t;
 }
 
-const KernelEntry* find(int32_t fmt, int bn, int epi, int act) {
+const KernelEntry* find(int32_t fmt, int bn, int epi, int act, bool gather) {
     int n;
     const KernelEntry* t = table(&n);
     if (epi != kEpiGateUp) act = kActSilu;
     for (int i = 0; i < n; i++)
-        if (t[i].fmt == fmt && t[i].bn == bn && t[i].epi == epi && t[i].act == act) return &t[i];
+        if (t[i].fmt == fmt && t[i].bn == bn && t[i].epi == epi && t[i].act == act && t[i].gather == gather) return &t[i];
     return nullptr;
 }
 
@@ -123,7 +145,7 @@ int32_t cached_rowblock_map(iq_ctx* ctx, const void* base, int64_t rows, int32_t
 }
 
 int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
-    const KernelEntry* ke = find(c.fmt, c.bn, c.epi, c.act);
+    const KernelEntry* ke = find(c.fmt, c.bn, c.epi, c.act, c.gather_map != nullptr);
     if (ke == nullptr) return fail(ctx, kErrNoKernel, "qmm: no kernel for format %d, tile %d, epilogue %d", c.fmt, c.bn, c.epi);
     const bool plain = c.fmt == kFmtBf16Plain;  // bf16 activations and bf16 weights, both copied as they are
     const int pack_row = c.fmt == kFmtAffine8 ? 64 : 32;
@@ -152,6 +174,10 @@ int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
     p.tiles = c.tiles; p.ntiles = c.ntiles;
     p.y = c.y; p.y_dtype = c.y_dtype; p.ldy = c.ldy; p.accumulate = c.accumulate;
     p.limit = c.limit;
+    p.xg = c.gather_map != nullptr ? static_cast<const __half*>(c.x16) : nullptr;
+    p.gather_map = c.gather_map;
+    p.ldxg = c.ldx;
+    p.gather_div = c.gather_div;
     p.status = ctx->d_status;
     p.reserved = 0;
     int grid = ctx->sms;
@@ -159,7 +185,7 @@ int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
         const int work = ((c.M + c.bn - 1) / c.bn) * ((c.N + kWRows - 1) / kWRows);
         if (work < grid) grid = work;
     }
-    ke->fn<<<grid, kQmmThreads, ke->smem, st>>>(mx, mw0, mw1, p);
+    ke->fn<<<grid, c.gather_map != nullptr ? kQmmGatherThreads : kQmmThreads, ke->smem, st>>>(mx, mw0, mw1, p);
     return check_cuda(ctx, cudaGetLastError(), "qmm launch");
 }
 
@@ -169,6 +195,8 @@ using namespace iq;
 
 extern "C" int32_t iq_qmm_workspace_bytes(iq_ctx* ctx, const iq_qlinear* m, int32_t rows, int32_t x_dtype, size_t* bytes) {
     if (ctx == nullptr || m == nullptr || bytes == nullptr || rows < 1) return kErrInvalidArg;
+    // The MMA takes fp16 weights with fp16 activations only (a bf16 B operand beside an fp16 A operand is an illegal
+    // instruction on sm_100a: kind::f16 wants both operands of one type), so bf16 and fp32 activations are converted
     *bytes = x_dtype == IQ_F16 ? 0 : round_up_sz((size_t)rows * m->k * 2, 256);
     return kOk;
 }

@@ -28,6 +28,7 @@
 namespace iq {
 
 constexpr int kQmmThreads = 448;
+constexpr int kQmmGatherThreads = 544;  // + three warps that help the producer fetch gathered activation rows
 constexpr int kBK = 64;              // inputs per K step (= one affine group, two mxfp4 groups)
 constexpr int kWRows = 128;          // weight rows per tile (MMA M)
 
@@ -50,6 +51,13 @@ struct QmmParams {
     int32_t accumulate;
     const float* ebias[2];   // fp32 [E, N] or null
     float limit;
+    // Gathered activations (grouped gate/up): row r of a tile is row gather_map[tile.start + r] / gather_div of xg (fp16
+    // [*, ldxg]) instead of row tile.start + r of the tensor map's matrix: the producer warp fetches the rows itself with
+    // 16-byte asynchronous copies, so the rows never have to be packed in expert order first. Null: the tensor map.
+    const __half* xg;
+    const uint32_t* gather_map;
+    int64_t ldxg;
+    uint32_t gather_div;
     int32_t* status;         // device status word (0 = ok)
     int32_t reserved;        // keeps the parameter block off an exact 512 bytes: at that size the fused gate/up kernel
                              // measured a quarter slower (487 against 386 us on the 4096-token layer), same code otherwise
@@ -66,8 +74,9 @@ __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr) {
     d |= (uint64_t)2 << 61;              // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor, kind::f16: D = f32, A = B = f16 (or both bf16), both K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t make_idesc(int n, bool bf16 = false) {
+// Instruction descriptor, kind::f16: D = f32, A and B both f16 or both bf16 (the two format fields must agree: fp16
+// weights with bf16 activations raised "illegal instruction" on sm_100a), both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc(int n, bool bf16) {
     return (1u << 4) | (bf16 ? (1u << 7) | (1u << 10) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kWRows >> 4) << 24);
 }
 
@@ -146,8 +155,10 @@ struct QmmSmem {
 
 // ACT: activation of the gate/up epilogue (kAct*), fixed at compile time: the epilogue is on the critical path when gate
 // and up fill tensor memory, and a run-time choice in its inner loop measured a quarter slower.
-template <int FMT, int BN, int EPI, int ACT = kActSilu>
-__global__ void __launch_bounds__(kQmmThreads, 1)
+// GATHER: the activation rows of a tile are fetched by row index (three more warps help the producer); a variant of
+// its own because more than 448 threads cap the registers at 96 per thread, which costs the dense kernels 4-8 %.
+template <int FMT, int BN, int EPI, int ACT = kActSilu, bool GATHER = false>
+__global__ void __launch_bounds__(GATHER ? kQmmGatherThreads : kQmmThreads, 1)
     qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w0,
                   const __grid_constant__ CUtensorMap map_w1, const QmmParams p) {
     using S = QmmSmem<FMT, BN, EPI>;
@@ -161,12 +172,14 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
     const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    constexpr bool gather = GATHER;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(bar_full + 8 * s, 1);
+            // the producer's arrive.expect_tx; gathered rows: plus one arrival per lane when its copies have landed
+            mbar_init(bar_full + 8 * s, gather ? 129 : 1);
             mbar_init(bar_ready + 8 * s, 4);  // the four warps of the dequantiser group that owns the step
             mbar_init(bar_empty + 8 * s, 1);
         }
@@ -215,7 +228,54 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
         }
     };
 
-    if (warp == 0) {
+    if (gather && (warp == 0 || warp >= 14)) {
+        // ================= producers, gathered activation rows: warps 0, 14, 15, 16 =================
+        // Producer warp pw copies rows [pw * BN / 4, (pw + 1) * BN / 4) of every tile: a lane takes 16-byte chunk c of rows
+        // rq, rq + 4, ... of that range (eight lanes cover one row's 128 bytes), with the rows' indices in registers for
+        // the whole tile. Warp 0's first lane also issues the tensor copies of the packed weight tiles.
+        constexpr int RPL = BN / 16;  // rows per lane
+        const int pw = warp == 0 ? 0 : warp - 13;
+        const int c = lane & 7, rq = lane >> 3;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int wi = blockIdx.x; wi < total_work && ok; wi += gridDim.x) {
+            uint32_t expert; int row0, rows, n0;
+            decode(wi, expert, row0, rows, n0);
+            uint32_t g[RPL];
+#pragma unroll
+            for (int i = 0; i < RPL; i++) {
+                const int r = pw * (BN / 4) + 4 * i + rq;
+                g[i] = r < rows ? p.gather_map[row0 + r] / p.gather_div : 0xFFFFFFFFu;
+            }
+            const int wrow = (int)expert * p.N + n0;
+            for (int ks = 0; ks < ksteps; ks++, it++) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                ok = mbar_wait_relaxed(bar_empty + 8 * s, ph ^ 1, abort_flag);
+                if (!(ok = __all_sync(0xffffffffu, ok))) break;
+                unsigned char* st = smem + s * S::STAGE_BYTES;
+                if (warp == 0 && lane == 0) {
+                    mbar_arrive_expect_tx(bar_full + 8 * s, NWT * S::WP_BYTES);
+                    tma_load_2d(smem_u32(st + S::X_BYTES + NWT * S::WD_BYTES), &map_w0, bar_full + 8 * s, ks * S::PACK_ROW, wrow);
+                    if (NWT == 2)
+                        tma_load_2d(smem_u32(st + S::X_BYTES + NWT * S::WD_BYTES + S::WP_BYTES), &map_w1, bar_full + 8 * s,
+                                    ks * S::PACK_ROW, wrow);
+                }
+                // row r of the tile lands where the tensor copy would have put it: 128-byte rows, eight-row groups of
+                // 1024 bytes, the 16-byte chunks of a row XORed with the row's index in its group. Rows beyond the
+                // tile's keep whatever the stage held: a column of B only feeds its own column of D, which is not stored.
+                const __half* src0 = p.xg + (size_t)ks * kBK + c * 8;
+                const uint32_t dst0 = smem_u32(st);
+#pragma unroll
+                for (int i = 0; i < RPL; i++) {
+                    const int r = pw * (BN / 4) + 4 * i + rq;
+                    if (g[i] != 0xFFFFFFFFu)
+                        cp_async16(dst0 + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4), src0 + (size_t)g[i] * p.ldxg);
+                }
+                cp_async_arrive_noinc(bar_full + 8 * s);
+            }
+        }
+    } else if (warp == 0) {
         // ================= TMA producer =================
         if (lane == 0) {
             uint32_t it = 0;
@@ -304,6 +364,29 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
                 if (EPI == kEpiGateUp) tmem_ld32(tbase + BN + c0, r1);
                 tmem_ld_wait();
                 if (!n_ok) continue;
+                if (EPI == kEpiStore && p.tiles == nullptr) {
+                    // Dense tiling: two accumulators, the epilogue runs under the next tile's main loop and has time
+                    // to spare. Element after element with the exit test between them, its stores trickle out; issued
+                    // as a burst of 32 (the branch-free form below) they got in the way of the dequantisers' shared-
+                    // memory traffic and cost the dense GEMM 4-8 % (253.8 -> 265 us at M = 2048, 85 -> 93 at M = 512).
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (c0 + j >= rows) break;
+                        const float v = __uint_as_float(r0[j]) + bias0;
+                        const size_t o = (size_t)(row0 + c0 + j) * p.ldy + n;
+                        if (p.y_dtype == kF32) {
+                            float* yp = reinterpret_cast<float*>(p.y) + o;
+                            *yp = p.accumulate ? *yp + v : v;
+                        } else if (p.y_dtype == kF16) {
+                            __half* yp = reinterpret_cast<__half*>(p.y) + o;
+                            *yp = __float2half_rn(p.accumulate ? __half2float(*yp) + v : v);
+                        } else {
+                            uint16_t* yp = reinterpret_cast<uint16_t*>(p.y) + o;
+                            *yp = (uint16_t)f32_to_bf16_bits(p.accumulate ? bf16_bits_to_f32(*yp) + v : v);
+                        }
+                    }
+                    continue;
+                }
                 // The 32 token columns of this thread's output feature. No early exit inside the loops: an exit test
                 // between the elements serialises them (each then pays the whole dependent chain of the activation,
                 // about a hundred cycles) and made the epilogue a third of the grouped GEMM's time; the columns beyond
@@ -353,7 +436,7 @@ __global__ void __launch_bounds__(kQmmThreads, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * a);
         }
-    } else if (!S::PLAIN) {
+    } else if (!S::PLAIN && warp < 14) {
         // ================= dequantisers (256 threads, two groups of four warps) =================
         // Group g takes the K steps with (global step index) % 2 == g: one thread per weight row, both halves of the
         // step. While one group waits for its stage, converts and publishes it, the other is half a period ahead, so the
