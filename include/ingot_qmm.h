@@ -75,8 +75,10 @@ typedef struct iq_qlinear {
     const void* biases; /* NULL for mxfp4 */
     int32_t n;          /* output features (rows of W) */
     int32_t k;          /* input features */
-    int32_t bits;       /* 4 or 8; 6 for the decode GEMV (k a multiple of 2048) and the embedding */
-    int32_t group;      /* 64 (affine; 32 also for the 4-bit decode GEMV and the embedding) or 32 (mxfp4) */
+    int32_t bits;       /* 4 or 8; 6 for the decode GEMV (k a multiple of 2048) and the embedding; 2 = the rotated
+                           ternary format: group 128, `scales` fp16, biases unused (w = (q - 1) * scale), activations
+                           rotated by iq_had_rows first (Shaders/xc_tern.metal) */
+    int32_t group;      /* 64 (affine; 32 also for the 4-bit decode GEMV and the embedding), 128 (ternary) or 32 (mxfp4) */
     int32_t mode;       /* iq_mode */
     int32_t experts;    /* leading dimension, 1 for a plain layer */
 } iq_qlinear;
@@ -343,6 +345,18 @@ int32_t iq_linear_colsplit(iq_colsplit* cs, void* stream, const void* x, int32_t
  * tokens is a device array; a token >= table->n gives a zero row. */
 int32_t iq_embed_rows(iq_ctx* ctx, void* stream, const iq_qlinear* table, const uint32_t* tokens, int32_t rows,
                       float* out_f32, void* out_f16, int64_t ldo);
+
+/* ---- the rotated ternary format ------------------------------------------------------------------------------------------
+ * y[r, :] = half(H_1024(x[r, :] * signs) / 32) per block of 1024 inputs: the input rotation that precedes every ternary
+ * matrix (had_rows_h, Shaders/xc_tern.metal:29-40; DenseQ.encodeRotate in Layers/Linear.swift:292-297). x of any
+ * dtype, y fp16 [rows, ldy], k a multiple of 1024, signs fp32 [k]. iq_qmv (fp16 x, rows <= 16) and iq_qmm then take the
+ * rotated rows with a 2-bit iq_qlinear. */
+int32_t iq_had_rows(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx, const float* signs, void* y_f16,
+                    int64_t ldy, int32_t rows, int32_t k);
+/* Rows of a ternary table, dequantised and rotated back (H_1024(row) / 32 * signs): embed_rows_t
+ * (Shaders/xc_tern.metal:44-65; the bonsai-embed case, Tests/IngotTests/KernelCaseTests.swift:133-155). */
+int32_t iq_embed_rows_ternary(iq_ctx* ctx, void* stream, const iq_qlinear* table, const float* signs, const uint32_t* tokens,
+                              int32_t rows, float* out_f32, void* out_f16, int64_t ldo);
 
 /* ---- after the lm_head GEMV (decode) ----------------------------------------------------------------------------------
  * out[r] = index of the largest of x[r, 0..n), ties to the lower index (argmax_rows, Shaders/verify.metal:525-547). */

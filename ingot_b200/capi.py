@@ -29,7 +29,7 @@ SYMBOLS = [
     "iq_st_open", "iq_st_close", "iq_st_count", "iq_st_entry", "iq_st_find", "iq_st_last_error", "iq_widen4to8_words",
     "iq_scales_div16_bf16", "iq_argmax_rows", "iq_topk64_scratch_bytes", "iq_topk64", "iq_embed_rows",
     "iq_ctx_set_wait_cycles", "iq_colsplit_create", "iq_colsplit_destroy", "iq_linear_colsplit_workspace_bytes",
-    "iq_linear_colsplit",
+    "iq_linear_colsplit", "iq_had_rows", "iq_embed_rows_ternary",
 ]
 
 
@@ -148,6 +148,10 @@ def lib() -> C.CDLL:
         for name in ("iq_ctx_set_wait_cycles", "iq_colsplit_create", "iq_linear_colsplit_workspace_bytes",
                      "iq_linear_colsplit"):
             getattr(l, name).restype = i32
+        l.iq_had_rows.argtypes = [vp, vp, vp, i32, i64, vp, vp, i64, i32, i32]
+        l.iq_embed_rows_ternary.argtypes = [vp, vp, C.POINTER(QLinear), vp, vp, i32, vp, vp, i64]
+        l.iq_had_rows.restype = i32
+        l.iq_embed_rows_ternary.restype = i32
         l.iq_moe_pack_rows.argtypes = [vp, vp, vp, i32, i64, i32, vp, sz, vp]
         l.iq_moe_experts_workspace_bytes.argtypes = [vp, i32, i32, C.POINTER(sz)]
         l.iq_moe_experts.argtypes = [vp, vp, vp, i32, i32, vp, i32, i32, vp, i32, vp, vp, sz]

@@ -48,6 +48,7 @@ const KernelEntry* table(int* n) {
         entry<kFmtMxfp4, 128, kEpiGateUp, kActGelu>(), entry<kFmtMxfp4, 256, kEpiGateUp, kActGelu>(),
         entry<kFmtMxfp4, 128, kEpiGateUp, kActRelu2>(), entry<kFmtMxfp4, 256, kEpiGateUp, kActRelu2>(),
         entry<kFmtBf16Plain, 128, kEpiStore>(),  // bf16 x bf16 (the router's approximate logits)
+        entry<kFmtTernary, 256, kEpiStore>(), entry<kFmtTernary, 128, kEpiStore>(),
     };
     constexpr int kFixed = (int)(sizeof(fixed) / sizeof(fixed[0]));
     static KernelEntry t[kFixed + 16];
@@ -148,7 +149,7 @@ int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
     const KernelEntry* ke = find(c.fmt, c.bn, c.epi, c.act, c.gather_map != nullptr);
     if (ke == nullptr) return fail(ctx, kErrNoKernel, "qmm: no kernel for format %d, tile %d, epilogue %d", c.fmt, c.bn, c.epi);
     const bool plain = c.fmt == kFmtBf16Plain;  // bf16 activations and bf16 weights, both copied as they are
-    const int pack_row = c.fmt == kFmtAffine8 ? 64 : 32;
+    const int pack_row = c.fmt == kFmtAffine8 ? 64 : (c.fmt == kFmtTernary ? 16 : 32);
     const uint64_t row_bytes = (uint64_t)c.K / kBK * pack_row;
     CUtensorMap mx, mw0, mw1;
     int32_t r = make_map_2d(ctx, &mx, c.x16, plain ? 2 : 1, (uint64_t)c.K, (uint64_t)c.x_rows, (uint64_t)c.ldx * 2, kBK, c.bn, true);
@@ -209,9 +210,12 @@ extern "C" int32_t iq_qmm(iq_ctx* ctx, void* stream, const void* x, int32_t x_dt
         return fail(ctx, kErrInvalidArg, "qmm: null pointer");
     const int32_t fmt = format_of(m);
     if (fmt < 0 || fmt == kFmtAffine6)
-        return fail(ctx, kErrUnsupported, "qmm: %d-bit group %d mode %d has no kernel (affine 4/8-bit g64, 4-bit g32, mxfp4 g32)",
+        return fail(ctx, kErrUnsupported,
+                    "qmm: %d-bit group %d mode %d has no kernel (affine 4/8-bit g64, 4-bit g32, ternary 2-bit g128, mxfp4 g32)",
                     m->bits, m->group, m->mode);
-    if (fmt != kFmtMxfp4 && m->biases == nullptr) return fail(ctx, kErrInvalidArg, "qmm: affine layer without biases");
+    if (fmt != kFmtMxfp4 && fmt != kFmtTernary && m->biases == nullptr)
+        return fail(ctx, kErrInvalidArg, "qmm: affine layer without biases");
+    if (fmt == kFmtTernary && m->k % 128 != 0) return fail(ctx, kErrInvalidArg, "qmm: ternary k = %d must be a multiple of 128", m->k);
     // the reference's preconditions (Layers/Linear.swift:695)
     if (rows < 64 || rows % 64 != 0) return fail(ctx, kErrInvalidArg, "qmm: rows = %d must be a multiple of 64", rows);
     if (m->n % 64 != 0 || m->k % 64 != 0 || m->n <= 0 || m->k <= 0)

@@ -121,6 +121,25 @@ __device__ __forceinline__ void dequant32(uint32_t packed_row_half, uint32_t sc_
             }
             out[i] = make_uint4(o[0], o[1], o[2], o[3]);
         }
+    } else if (FMT == kFmtTernary) {
+        // 32 codes of two bits in eight bytes; w = (q - 1) * s with the fp16 scale as it is stored: exact in fp16
+        const uint2 v = lds64(packed_row_half);
+        const uint32_t s2 = (sc_raw & 0xFFFFu) | (sc_raw << 16);
+        const uint32_t k1025 = 0x64016401u;
+        const uint32_t w[2] = {v.x, v.y};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t h16 = w[i >> 1] >> ((i & 1) * 16);  // eight codes in the low 16 bits
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint32_t t = ((h16 >> (4 * j)) & 3u) | (((h16 >> (4 * j + 2)) & 3u) << 16) | 0x64006400u;  // 1024 + q
+                __half2 q = __hsub2(*reinterpret_cast<const __half2*>(&t), *reinterpret_cast<const __half2*>(&k1025));
+                __half2 r = __hmul2(q, *reinterpret_cast<const __half2*>(&s2));
+                o[j] = *reinterpret_cast<uint32_t*>(&r);
+            }
+            out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
     } else {
         const uint4 v = lds128(packed_row_half);
         const DqConst d = make_dq<kFmtMxfp4>(sc_raw);
@@ -139,7 +158,7 @@ template <int FMT, int BN, int EPI>
 struct QmmSmem {
     static constexpr int NWT = EPI == kEpiGateUp ? 2 : 1;                 // weight tiles per stage
     static constexpr bool PLAIN = FMT == kFmtBf16Plain;                   // bf16 weights used as they are: no packed tile
-    static constexpr int PACK_ROW = PLAIN ? 0 : (FMT == kFmtAffine8 ? 64 : 32);  // packed bytes per row per K step
+    static constexpr int PACK_ROW = PLAIN ? 0 : (FMT == kFmtAffine8 ? 64 : (FMT == kFmtTernary ? 16 : 32));  // packed bytes per row per K step
     static constexpr int X_BYTES = BN * 128;
     static constexpr int WD_BYTES = kWRows * 128;
     static constexpr int WP_BYTES = kWRows * PACK_ROW;
@@ -213,7 +232,7 @@ __global__ void __launch_bounds__(GATHER ? kQmmGatherThreads : kQmmThreads, 1)
         total_work = m_tiles * n_tiles_n;
     }
     const int ksteps = p.K / kBK;
-    const int row_groups = p.K / ((FMT == kFmtMxfp4 || FMT == kFmtAffine4G32) ? 32 : 64);
+    const int row_groups = p.K / ((FMT == kFmtMxfp4 || FMT == kFmtAffine4G32) ? 32 : (FMT == kFmtTernary ? 128 : 64));
 
     // Decodes work item `wi` into (expert, first token row, live token rows, first weight row).
     auto decode = [&](int wi, uint32_t& expert, int& row0, int& rows, int& n0) {
@@ -475,6 +494,9 @@ __global__ void __launch_bounds__(GATHER ? kQmmGatherThreads : kQmmThreads, 1)
                     const unsigned char* sp = reinterpret_cast<const unsigned char*>(p.s[wt]) + c.srow + 2 * c.ks;
                     v.sc[wt][0] = live ? ldg_nc_u8_early(sp) : 127u;
                     v.sc[wt][1] = live ? ldg_nc_u8_early(sp + 1) : 127u;
+                    v.bi[wt][0] = 0;
+                } else if (FMT == kFmtTernary) {  // one fp16 scale per 128 inputs = two K steps, no bias tensor
+                    v.sc[wt][0] = v.sc[wt][1] = live ? ldg_nc_u16_early(reinterpret_cast<const uint16_t*>(p.s[wt]) + c.srow + (c.ks >> 1)) : 0u;
                     v.bi[wt][0] = 0;
                 } else if (FMT == kFmtAffine4G32) {
 #pragma unroll

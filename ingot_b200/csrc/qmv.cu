@@ -494,6 +494,7 @@ int32_t format_of(const iq_qlinear* m) {
     if (m->mode == IQ_MODE_MXFP4) return (m->bits == 4 && m->group == 32) ? kFmtMxfp4 : -1;
     if (m->mode != IQ_MODE_AFFINE) return -1;
     if (m->group == 32) return m->bits == 4 ? kFmtAffine4G32 : -1;
+    if (m->group == 128) return m->bits == 2 ? kFmtTernary : -1;
     if (m->group != 64) return -1;
     if (m->bits == 6) return kFmtAffine6;
     if (m->bits == 4) return kFmtAffine4;
@@ -512,9 +513,10 @@ extern "C" int32_t iq_qmv(iq_ctx* ctx, void* stream, const void* x, int32_t x_dt
         return fail(ctx, kErrInvalidArg, "qmv: null pointer");
     const int32_t fmt = format_of(m);
     if (fmt < 0)
-        return fail(ctx, kErrUnsupported, "qmv: %d-bit group %d mode %d has no kernel (affine 4/6/8-bit g64, 4-bit g32, mxfp4 g32)",
+        return fail(ctx, kErrUnsupported, "qmv: %d-bit group %d mode %d has no kernel (affine 4/6/8-bit g64, 4-bit g32, ternary 2-bit g128, mxfp4 g32)",
                     m->bits, m->group, m->mode);
-    if (fmt != kFmtMxfp4 && m->biases == nullptr) return fail(ctx, kErrInvalidArg, "qmv: affine layer without biases");
+    if (fmt != kFmtMxfp4 && fmt != kFmtTernary && m->biases == nullptr)
+        return fail(ctx, kErrInvalidArg, "qmv: affine layer without biases");
     if (rows < 1 || rows > 16) return fail(ctx, kErrInvalidArg, "qmv: rows = %d (1..16)", rows);
     if (m->n % 16 != 0 || m->k % 64 != 0 || m->n <= 0 || m->k <= 0)
         return fail(ctx, kErrInvalidArg, "qmv: n = %d must be a multiple of 16 and k = %d of 64", m->n, m->k);
@@ -527,6 +529,9 @@ extern "C" int32_t iq_qmv(iq_ctx* ctx, void* stream, const void* x, int32_t x_dt
         n = n_prefix;
     }
     if (ldy < n) return fail(ctx, kErrInvalidArg, "qmv: ldy = %lld < n", (long long)ldy);
+    if (fmt == kFmtTernary)  // the rotated ternary format has kernels of its own (csrc/tern.cu)
+        return launch_tern_qmv(ctx, reinterpret_cast<cudaStream_t>(stream), x, x_dtype, ldx, m, y, y_dtype, ldy, rows, n,
+                               (flags & IQ_FLAG_ACCUMULATE) ? 1 : 0);
     GqmvCall c;
     c.mode = kModePlain;
     c.fmt = fmt;

@@ -42,6 +42,7 @@ class DenseQ:
 
     def __init__(self, w: torch.Tensor, scales: torch.Tensor, biases: Optional[torch.Tensor], N: int, K: int, bits: int,
                  gs: int = 64, mode: str = "affine", experts: int = 1):
+        self.had, self._rot = None, None
         if bits == 16:
             # a plain bf16 table (an unquantized embedding, Linear.swift:58-63): only encode_embed takes it
             _need_cuda(w)
@@ -49,6 +50,16 @@ class DenseQ:
                 raise ValueError("a 16-bit table is bf16 [N, K] without scales or biases")
             self.w, self.s, self.b = w.contiguous(), None, None
             self.N, self.K, self.bits, self.gs, self.mode, self.experts = N, K, 16, 64, "affine", 1
+            return
+        if bits == 2:
+            # the rotated ternary format (xc_tern.metal): 2-bit codes, groups of 128, fp16 scales, w = (q - 1) * s
+            _need_cuda(w, scales)
+            if gs != 128 or mode != "affine" or scales.dtype != torch.float16 or experts != 1:
+                raise ValueError("a 2-bit layer is ternary: groups of 128, fp16 scales, one matrix")
+            if w.dtype not in (torch.int32, torch.uint32) or w.numel() != N * K // 16 or scales.numel() != N * (K // 128):
+                raise ValueError(f"bits do not add up (packed {tuple(w.shape)}, N {N}, K {K}, 2 bits)")
+            self.w, self.s, self.b = w.contiguous(), scales.contiguous(), None
+            self.N, self.K, self.bits, self.gs, self.mode, self.experts = N, K, 2, 128, "affine", 1
             return
         _need_cuda(w, scales, biases)
         if mode not in ("affine", "mxfp4"):
@@ -86,6 +97,23 @@ class DenseQ:
         n = self.w.numel() * self.w.element_size() + (0 if self.s is None else self.s.numel() * self.s.element_size())
         return n + (0 if self.b is None else self.b.numel() * 2)
 
+    # ---- input rotation of the ternary format (Linear.swift encodeRotate; had_rows_h, xc_tern.metal:29-40) ------
+    def set_hadamard(self, signs: torch.Tensor):
+        """Signs (float32 [K], +1 / -1) of the rotation x <- H_1024(x * signs) / 32 that precedes this matrix."""
+        _need_cuda(signs)
+        if signs.dtype != torch.float32 or signs.numel() != self.K or self.K % 1024 != 0:
+            raise ValueError("the rotation's signs are float32 [K], K a multiple of 1024")
+        self.had = signs.contiguous()
+
+    def encode_rotate(self, x: torch.Tensor, rows: int, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        """x[rows, K] rotated into a float16 scratch (grown on demand, like the reference's rotation buffer)."""
+        if self._rot is None or self._rot.shape[0] < rows:
+            self._rot = torch.empty(max(rows, 16), self.K, dtype=torch.float16, device=self.w.device)
+        ctx = capi.context(self.device_index)
+        ctx.check(capi.lib().iq_had_rows(ctx.handle, _stream_ptr(stream), x.data_ptr(), _dtype_id(x), x.stride(0),
+                                         self.had.data_ptr(), self._rot.data_ptr(), self.K, rows, self.K))
+        return self._rot
+
     # ---- embedding (Linear.swift:65-93) -------------------------------------------------------------------------
     def encode_embed(self, tok: torch.Tensor, rows: int, out_f: Optional[torch.Tensor] = None,
                      out_h: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None):
@@ -103,6 +131,13 @@ class DenseQ:
         o = out_f if out_f is not None else out_h
         ctx = capi.context(self.device_index)
         q = self.qlinear()
+        if self.bits == 2:  # ternary table: dequantise, then the inverse rotation (embed_rows_t, xc_tern.metal:44-65)
+            if self.had is None:
+                raise ValueError("a ternary table needs the rotation's signs (set_hadamard)")
+            ctx.check(capi.lib().iq_embed_rows_ternary(ctx.handle, _stream_ptr(stream), C.byref(q), self.had.data_ptr(),
+                                                       tok.data_ptr(), rows, 0 if out_f is None else out_f.data_ptr(),
+                                                       0 if out_h is None else out_h.data_ptr(), o.stride(0)))
+            return
         ctx.check(capi.lib().iq_embed_rows(ctx.handle, _stream_ptr(stream), C.byref(q), tok.data_ptr(), rows,
                                            0 if out_f is None else out_f.data_ptr(),
                                            0 if out_h is None else out_h.data_ptr(), o.stride(0)))
@@ -122,6 +157,8 @@ class DenseQ:
         _need_cuda(x, y)
         ctx = capi.context(self.device_index)
         ql = self.qlinear()
+        if self.had is not None:  # rotated basis: the rotation runs first, as in the reference's launcher
+            x = self.encode_rotate(x, rows, stream)
         ws_ptr, ws_bytes = (0, 0) if workspace is None else (workspace.data_ptr(), workspace.numel() * workspace.element_size())
         ctx.check(capi.lib().iq_qmm(ctx.handle, _stream_ptr(stream), x.data_ptr(), _dtype_id(x), x.stride(0), C.byref(ql),
                                     y.data_ptr(), _dtype_id(y), y.stride(0), rows,
@@ -156,6 +193,8 @@ class VQMV:
         _need_cuda(x, y)
         ctx = capi.context(m.device_index)
         ql = m.qlinear()
+        if m.had is not None:  # Linear.swift:292-297: the input rotation first, then the kernel on the rotated rows
+            x, ldx = m.encode_rotate(x, rows, stream), m.K
         ctx.check(capi.lib().iq_qmv(ctx.handle, _stream_ptr(stream), x.data_ptr(), _dtype_id(x),
                                     ldx if ldx is not None else (x.stride(0) if x.dim() > 1 else m.K), C.byref(ql),
                                     y.data_ptr(), _dtype_id(y),

@@ -50,6 +50,18 @@ def mxfp4_np(rng: np.random.Generator, N: int, K: int, experts: int = 1):
     return w, s
 
 
+def ternary_np(rng: np.random.Generator, N: int, K: int):
+    """The rotated ternary format as the reference's tests draw it (Syn.ternary, KernelHarness.swift:125-148): codes q in
+    {0, 1, 2} sixteen per word, one fp16 scale in [0.01, 0.04) per group of 128, and the rotation's signs.
+    Returns (w uint32 [N, K/16], scales float16 [N, K/128], signs float32 [K])."""
+    q = rng.integers(0, 3, size=(N, K), dtype=np.uint64)
+    sh = (2 * (np.arange(K, dtype=np.uint64) % 16))[None, :]
+    w = (q << sh).reshape(N, K // 16, 16).sum(axis=2).astype(np.uint32)
+    scales = (0.01 + 0.03 * rng.random(size=(N, K // 128))).astype(np.float16)
+    signs = np.where(rng.integers(0, 2, size=K) == 0, 1.0, -1.0).astype(np.float32)
+    return w, scales, signs
+
+
 def activations_np(rng: np.random.Generator, rows: int, K: int) -> np.ndarray:
     """x ~ N(0, 1) rounded to bf16, returned as float32 values."""
     return round_bf16(rng.normal(0, 1, size=(rows, K)).astype(np.float32))
@@ -77,6 +89,14 @@ def dense_q_affine(w: np.ndarray, s: np.ndarray, b: np.ndarray, bits: int, devic
     E, N, words = w.shape
     K = words * 32 // bits
     return DenseQ(_u32_tensor(w, device), _bf16_tensor(s, device), _bf16_tensor(b, device), N, K, bits, group, "affine", E)
+
+
+def dense_q_ternary(w: np.ndarray, scales: np.ndarray, signs: np.ndarray, device) -> DenseQ:
+    N, K = w.shape[0], w.shape[1] * 16
+    m = DenseQ(torch.from_numpy(w.view(np.int32).copy()).to(device), torch.from_numpy(scales.copy()).to(device), None, N, K, 2,
+               128, "affine")
+    m.set_hadamard(torch.from_numpy(signs.copy()).to(device))
+    return m
 
 
 def dense_q_mxfp4(w: np.ndarray, s: np.ndarray, device) -> DenseQ:
