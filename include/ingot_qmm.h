@@ -144,6 +144,19 @@ int32_t iq_qmm(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_
 int32_t iq_qmm_noalloc(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx, const iq_qlinear* m,
                        void* y, int32_t y_dtype, int64_t ldy, int32_t rows, uint32_t flags);
 
+/* Rotated W8A8 prefill GEMM (lossy; an option of the serving path, not the default). Replaces DenseQ.encodeQmmI8(ctx, enc,
+ * x:, y:, rows:, scratch:, accumulate:, halfOut:) (Sources/Ingot/Layers/Dense.swift:99-172) and w4_i8rot /
+ * quant_rows_rot_i8g / qmm_i8 (Shaders/xa_dense_i8.metal): per call the 4-bit weights and the activations are rotated
+ * along K (unnormalised Hadamard of 256 inputs per block when k / 32 is a multiple of 32, else of 32), quantised to int8
+ * per row, and Y = (Xq Wq^T) sx sw / n runs on the int8 tensor cores. The workspace (the reference's DenseI8Scratch)
+ * holds the int8 weights [n, k], the int8 activations [rows, k] and both scale vectors. 4-bit affine weights only
+ * (group 64 or 32), rows and n multiples of 64, k a multiple of 128. Bound of the reference's int8-serve case
+ * (Tests/IngotTests/KernelCaseTests.swift:623-661): relative RMS error 2e-3 against the CPU emulation of the same
+ * arithmetic, 5e-2 against the exact product. */
+int32_t iq_qmm_w8a8_workspace_bytes(iq_ctx* ctx, const iq_qlinear* m, int32_t rows, size_t* bytes);
+int32_t iq_qmm_w8a8(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx, const iq_qlinear* m, void* y,
+                    int32_t y_dtype, int64_t ldy, int32_t rows, uint32_t flags, void* workspace, size_t workspace_bytes);
+
 /* ---- dense gated FFN ------------------------------------------------------------------------------------------------
  * out[rows, d] (+)= down( act(gate x) * up x ) with gate|up concatenated by rows as one [2*d_ff, d] matrix (gate rows
  * first). Replaces DenseMLP.encode / encodePrefill (Sources/Ingot/Layers/Dense.swift:56-96) and dswiglu*

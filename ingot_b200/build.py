@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIBDIR, "libingot_qmm.so")
-SOURCES = ["api.cu", "qmv.cu", "moe.cu", "qmm.cu", "ep.cu", "colsplit.cu", "loader.cu", "sample.cu", "embed.cu", "tern.cu"]
+SOURCES = ["api.cu", "qmv.cu", "moe.cu", "qmm.cu", "ep.cu", "colsplit.cu", "loader.cu", "sample.cu", "embed.cu", "tern.cu", "w8a8.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -29,7 +29,7 @@ SYMBOLS = [
     "iq_st_open", "iq_st_close", "iq_st_count", "iq_st_entry", "iq_st_find", "iq_st_last_error", "iq_widen4to8_words",
     "iq_scales_div16_bf16", "iq_argmax_rows", "iq_topk64_scratch_bytes", "iq_topk64", "iq_embed_rows",
     "iq_ctx_set_wait_cycles", "iq_colsplit_create", "iq_colsplit_destroy", "iq_linear_colsplit_workspace_bytes",
-    "iq_linear_colsplit", "iq_had_rows", "iq_embed_rows_ternary",
+    "iq_linear_colsplit", "iq_had_rows", "iq_embed_rows_ternary", "iq_qmm_w8a8_workspace_bytes", "iq_qmm_w8a8",
 ]
 
 
@@ -150,6 +150,10 @@ def lib() -> C.CDLL:
             getattr(l, name).restype = i32
         l.iq_had_rows.argtypes = [vp, vp, vp, i32, i64, vp, vp, i64, i32, i32]
         l.iq_embed_rows_ternary.argtypes = [vp, vp, C.POINTER(QLinear), vp, vp, i32, vp, vp, i64]
+        l.iq_qmm_w8a8_workspace_bytes.argtypes = [vp, C.POINTER(QLinear), i32, C.POINTER(sz)]
+        l.iq_qmm_w8a8.argtypes = [vp, vp, vp, i32, i64, C.POINTER(QLinear), vp, i32, i64, i32, u32, vp, sz]
+        l.iq_qmm_w8a8_workspace_bytes.restype = i32
+        l.iq_qmm_w8a8.restype = i32
         l.iq_had_rows.restype = i32
         l.iq_embed_rows_ternary.restype = i32
         l.iq_moe_pack_rows.argtypes = [vp, vp, vp, i32, i64, i32, vp, sz, vp]

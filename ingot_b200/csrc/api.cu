@@ -83,6 +83,7 @@ extern "C" int32_t iq_ctx_create(int32_t device, iq_ctx** out) {
     if (st == kOk) st = qmm_init(ctx);
     if (st == kOk) st = moe_init(ctx);
     if (st == kOk) st = tern_init(ctx);
+    if (st == kOk) st = w8a8_init(ctx);
     if (st != kOk) {
         if (ctx->d_status) cudaFree(ctx->d_status);
         if (ctx->qmv_tail_scratch) cudaFree(ctx->qmv_tail_scratch);

@@ -26,8 +26,10 @@ enum : int32_t { kF32 = 0, kF16 = 1, kBF16 = 2 };
 // kFmtAffine4G32: 4-bit affine with groups of 32 (dense matrices); kFmtAffine6: 6-bit affine, groups of 64 (decode GEMV)
 // kFmtBf16Plain: not a quantized format: a bf16 matrix used as it is (the router's approximate logits on the tensor cores)
 // kFmtTernary: 2-bit codes in groups of 128 with an fp16 scale, w = (q - 1) * s (the rotated ternary format)
+// kFmtInt8Plain: not a stored format: int8 rows with a scale per row on both sides (the rotated W8A8 prefill GEMM)
 enum : int32_t {
-    kFmtAffine4 = 0, kFmtAffine8 = 1, kFmtMxfp4 = 2, kFmtAffine4G32 = 3, kFmtAffine6 = 4, kFmtBf16Plain = 5, kFmtTernary = 6
+    kFmtAffine4 = 0, kFmtAffine8 = 1, kFmtMxfp4 = 2, kFmtAffine4G32 = 3, kFmtAffine6 = 4, kFmtBf16Plain = 5, kFmtTernary = 6,
+    kFmtInt8Plain = 7
 };
 
 // FFN activations, numbered as the reference's lab_glu (qmm.metal:9-31): 0 SiLU gate, 1 GELU (tanh form) gate,

@@ -134,6 +134,7 @@ int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c);
 int32_t launch_tern_qmv(iq_ctx* ctx, cudaStream_t st, const void* x, int32_t x_dtype, int64_t ldx, const iq_qlinear* m, void* y,
                         int32_t y_dtype, int64_t ldy, int32_t rows, int32_t n, int32_t accumulate);
 int32_t tern_init(iq_ctx* ctx);
+int32_t w8a8_init(iq_ctx* ctx);
 int32_t gqmv_init(iq_ctx* ctx);
 int32_t qmm_init(iq_ctx* ctx);
 int32_t moe_init(iq_ctx* ctx);

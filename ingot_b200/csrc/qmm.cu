@@ -49,6 +49,7 @@ const KernelEntry* table(int* n) {
         entry<kFmtMxfp4, 128, kEpiGateUp, kActRelu2>(), entry<kFmtMxfp4, 256, kEpiGateUp, kActRelu2>(),
         entry<kFmtBf16Plain, 128, kEpiStore>(),  // bf16 x bf16 (the router's approximate logits)
         entry<kFmtTernary, 256, kEpiStore>(), entry<kFmtTernary, 128, kEpiStore>(),
+        entry<kFmtInt8Plain, 256, kEpiStore>(), entry<kFmtInt8Plain, 128, kEpiStore>(),  // rotated W8A8
     };
     constexpr int kFixed = (int)(sizeof(fixed) / sizeof(fixed[0]));
     static KernelEntry t[kFixed + 16];
@@ -148,7 +149,23 @@ int32_t cached_rowblock_map(iq_ctx* ctx, const void* base, int64_t rows, int32_t
 int32_t launch_qmm(iq_ctx* ctx, cudaStream_t st, const QmmCall& c) {
     const KernelEntry* ke = find(c.fmt, c.bn, c.epi, c.act, c.gather_map != nullptr);
     if (ke == nullptr) return fail(ctx, kErrNoKernel, "qmm: no kernel for format %d, tile %d, epilogue %d", c.fmt, c.bn, c.epi);
+    const bool i8 = c.fmt == kFmtInt8Plain;     // int8 rows on both sides, 128 inputs per K step
     const bool plain = c.fmt == kFmtBf16Plain;  // bf16 activations and bf16 weights, both copied as they are
+    if (i8) {
+        CUtensorMap ax, aw;
+        int32_t ri = make_map_2d(ctx, &ax, c.x16, 0, (uint64_t)c.K, (uint64_t)c.x_rows, (uint64_t)c.ldx, 128, c.bn, true);
+        if (ri == kOk) ri = make_map_2d(ctx, &aw, c.w[0], 0, (uint64_t)c.K, (uint64_t)c.N, (uint64_t)c.K, 128, kWRows, true);
+        if (ri != kOk) return ri;
+        QmmParams q = {};
+        q.s[0] = q.s[1] = c.s[0]; q.b[0] = q.b[1] = c.b[0];
+        q.N = c.N; q.K = c.K; q.M = c.M;
+        q.y = c.y; q.y_dtype = c.y_dtype; q.ldy = c.ldy; q.accumulate = c.accumulate;
+        q.limit = c.limit;
+        q.status = ctx->d_status;
+        const int work = ((c.M + c.bn - 1) / c.bn) * ((c.N + kWRows - 1) / kWRows);
+        ke->fn<<<work < ctx->sms ? work : ctx->sms, kQmmThreads, ke->smem, st>>>(ax, aw, aw, q);
+        return check_cuda(ctx, cudaGetLastError(), "qmm_i8 launch");
+    }
     const int pack_row = c.fmt == kFmtAffine8 ? 64 : (c.fmt == kFmtTernary ? 16 : 32);
     const uint64_t row_bytes = (uint64_t)c.K / kBK * pack_row;
     CUtensorMap mx, mw0, mw1;

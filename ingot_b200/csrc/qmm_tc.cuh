@@ -79,6 +79,10 @@ __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr) {
 __device__ __forceinline__ uint32_t make_idesc(int n, bool bf16) {
     return (1u << 4) | (bf16 ? (1u << 7) | (1u << 10) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kWRows >> 4) << 24);
 }
+// kind::i8: D = s32, A = B = signed 8-bit, both K-major (32 inputs per MMA), M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc_i8(int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kWRows >> 4) << 24);
+}
 
 // ---- dequantisation of 32 consecutive inputs of one weight row into four 16-byte chunks --------------------------
 template <int FMT>
@@ -157,7 +161,9 @@ __device__ __forceinline__ void dequant32(uint32_t packed_row_half, uint32_t sc_
 template <int FMT, int BN, int EPI>
 struct QmmSmem {
     static constexpr int NWT = EPI == kEpiGateUp ? 2 : 1;                 // weight tiles per stage
-    static constexpr bool PLAIN = FMT == kFmtBf16Plain;                   // bf16 weights used as they are: no packed tile
+    static constexpr bool I8 = FMT == kFmtInt8Plain;                      // int8 x int8 -> s32, a scale per row on both sides
+    static constexpr bool PLAIN = FMT == kFmtBf16Plain || I8;             // weights used as they are: no packed tile
+    static constexpr int BKE = I8 ? 128 : kBK;                            // inputs per K step (128 bytes of a row either way)
     static constexpr int PACK_ROW = PLAIN ? 0 : (FMT == kFmtAffine8 ? 64 : (FMT == kFmtTernary ? 16 : 32));  // packed bytes per row per K step
     static constexpr int X_BYTES = BN * 128;
     static constexpr int WD_BYTES = kWRows * 128;
@@ -231,7 +237,7 @@ __global__ void __launch_bounds__(GATHER ? kQmmGatherThreads : kQmmThreads, 1)
         m_tiles = (p.M + BN - 1) / BN;
         total_work = m_tiles * n_tiles_n;
     }
-    const int ksteps = p.K / kBK;
+    const int ksteps = p.K / S::BKE;
     const int row_groups = p.K / ((FMT == kFmtMxfp4 || FMT == kFmtAffine4G32) ? 32 : (FMT == kFmtTernary ? 128 : 64));
 
     // Decodes work item `wi` into (expert, first token row, live token rows, first weight row).
@@ -309,8 +315,8 @@ __global__ void __launch_bounds__(GATHER ? kQmmGatherThreads : kQmmThreads, 1)
                     unsigned char* st = smem + s * S::STAGE_BYTES;
                     if (S::PLAIN) {  // the bf16 weight tile goes straight where the MMA reads it (128-byte swizzle)
                         mbar_arrive_expect_tx(bar_full + 8 * s, S::X_BYTES + S::WD_BYTES);
-                        tma_load_2d(smem_u32(st), &map_x, bar_full + 8 * s, ks * kBK, row0);
-                        tma_load_2d(smem_u32(st + S::X_BYTES), &map_w0, bar_full + 8 * s, ks * kBK, (int)expert * p.N + n0);
+                        tma_load_2d(smem_u32(st), &map_x, bar_full + 8 * s, ks * S::BKE, row0);
+                        tma_load_2d(smem_u32(st + S::X_BYTES), &map_w0, bar_full + 8 * s, ks * S::BKE, (int)expert * p.N + n0);
                         continue;
                     }
                     mbar_arrive_expect_tx(bar_full + 8 * s, S::X_BYTES + NWT * S::WP_BYTES);
@@ -333,7 +339,7 @@ __global__ void __launch_bounds__(GATHER ? kQmmGatherThreads : kQmmThreads, 1)
                 uint32_t expert; int row0, rows, n0;
                 decode(wi, expert, row0, rows, n0);
                 const int nmma = min(BN, (rows + 15) & ~15);
-                const uint32_t idesc = make_idesc(nmma, S::PLAIN);
+                const uint32_t idesc = S::I8 ? make_idesc_i8(nmma) : make_idesc(nmma, S::PLAIN);
                 const int a = tcount % S::NACC;
                 const uint32_t aph = (tcount / S::NACC) & 1;
                 if (!(ok = mbar_wait(bar_tempty + 8 * a, aph ^ 1, abort_flag))) break;
@@ -351,8 +357,10 @@ __global__ void __launch_bounds__(GATHER ? kQmmGatherThreads : kQmmThreads, 1)
                     for (int wt = 0; wt < NWT; wt++) {
                         const uint64_t adesc = make_sw128_desc(smem_u32(st + S::X_BYTES + wt * S::WD_BYTES));
 #pragma unroll
-                        for (int kk = 0; kk < kBK / 16; kk++)
-                            umma_f16(tacc + wt * BN, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
+                        for (int kk = 0; kk < kBK / 16; kk++) {  // four MMAs of 32 bytes of K each
+                            if (S::I8) umma_i8(tacc + wt * BN, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
+                            else umma_f16(tacc + wt * BN, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
+                        }
                     }
                     umma_commit(bar_empty + 8 * s);  // the stage is free once these MMAs have read it
                 }
@@ -391,7 +399,10 @@ __global__ void __launch_bounds__(GATHER ? kQmmGatherThreads : kQmmThreads, 1)
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         if (c0 + j >= rows) break;
-                        const float v = __uint_as_float(r0[j]) + bias0;
+                        // int8: ((sum * sx[token]) * sw[feature]) / n, in the order of the CPU emulation
+                        const float v = S::I8 ? ((float)(int)r0[j] * reinterpret_cast<const float*>(p.s[0])[row0 + c0 + j]) *
+                                                    reinterpret_cast<const float*>(p.b[0])[n] * p.limit
+                                              : __uint_as_float(r0[j]) + bias0;
                         const size_t o = (size_t)(row0 + c0 + j) * p.ldy + n;
                         if (p.y_dtype == kF32) {
                             float* yp = reinterpret_cast<float*>(p.y) + o;

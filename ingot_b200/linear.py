@@ -164,6 +164,27 @@ class DenseQ:
                                     y.data_ptr(), _dtype_id(y), y.stride(0), rows,
                                     capi.IQ_FLAG_ACCUMULATE if accumulate else 0, ws_ptr, ws_bytes))
 
+    def encode_qmm_i8(self, x: torch.Tensor, y: torch.Tensor, rows: int, accumulate: bool = False,
+                      scratch: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None):
+        """Y[rows, N] (+)= X · Wᵀ in rotated W8A8 (lossy; DenseQ.encodeQmmI8, Dense.swift:131-172): 4-bit weights and
+        activations rotated along K, int8 per row, the product on the int8 tensor cores. `scratch` plays the reference's
+        DenseI8Scratch (sized by `qmm_i8_scratch_bytes`; allocated here when absent)."""
+        _need_cuda(x, y)
+        ctx = capi.context(self.device_index)
+        ql = self.qlinear()
+        if scratch is None:
+            scratch = torch.empty(self.qmm_i8_scratch_bytes(rows), dtype=torch.uint8, device=self.w.device)
+        ctx.check(capi.lib().iq_qmm_w8a8(ctx.handle, _stream_ptr(stream), x.data_ptr(), _dtype_id(x), x.stride(0), C.byref(ql),
+                                         y.data_ptr(), _dtype_id(y), y.stride(0), rows,
+                                         capi.IQ_FLAG_ACCUMULATE if accumulate else 0, scratch.data_ptr(), scratch.numel()))
+
+    def qmm_i8_scratch_bytes(self, rows: int) -> int:
+        ctx = capi.context(self.device_index)
+        n = C.c_size_t()
+        ql = self.qlinear()
+        ctx.check(capi.lib().iq_qmm_w8a8_workspace_bytes(ctx.handle, C.byref(ql), rows, C.byref(n)))
+        return n.value
+
     def encode_qmm_noalloc(self, x: torch.Tensor, y: torch.Tensor, rows: int, accumulate: bool = False,
                            stream: Optional[torch.cuda.Stream] = None):
         """The prefill GEMM for callers that may not allocate device memory (a plugin inside an engine that owns the
