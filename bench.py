@@ -422,12 +422,12 @@ def piece_times(torch, dist, world, stack, r, t_n):
     out["barrier_plan"] = tm(lambda: dx.barrier(then_plan=True))
     merged = [None]
 
-    def compact():
-        merged[0] = dx.compact(b["xc_dx"], b["rows_dx"])
+    def index():
+        merged[0] = dx.index(b["index_dx"], b["rows_dx"])
 
-    out["compact"] = tm(compact)
-    out["experts_gateup_down_return"] = tm(lambda: L.experts(b["xc_dx"], min(t_n * k, dx.max_rows), merged[0], 1, b["yd_dx"],
-                                                            b["ws_dx"], yd_rows=b["rows_dx"]))
+    out["index"] = tm(index)
+    out["experts_gateup_down_return"] = tm(lambda: L.experts_indexed(dx.recv, b["index_dx"], min(t_n * k, dx.max_rows), merged[0],
+                                                                    b["yd_dx"], b["ws_dx"], yd_rows=b["rows_dx"]))
     out["barrier"] = tm(lambda: dx.barrier())
     out["combine"] = tm(lambda: L.combine_rows(dx.back, r, t_n, accumulate=True))
     return out

@@ -281,6 +281,12 @@ int32_t iq_moe_experts_workspace_bytes(const iq_moe* layer, int32_t max_rows, in
 int32_t iq_moe_experts(iq_moe* layer, void* stream, const void* rows_f16, int32_t total_rows, int32_t max_rows,
                        const uint32_t* counts, int32_t sources, int32_t region_rows, void* yd, int32_t yd_dtype,
                        void* const* yd_rows, void* workspace, size_t workspace_bytes);
+/* The same for rows left where they arrived: row i of the expert-major order (sum(counts) rows, experts ascending) is
+ * row row_index[i] of rows_f16 (device array of max_rows entries, e.g. from iq_ep_index); the kernels fetch the rows
+ * through the index, so nothing is gathered first. counts: device uint32 [experts] (one source). */
+int32_t iq_moe_experts_indexed(iq_moe* layer, void* stream, const void* rows_f16, const uint32_t* row_index, int32_t total_rows,
+                               int32_t max_rows, const uint32_t* counts, void* yd, int32_t yd_dtype, void* const* yd_rows,
+                               void* workspace, size_t workspace_bytes);
 /* out[t, :] (+)= sum_k wts[t, k] * yd_rows[pos[t*top_k + k], :] with the routing in `workspace`. */
 int32_t iq_moe_combine_rows(iq_moe* layer, void* stream, const void* yd_rows, int32_t yd_dtype, int32_t tokens, void* out,
                             int32_t out_dtype, int64_t ldo, uint32_t flags, void* workspace, size_t workspace_bytes);
@@ -293,8 +299,9 @@ int32_t iq_moe_combine_rows(iq_moe* layer, void* stream, const void* yd_rows, in
  * [world, experts]). Per layer, on every rank, in stream order:
  *   iq_moe_forward(ROUTER|ROUTE|GROUP); iq_ep_pack_push; iq_ep_barrier(then_plan = 1);
  *   iq_moe_experts(recv, counts = own counts matrix, region_rows); iq_ep_return_push; iq_ep_barrier(0);
- *   (or, faster: iq_ep_compact, then iq_moe_experts(compacted rows, merged counts, 1 source, yd_rows = table), and no
- *   iq_ep_return_push: the rows go from yd straight into the sources' return buffers through the table)
+ *   (or, faster: iq_ep_index, then iq_moe_experts_indexed(recv, row_index, merged counts, yd_rows = table), and no
+ *   iq_ep_return_push: the experts fetch the rows through the index and their outputs go from yd straight into the
+ *   sources' return buffers through the table; iq_ep_compact gathers the rows first instead)
  *   iq_moe_combine_rows(back).
  * Rows move with plain 16-byte peer stores (no TMA, no multicast). Every rank must run the same sequence; the barrier's
  * wait is bounded (IQ_ERR_TIMEOUT in iq_ctx_status when a peer never arrives). At most 8 ranks. */
@@ -326,6 +333,11 @@ int32_t iq_ep_return_rows(iq_ep* ep, void* stream, int32_t yd_dtype, int32_t d_m
  * with sources = 1, region_rows = 0. After iq_ep_barrier(then_plan = 1). */
 int32_t iq_ep_compact(iq_ep* ep, void* stream, const void* recv_rows, int32_t d_model, int32_t yd_dtype, void* rows_out,
                       void** table, const uint32_t** merged_counts);
+/* The same order without moving the rows: row_index[i] = the receive-buffer row at position i of the expert-major order
+ * (device array of world * region_rows entries), table and merged_counts as in iq_ep_compact; for
+ * iq_moe_experts_indexed(recv, row_index, ...). Faster: the rows are read once, by the experts' kernels. */
+int32_t iq_ep_index(iq_ep* ep, void* stream, int32_t d_model, int32_t yd_dtype, uint32_t* row_index, void** table,
+                    const uint32_t** merged_counts);
 
 /* ---- column-split dense linear ---------------------------------------------------------------------------------------
  * One dense quantized linear over the GPUs of one box: rank r holds output features [r*n/G, (r+1)*n/G) (rows of w /

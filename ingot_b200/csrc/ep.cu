@@ -170,6 +170,33 @@ __global__ void __launch_bounds__(256) ep_compact_kernel(const __half* __restric
     }
 }
 
+// The expert-major order without moving a row: index[i] = the receive-buffer row that position i of the expert-major
+// order holds, table[i] = where its output goes in its source rank's return buffer (0 past the rows received). The
+// experts' kernels then fetch their rows through `index` (the grouped GEMM's producer gathers by row index).
+__global__ void __launch_bounds__(256) ep_index_kernel(const EpPlan* __restrict__ plan, PeerPtrs back, int row_bytes_back, int world,
+                                                      int El, uint32_t region_rows, uint32_t* __restrict__ index,
+                                                      uint64_t* __restrict__ table) {
+    uint32_t total = 0;
+    for (int q = 0; q < world; q++) total += plan->from[q];
+    for (uint32_t j = blockIdx.x * 256 + threadIdx.x; j < (uint32_t)world * region_rows; j += gridDim.x * 256) {
+        if (j >= total) {
+            table[j] = 0;
+            index[j] = 0;
+        }
+        const uint32_t s = j / region_rows;
+        if (j - s * region_rows >= plan->from[s]) continue;
+        int lo = s * El, hi = (s + 1) * El;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (plan->seg_recv[mid] <= j) lo = mid; else hi = mid;
+        }
+        const uint32_t idx = j - plan->seg_recv[lo];
+        const uint32_t dst = plan->seg_dst[lo] + idx;
+        index[dst] = j;
+        table[dst] = reinterpret_cast<uint64_t>(static_cast<char*>(back.p[s]) + (size_t)(plan->seg_src[lo] + idx) * row_bytes_back);
+    }
+}
+
 // The same mapping as a table: table[j] = address, in the source rank's return buffer, of the output of received row j
 // (0 for rows nobody sent). A GEMM epilogue that stores through this table returns the rows without a copy kernel.
 __global__ void __launch_bounds__(256) ep_return_rows_kernel(const EpPlan* __restrict__ plan, PeerPtrs back, int row_bytes, int world,
@@ -341,4 +368,18 @@ extern "C" int32_t iq_ep_compact(iq_ep* ep, void* stream, const void* recv_rows,
         ep->experts / ep->world, (uint32_t)ep->region_rows, static_cast<__half*>(rows_out), reinterpret_cast<uint64_t*>(table));
     if (merged_counts != nullptr) *merged_counts = ep->plan->merged;
     return check_cuda(ep->ctx, cudaGetLastError(), "ep_compact launch");
+}
+
+extern "C" int32_t iq_ep_index(iq_ep* ep, void* stream, int32_t d_model, int32_t yd_dtype, uint32_t* row_index, void** table,
+                               const uint32_t** merged_counts) {
+    if (ep == nullptr) return kErrInvalidArg;
+    if (row_index == nullptr || table == nullptr || (yd_dtype != kF32 && yd_dtype != kF16) || d_model % 8 != 0)
+        return fail(ep->ctx, kErrInvalidArg, "ep_index: arguments");
+    const int64_t rows = (int64_t)ep->world * ep->region_rows;
+    const int64_t want = (rows + 255) / 256, cap = (int64_t)ep->ctx->sms * 4;
+    ep_index_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        ep->plan, ep->back, d_model * (yd_dtype == kF32 ? 4 : 2), ep->world, ep->experts / ep->world, (uint32_t)ep->region_rows,
+        row_index, reinterpret_cast<uint64_t*>(table));
+    if (merged_counts != nullptr) *merged_counts = ep->plan->merged;
+    return check_cuda(ep->ctx, cudaGetLastError(), "ep_index launch");
 }

@@ -159,7 +159,7 @@ int32_t launch_route(iq_moe* l, cudaStream_t st, const float* logits, int ld, in
 // Gate + up + activation of every tile: h[row, :] = half(act(x W_gate^T + b_g, x W_up^T + b_u)). Expert e's weights live
 // at local slot e - expert_lo: the offset is folded into the base pointers. row_map == nullptr: x rows are in place.
 int32_t run_gateup(iq_moe* l, cudaStream_t cs, const void* x, int32_t x_dtype, int64_t ldx, const uint32_t* row_map,
-                   const Tile* tiles, const uint32_t* ntiles, int max_tiles, int bm, __half* h) {
+                   const Tile* tiles, const uint32_t* ntiles, int max_tiles, int bm, __half* h, int row_map_div = 0) {
     const iq_moe_desc& d = l->d;
     const int64_t lo = d.expert_lo;
     GqmvCall c;
@@ -179,7 +179,7 @@ int32_t run_gateup(iq_moe* l, cudaStream_t cs, const void* x, int32_t x_dtype, i
     c.expert_lo = d.expert_lo; c.expert_count = d.expert_count;
     c.N = d.d_ff; c.K = d.d_model;
     c.x = x; c.x_dtype = x_dtype; c.ldx = ldx;
-    c.row_map = row_map; c.topk = d.top_k;
+    c.row_map = row_map; c.topk = row_map_div > 0 ? row_map_div : d.top_k;  // x row = row_map[sorted position] / divisor
     c.tiles = tiles; c.ntiles = ntiles; c.grid_tiles = max_tiles;
     c.rows = 0; c.max_rows = bm;
     c.y = h; c.y_dtype = kF16; c.ldy = d.d_ff;
@@ -372,7 +372,7 @@ extern "C" int32_t iq_dense_ffn(iq_ctx* ctx, void* stream, const void* x, int32_
     if (st != kOk) return st;
     if (workspace == nullptr || workspace_bytes < need)
         return fail(ctx, kErrWorkspace, "dense_ffn: workspace %zu < %zu", workspace_bytes, need);
-    if (act != IQ_ACT_SILU && act != IQ_ACT_SWIGLU_OAI) return fail(ctx, kErrUnsupported, "dense_ffn: activation %d", act);
+    if (act < IQ_ACT_SILU || act > IQ_ACT_RELU2) return fail(ctx, kErrUnsupported, "dense_ffn: activation %d", act);
     const int32_t fmt = format_of(gate_up);
     if (fmt < 0 || format_of(down) < 0) return fail(ctx, kErrUnsupported, "dense_ffn: weight format");
     cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
@@ -405,7 +405,49 @@ extern "C" int32_t iq_dense_ffn(iq_ctx* ctx, void* stream, const void* x, int32_
         if (st != kOk) return st;
         return iq_qmv(ctx, stream, h, IQ_F16, d_ff, down, out, out_dtype, ldo, rows, flags, 0);
     }
-    // GEMM path: gate|up GEMM -> activation -> down GEMM
+    if (fmt == kFmtAffine4 || fmt == kFmtMxfp4) {
+        // GEMM path, fused: the gate and the up rows of the concatenated matrix are the two weight tiles of one stage of
+        // the tcgen05 kernel, whose epilogue applies the activation and writes h = half(act(gate x, up x)) directly
+        // (dswiglu_hh of the reference, Shaders/yy_model.metal:187-227, without the fp32 gate|up round trip: at
+        // rows = 2048, d_ff = 14336 that is 235 MB not written and read back); then the down GEMM.
+        if (rows % 64 != 0 || d_ff % 64 != 0 || gate_up->k % 64 != 0)
+            return fail(ctx, kErrInvalidArg, "dense_ffn: rows = %d, d_ff = %d, d = %d must be multiples of 64", rows, d_ff, gate_up->k);
+        char* q = static_cast<char*>(workspace) + round_up_sz((size_t)rows * d_ff * 2, 256);
+        const void* x16 = x;
+        int64_t ld16 = ldx;
+        if (x_dtype != IQ_F16) {
+            if (ldx < gate_up->k || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+                return fail(ctx, kErrInvalidArg, "dense_ffn: x must be 16-byte aligned with ldx >= d and ldx %% 8 == 0");
+            const size_t units = (size_t)rows * gate_up->k / 8;
+            rows_to_f16_kernel<<<(unsigned)((units + 255) / 256), 256, 0, cs>>>(x, x_dtype, ldx, reinterpret_cast<__half*>(q), rows,
+                                                                               gate_up->k);
+            st = check_cuda(ctx, cudaGetLastError(), "rows_to_f16 launch");
+            if (st != kOk) return st;
+            x16 = q;
+            ld16 = gate_up->k;
+        }
+        const size_t row_words = (size_t)gate_up->k / 32 * gate_up->bits;
+        const size_t row_groups = (size_t)gate_up->k / gate_up->group;
+        const size_t sbytes = fmt == kFmtMxfp4 ? 1 : 2;
+        QmmCall c;
+        c.fmt = fmt; c.epi = 1; c.bn = rows >= 256 ? 256 : 128;
+        c.x16 = x16; c.ldx = ld16; c.x_rows = rows;
+        c.w[0] = gate_up->w;
+        c.w[1] = static_cast<const uint32_t*>(gate_up->w) + (size_t)d_ff * row_words;
+        c.s[0] = gate_up->scales;
+        c.s[1] = static_cast<const char*>(gate_up->scales) + (size_t)d_ff * row_groups * sbytes;
+        c.b[0] = gate_up->biases;
+        c.b[1] = gate_up->biases ? static_cast<const char*>(gate_up->biases) + (size_t)d_ff * row_groups * 2 : nullptr;
+        c.experts = 1;
+        c.N = d_ff; c.K = gate_up->k; c.M = rows;
+        c.y = h; c.y_dtype = kF16; c.ldy = d_ff;
+        c.limit = act == IQ_ACT_SWIGLU_OAI ? act_limit : 0.f;
+        c.act = act;
+        st = launch_qmm(ctx, cs, c);
+        if (st != kOk) return st;
+        return iq_qmm(ctx, stream, h, IQ_F16, d_ff, down, out, out_dtype, ldo, rows, flags, nullptr, 0);
+    }
+    // other formats (8-bit, 4-bit g32): gate|up GEMM -> activation -> down GEMM
     char* p = static_cast<char*>(workspace) + round_up_sz((size_t)rows * d_ff * 2, 256);
     float* gu = reinterpret_cast<float*>(p);
     p += round_up_sz((size_t)rows * 2 * d_ff * 4, 256);
@@ -610,7 +652,7 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
         } else {
         // experts per block: small ranges for few tokens (more blocks, shorter dot products per thread)
         int eb = d.experts < 256 ? d.experts : 256;
-        if (tokens <= 16) eb = 8;
+        if (tokens <= 64) eb = 8;  // a decode batch: 256 blocks of 8 experts x 32 K slices fill the GPU (20 -> 10 us at 64 tokens)
         else if (tokens <= 256 && eb > 32) eb = 32;
         while (d.experts % eb != 0) eb /= 2;
         const size_t smem = (size_t)kRouterTT * d.d_model * 8 + (size_t)256 * kRouterTT * 8;
@@ -753,9 +795,31 @@ extern "C" int32_t iq_moe_experts_workspace_bytes(const iq_moe* l, int32_t max_r
     return kOk;
 }
 
+namespace {
+int32_t moe_experts_impl(iq_moe* l, void* stream, const void* rows_f16, const uint32_t* row_index, int32_t total_rows,
+                         int32_t max_rows, const uint32_t* counts, int32_t sources, int32_t region_rows, void* yd, int32_t yd_dtype,
+                         void* const* yd_rows, void* workspace, size_t workspace_bytes);
+}
+
 extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16, int32_t total_rows, int32_t max_rows,
                                   const uint32_t* counts, int32_t sources, int32_t region_rows, void* yd, int32_t yd_dtype,
                                   void* const* yd_rows, void* workspace, size_t workspace_bytes) {
+    return moe_experts_impl(l, stream, rows_f16, nullptr, total_rows, max_rows, counts, sources, region_rows, yd, yd_dtype, yd_rows,
+                            workspace, workspace_bytes);
+}
+
+extern "C" int32_t iq_moe_experts_indexed(iq_moe* l, void* stream, const void* rows_f16, const uint32_t* row_index,
+                                          int32_t total_rows, int32_t max_rows, const uint32_t* counts, void* yd, int32_t yd_dtype,
+                                          void* const* yd_rows, void* workspace, size_t workspace_bytes) {
+    if (l != nullptr && row_index == nullptr) return fail(l->ctx, kErrInvalidArg, "moe_experts_indexed: row_index");
+    return moe_experts_impl(l, stream, rows_f16, row_index, total_rows, max_rows, counts, 1, 0, yd, yd_dtype, yd_rows, workspace,
+                            workspace_bytes);
+}
+
+namespace {
+int32_t moe_experts_impl(iq_moe* l, void* stream, const void* rows_f16, const uint32_t* row_index, int32_t total_rows,
+                         int32_t max_rows, const uint32_t* counts, int32_t sources, int32_t region_rows, void* yd, int32_t yd_dtype,
+                         void* const* yd_rows, void* workspace, size_t workspace_bytes) {
     if (l == nullptr) return kErrInvalidArg;
     iq_ctx* ctx = l->ctx;
     const iq_moe_desc& d = l->d;
@@ -777,7 +841,9 @@ extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16,
                                            w.ntiles);
         int32_t st2 = check_cuda(ctx, cudaGetLastError(), "ep_tiles launch");
         // the row count is only known on the device: bounds come from the capacity, total_rows picks the kernels
-        if (st2 == kOk) st2 = run_gateup_tc(l, cs, static_cast<const __half*>(rows_f16), max_rows, w.tiles, w.ntiles, w.h, bn);
+        if (st2 == kOk)
+            st2 = run_gateup_tc(l, cs, static_cast<const __half*>(rows_f16), max_rows, w.tiles, w.ntiles, w.h, bn, row_index, 1,
+                                d.d_model, max_rows);
         if (st2 == kOk) st2 = run_down_tc(l, cs, w.h, max_rows, w.tiles, w.ntiles, yd, yd_dtype, bn);
         if (st2 == kOk && yd_rows != nullptr) st2 = scatter_rows(ctx, cs, yd, yd_rows, max_rows, d.d_model, yd_dtype);
         return st2;
@@ -790,12 +856,13 @@ extern "C" int32_t iq_moe_experts(iq_moe* l, void* stream, const void* rows_f16,
     const int64_t mt = max_rows / bm + slots;
     const int max_tiles = (int)(mt < max_rows ? mt : max_rows);
     if (max_tiles > 65535) return fail(ctx, kErrInvalidArg, "moe_experts: too many tiles for one launch");
-    st = run_gateup(l, cs, rows_f16, kF16, d.d_model, nullptr, w.tiles, w.ntiles, max_tiles, bm, w.h);
+    st = run_gateup(l, cs, rows_f16, kF16, d.d_model, row_index, w.tiles, w.ntiles, max_tiles, bm, w.h, 1);
     if (st != kOk) return st;
     st = run_down(l, cs, w.h, w.tiles, w.ntiles, max_tiles, bm, yd, yd_dtype);
     if (st != kOk || yd_rows == nullptr) return st;
     return scatter_rows(ctx, cs, yd, yd_rows, max_rows, d.d_model, yd_dtype);
 }
+}  // namespace
 
 extern "C" int32_t iq_moe_combine_rows(iq_moe* l, void* stream, const void* yd_rows, int32_t yd_dtype, int32_t tokens,
                                        void* out, int32_t out_dtype, int64_t ldo, uint32_t flags, void* workspace,

@@ -86,7 +86,9 @@ class ExpertParallelMoE:
             dev = self.layer.device
             self.buf["yd_dx"] = torch.empty(dx.max_rows, self.layer.D, dtype=dx.yd_dtype, device=dev)
             self.buf["rows_dx"] = torch.zeros(dx.max_rows, dtype=torch.int64, device=dev)
-            self.buf["xc_dx"] = torch.zeros(dx.max_rows, self.layer.D, dtype=torch.float16, device=dev)
+            self.buf["xc_dx"] = torch.zeros(dx.max_rows if dx.fused_return == "compact" else 1, self.layer.D, dtype=torch.float16,
+                                            device=dev)
+            self.buf["index_dx"] = torch.zeros(dx.max_rows, dtype=torch.int32, device=dev)
             self.buf["ws_dx"] = torch.empty(self.layer.experts_workspace_bytes(dx.max_rows, self.world), dtype=torch.uint8,
                                             device=dev)
 
@@ -98,11 +100,16 @@ class ExpertParallelMoE:
         dx.pack_push(x, rows, k, v["inds"], v["pos"], v["offsets"])  # rows and counts go out; no peer input needed
         dx.barrier(then_plan=True)
         # the kernels are picked for the rows this rank expects to receive (about as many as it sends)
-        if dx.fused_return:
+        if dx.fused_return == "compact":
             # rows gathered expert-major (one run of rows per expert, whatever their source); the expert outputs then
             # go through the table of return addresses straight into the sources' buffers
             merged = dx.compact(b["xc_dx"], b["rows_dx"])
             L.experts(b["xc_dx"], min(rows * k, dx.max_rows), merged, 1, b["yd_dx"], b["ws_dx"], yd_rows=b["rows_dx"])
+        elif dx.fused_return:
+            # the same order as an index into the receive buffer: the experts' kernels fetch the rows themselves
+            merged = dx.index(b["index_dx"], b["rows_dx"])
+            L.experts_indexed(dx.recv, b["index_dx"], min(rows * k, dx.max_rows), merged, b["yd_dx"], b["ws_dx"],
+                              yd_rows=b["rows_dx"])
         else:
             L.experts(dx.recv, min(rows * k, dx.max_rows), dx.counts, self.world, b["yd_dx"], b["ws_dx"],
                       region_rows=dx.region_rows)
@@ -143,8 +150,11 @@ class DeviceExchange:
     """
 
     def __init__(self, experts: int, top_k: int, d_model: int, max_local_tokens: int, yd_dtype: torch.dtype,
-                 device: torch.device, group=None, fused_return: bool = True):
-        """max_local_tokens: the largest token count any rank handles per call (the same value on every rank)."""
+                 device: torch.device, group=None, fused_return=True):
+        """max_local_tokens: the largest token count any rank handles per call (the same value on every rank).
+        fused_return: True (the experts fetch the received rows through an index and store their outputs straight into the
+        sources' return buffers), "compact" (the rows are gathered expert-major first) or False (a copy kernel returns
+        the outputs)."""
         import os
 
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -204,6 +214,15 @@ class DeviceExchange:
         merged = C.c_void_p()
         self.ctx.check(capi.lib().iq_ep_compact(self._h, _stream_ptr(stream), self.recv.data_ptr(), self.d_model, dt,
                                                 rows_out.data_ptr(), table.data_ptr(), C.byref(merged)))
+        return merged.value
+
+    def index(self, row_index: torch.Tensor, table: torch.Tensor, stream=None) -> int:
+        """The expert-major order as an index into the receive buffer (row_index int32 [max_rows]) with the table of return
+        addresses; returns the device address of this rank's per-expert row totals."""
+        dt = capi.IQ_F32 if self.yd_dtype == torch.float32 else capi.IQ_F16
+        merged = C.c_void_p()
+        self.ctx.check(capi.lib().iq_ep_index(self._h, _stream_ptr(stream), self.d_model, dt, row_index.data_ptr(),
+                                              table.data_ptr(), C.byref(merged)))
         return merged.value
 
     def return_rows(self, table: torch.Tensor, stream=None):

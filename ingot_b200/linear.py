@@ -230,7 +230,8 @@ class DenseMLP:
         if gate_up.N % 2 or gate_up.N // 2 != down.K or gate_up.K != down.N:
             raise ValueError("gate|up and down do not chain")
         self.gate_up, self.down = gate_up, down
-        self.act = {"silu": capi.IQ_ACT_SILU, "swiglu_oai": capi.IQ_ACT_SWIGLU_OAI}[act]
+        self.act = {"silu": capi.IQ_ACT_SILU, "gelu": capi.IQ_ACT_GELU, "swiglu_oai": capi.IQ_ACT_SWIGLU_OAI,
+                    "relu2": capi.IQ_ACT_RELU2}[act]
         self.limit = limit
         self._ws = None
 

@@ -190,6 +190,15 @@ class MoELayer:
                                                  _dtype_id(yd), 0 if yd_rows is None else yd_rows.data_ptr(),
                                                  workspace.data_ptr(), workspace.numel()))
 
+    def experts_indexed(self, rows_f16: torch.Tensor, row_index: torch.Tensor, total_rows: int, counts, yd: torch.Tensor,
+                        workspace: torch.Tensor, yd_rows: Optional[torch.Tensor] = None, stream=None):
+        """The same on rows left where they arrived: position i of the expert-major order is row row_index[i] of rows_f16
+        (int32 device tensor); counts: per-expert totals, a device tensor [experts] or the device address of one."""
+        self.ctx.check(capi.lib().iq_moe_experts_indexed(
+            self._h, _stream_ptr(stream), rows_f16.data_ptr(), row_index.data_ptr(), total_rows, rows_f16.shape[0],
+            counts.data_ptr() if hasattr(counts, "data_ptr") else int(counts), yd.data_ptr(), _dtype_id(yd),
+            0 if yd_rows is None else yd_rows.data_ptr(), workspace.data_ptr(), workspace.numel()))
+
     def combine_rows(self, yd_rows: torch.Tensor, out: torch.Tensor, tokens: int, accumulate: bool = False, stream=None):
         self.ctx.check(capi.lib().iq_moe_combine_rows(self._h, _stream_ptr(stream), yd_rows.data_ptr(), _dtype_id(yd_rows),
                                                       tokens, out.data_ptr(), _dtype_id(out), out.stride(0),

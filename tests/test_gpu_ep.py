@@ -126,6 +126,13 @@ def test_ep_device_pieces_emulated_on_one_gpu(cuda_device, world, T, yd_dtype, f
                     table = torch.zeros(cap, dtype=torch.int64, device=cuda_device)
                     ctx.check(capi.lib().iq_ep_return_rows(eps[r], 0, dt[yd_dtype], D, table.data_ptr()))
                     layers[r].experts(recv[r], min(cap, T * K), counts[r], world, yd, ws, region_rows=region, yd_rows=table)
+                elif fused and world == 2:  # the same order as an index: the experts fetch the rows where they arrived
+                    table = torch.full((cap,), -1, dtype=torch.int64, device=cuda_device)
+                    index = torch.full((cap,), -1, dtype=torch.int32, device=cuda_device)
+                    merged = C.c_void_p()
+                    ctx.check(capi.lib().iq_ep_index(eps[r], 0, D, dt[yd_dtype], index.data_ptr(), table.data_ptr(),
+                                                     C.byref(merged)))
+                    layers[r].experts_indexed(recv[r], index, min(cap, T * K), merged.value, yd, ws, yd_rows=table)
                 elif fused:  # the same with the rows gathered expert-major first
                     table = torch.full((cap,), -1, dtype=torch.int64, device=cuda_device)
                     xc = torch.zeros(cap, D, dtype=torch.float16, device=cuda_device)
@@ -171,7 +178,7 @@ def test_ep_nccl_two_ranks():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("ret", ["f32", "f16", "f16,copy"])
+@pytest.mark.parametrize("ret", ["f32", "f16", "f16,copy", "f16,compact"])
 def test_ep_device_exchange(ret):
     """The exchange done by the library's own kernels over peer memory (no host synchronisation), eager and from a CUDA
     graph, on as many GPUs as the box has (2, 4 or 8)."""

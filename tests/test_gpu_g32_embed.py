@@ -110,6 +110,28 @@ def test_dense_ffn(cuda_device, rows, group):
     assert qref.max_rel(out.cpu().numpy(), ref) <= 2 * TOL  # h is rounded to fp16 on both sides, from sums in other orders
 
 
+@pytest.mark.parametrize("act", ["silu", "gelu", "relu2", "swiglu_oai"])
+@pytest.mark.parametrize("rows", [5, 320])
+def test_dense_ffn_activations(cuda_device, rows, act):
+    """The four gated activations of the reference's dswiglu (Shaders/yy_model.metal:187-227) through the dense FFN:
+    decode rows on the fused GEMV, prefill rows on the tcgen05 GEMM whose epilogue applies the activation to the gate and
+    up tiles of one stage (no fp32 gate|up round trip)."""
+    from ingot_b200 import capi
+    rng = np.random.default_rng(50 + rows)
+    D, F = 512, 768
+    gu, hgu = affine_case(rng, 2 * F, D, 4, cuda_device)
+    dn, hdn = affine_case(rng, D, F, 4, cuda_device)
+    xh = synth.activations_np(rng, rows, D)
+    wgu = deq(hgu, 4)
+    g, u = qref.matmul_t(xh, wgu[:F]), qref.matmul_t(xh, wgu[F:])
+    h = qref.round_f16(qref.swiglu_oai(g, u, 7.0) if act == "swiglu_oai" else qref.ACTS[act](g, u))
+    ref = qref.matmul_t(h, deq(hdn, 4))
+    out = torch.zeros(rows, D, dtype=torch.float32, device=cuda_device)
+    DenseMLP(gu, dn, act=act).encode(x_tensor(xh, cuda_device), out, rows)
+    assert capi.context(0).device_status() == 0
+    assert qref.max_rel(out.cpu().numpy(), ref) <= 2 * TOL
+
+
 def test_moe_rejects_g32_experts(cuda_device):
     from ingot_b200.moe import MoELayer, RouterSpec
     rng = np.random.default_rng(37)
