@@ -290,13 +290,16 @@ int32_t launch_qmv_imma(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
 
 // ---- int8 tensor-core path for the MoE decode tiles (gate/up + activation, down; affine 4-bit experts) ---------------
 typedef void (*QgKernel)(const CUtensorMap, const CUtensorMap, const QgParams);
-template <bool TM>
-QgKernel qg_pick_tm(int mode, int ms) {
-    if (mode == kModeGateUp)
-        return ms == 4 ? qmv_imma_grouped_kernel<kModeGateUp, 4, TM> : qmv_imma_grouped_kernel<kModeGateUp, 2, TM>;
-    return ms == 4 ? qmv_imma_grouped_kernel<kModeDown, 4, TM> : qmv_imma_grouped_kernel<kModeDown, 2, TM>;
+// gw4: each consumer warp's K slice is four groups, its activation fragments stay in registers (8-row tiles only)
+template <int MODE, bool TM>
+QgKernel qg_pick_mt(int ms, bool gw4) {
+    if (ms == 4) return qmv_imma_grouped_kernel<MODE, 4, TM, 0>;
+    return gw4 ? qmv_imma_grouped_kernel<MODE, 2, TM, 4> : qmv_imma_grouped_kernel<MODE, 2, TM, 0>;
 }
-QgKernel qg_pick(int mode, int ms, bool tm) { return tm ? qg_pick_tm<true>(mode, ms) : qg_pick_tm<false>(mode, ms); }
+QgKernel qg_pick(int mode, int ms, bool tm, bool gw4) {
+    if (mode == kModeGateUp) return tm ? qg_pick_mt<kModeGateUp, true>(ms, gw4) : qg_pick_mt<kModeGateUp, false>(ms, gw4);
+    return tm ? qg_pick_mt<kModeDown, true>(ms, gw4) : qg_pick_mt<kModeDown, false>(ms, gw4);
+}
 // The down projection (K = d_ff, rows of 384 bytes) stays off this path: with tensor copies it measured 9.73 ms against
 // 8.57 ms per 48-layer step of 64 tokens on the fp16 tile kernels.
 constexpr bool kQgDown = false;
@@ -325,18 +328,20 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
     p.srow_bytes = G * 2;
     p.xq_bytes = G * ms * 512;
     p.xsc_bytes = G * ms * 32;
-    p.red_bytes = 2 * 8 * nw * ms * 64 * 4;
+    p.red_bytes = 2 * kQgWarps * nw * ms * 64 * 4;
     const int fixed = p.xq_bytes + p.xsc_bytes + p.red_bytes + 256 + (tm ? 1024 : 0);
-    // K slices per block of rows: four (32-row blocks: half as many hand-overs per byte; measured 86 against 100 us on
-    // the 64-token layer) when two stages of that size fit, else eight
+    // K slices per block of rows. 8-row tiles: one slice of four groups per warp when K allows it (the activation
+    // fragments then live in registers: 69 against 83 us on the 64-token layer); else four slices (32-row blocks: half as
+    // many hand-overs per byte) when two stages of that size fit, else eight.
     int ctas = 1, nstages = 0;
-    const int cand[4] = {4, 8, 2, 1};
+    const bool gw4 = ms == 2 && G == 4 * kQgWarps;
+    const int cand[4] = {gw4 ? kQgWarps : kQgWarps / 2, kQgWarps, kQgWarps / 4, kQgWarps / 8};
     for (int ci = 0; ci < 4 && nstages < 2; ci++) {
         const int wk = cand[ci];
-        if (G % wk != 0) continue;
-        const int R = 16 * (8 / wk);
+        if (G % wk != 0 || (G / wk) % 4 != 0) continue;  // a warp's K slice: runs of four groups
+        const int R = 16 * (kQgWarps / wk);
         if ((R * p.srow_bytes) % 16 != 0) continue;
-        p.wk = wk; p.rgs = 8 / wk;
+        p.wk = wk; p.rgs = kQgWarps / wk;
         p.NB = (c.N + R - 1) / R;
         p.mat_bytes = round_up(R * p.row_pitch + 2 * R * p.srow_bytes, tm ? 1024 : 16);
         p.stage_bytes = nw * p.mat_bytes;
@@ -384,7 +389,7 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return check_cuda(ctx, cudaLaunchKernelEx(&cfg, qg_pick(c.mode, ms, tm), *maps[0], *maps[1], p), "qmv_imma_grouped launch");
+    return check_cuda(ctx, cudaLaunchKernelEx(&cfg, qg_pick(c.mode, ms, tm, gw4 && p.wk == kQgWarps), *maps[0], *maps[1], p), "qmv_imma_grouped launch");
 }
 
 }  // namespace
@@ -402,8 +407,8 @@ int32_t gqmv_init(iq_ctx* ctx) {
         if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_imma)");
     }
     for (int mode = kModeGateUp; mode <= kModeDown; mode++)
-        for (int v = 0; v < 4; v++) {  // 2 or 4 row sets, bulk copies per row or tensor copies
-            cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(qg_pick(mode, (v & 1) ? 4 : 2, v >= 2)),
+        for (int v = 0; v < 6; v++) {  // 4 row sets, 2, 2 with register-resident activations; bulk or tensor copies
+            cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(qg_pick(mode, v % 3 == 0 ? 4 : 2, v >= 3, v % 3 == 2)),
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kQsSmemMax);
             if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(qmv_imma_grouped)");
         }
