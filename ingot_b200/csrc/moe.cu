@@ -613,6 +613,9 @@ extern "C" int32_t iq_moe_forward(iq_moe* l, void* stream, const void* x, int32_
     if ((pieces & IQ_PIECE_ROUTER) && fast_router) {
         QmmCall c;
         c.fmt = kFmtBf16Plain; c.epi = 0; c.bn = 128;
+        // one CTA per (token tile, 128 experts): narrower token tiles until the grid covers the GPU (4096 tokens and 128
+        // experts: 32 CTAs of 128 tokens took 21 us, the K loop's latency; 128 CTAs of 32 tokens run it side by side)
+        while (c.bn > 32 && ((tokens + c.bn - 1) / c.bn) * ((d.experts + 127) / 128) < ctx->sms) c.bn /= 2;
         c.x16 = x; c.ldx = ldx; c.x_rows = tokens;
         c.w[0] = d.router_w;
         c.experts = 1;

@@ -625,10 +625,15 @@ __global__ void __launch_bounds__(256) moe_scan_kernel(const GroupParams p) {
     uint32_t c_sum = 0, a_sum = 0, b_sum = 0;
     for (int e = e0; e < e1; e++) {
         uint32_t run = 0;
-        for (int c = 0; c < p.chunks; c++) {  // histogram -> exclusive prefix over the chunks
-            const uint32_t t = p.chunk_hist[(size_t)c * p.E + e];
-            p.chunk_hist[(size_t)c * p.E + e] = run;
-            run += t;
+        for (int c0 = 0; c0 < p.chunks; c0 += 8) {  // histogram -> exclusive prefix over the chunks, eight loads in flight
+            uint32_t t[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) t[k] = c0 + k < p.chunks ? p.chunk_hist[(size_t)(c0 + k) * p.E + e] : 0u;
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                if (c0 + k < p.chunks) p.chunk_hist[(size_t)(c0 + k) * p.E + e] = run;
+                run += t[k];
+            }
         }
         p.counts[e] = run;
         c_sum += run;

@@ -47,7 +47,8 @@ const KernelEntry* table(int* n) {
         entry<kFmtAffine4, 128, kEpiGateUp, kActRelu2>(), entry<kFmtAffine4, 256, kEpiGateUp, kActRelu2>(),
         entry<kFmtMxfp4, 128, kEpiGateUp, kActGelu>(), entry<kFmtMxfp4, 256, kEpiGateUp, kActGelu>(),
         entry<kFmtMxfp4, 128, kEpiGateUp, kActRelu2>(), entry<kFmtMxfp4, 256, kEpiGateUp, kActRelu2>(),
-        entry<kFmtBf16Plain, 128, kEpiStore>(),  // bf16 x bf16 (the router's approximate logits)
+        // bf16 x bf16 (the router's approximate logits); the small token tiles spread few experts over many CTAs
+        entry<kFmtBf16Plain, 128, kEpiStore>(), entry<kFmtBf16Plain, 64, kEpiStore>(), entry<kFmtBf16Plain, 32, kEpiStore>(),
         entry<kFmtTernary, 256, kEpiStore>(), entry<kFmtTernary, 128, kEpiStore>(),
         entry<kFmtInt8Plain, 256, kEpiStore>(), entry<kFmtInt8Plain, 128, kEpiStore>(),  // rotated W8A8
     };
