@@ -456,7 +456,7 @@ __global__ void __launch_bounds__(kQgThreads, 1)
             // Outputs (weight row n, activation row m), n fastest; with two matrices a pair of neighbouring lanes takes one
             // output, one matrix each, and the even lane gets the other's sum by shuffle. Slices are added in slice order.
             // Two outputs per thread and pass, all their loads first.
-            const int total = NW * (R * 4 * MS);  // a multiple of 32: whole warps stay together
+            const int total = NW * (R * 4 * ((M + 3) >> 2));  // live row sets only; a multiple of 32: whole warps stay together
             for (int u0 = et; u0 < total; u0 += 2 * NET) {
                 float part[2][kQgWarps];
                 int nl[2], m[2];
