@@ -102,22 +102,25 @@ MoeWs carve(const iq_moe* l, void* base, int tokens) {
 }
 
 typedef void (*RouteKernel)(const RouteParams);
-template <bool REFINE>
+template <bool REFINE, int WPT>
 RouteKernel route_kernel_of(int experts) {
     switch ((experts + 31) / 32) {
-        case 1: return route_topk_kernel<1, REFINE>;
-        case 2: return route_topk_kernel<2, REFINE>;
-        case 3: return route_topk_kernel<3, REFINE>;
-        case 4: return route_topk_kernel<4, REFINE>;
-        case 5: case 6: return route_topk_kernel<6, REFINE>;
-        case 7: case 8: return route_topk_kernel<8, REFINE>;
-        case 9: case 10: case 11: case 12: return route_topk_kernel<12, REFINE>;
-        default: return route_topk_kernel<16, REFINE>;
+        case 1: return route_topk_kernel<1, REFINE, WPT>;
+        case 2: return route_topk_kernel<2, REFINE, WPT>;
+        case 3: return route_topk_kernel<3, REFINE, WPT>;
+        case 4: return route_topk_kernel<4, REFINE, WPT>;
+        case 5: case 6: return route_topk_kernel<6, REFINE, WPT>;
+        case 7: case 8: return route_topk_kernel<8, REFINE, WPT>;
+        case 9: case 10: case 11: case 12: return route_topk_kernel<12, REFINE, WPT>;
+        default: return route_topk_kernel<16, REFINE, WPT>;
     }
 }
-RouteKernel route_kernel_for(int experts, bool refine) {
-    return refine ? route_kernel_of<true>(experts) : route_kernel_of<false>(experts);
+// wide: four warps per token share the refinement's exact dot products (few tokens: the chain per token is the time)
+RouteKernel route_kernel_for(int experts, bool refine, bool wide) {
+    if (!refine) return route_kernel_of<false, 1>(experts);
+    return wide ? route_kernel_of<true, 4>(experts) : route_kernel_of<true, 1>(experts);
 }
+constexpr int kRouteWideMaxTokens = 2048;
 
 // Many tokens with a bf16 router and bf16 activations: the logits come from the tensor cores (bf16 products are exact,
 // the fp32 accumulation is not), and the route kernel recomputes exactly, in float64, the few logits per token that
@@ -152,7 +155,8 @@ int32_t launch_route(iq_moe* l, cudaStream_t st, const float* logits, int ld, in
     rp.sigmoid = l->d.router_score == IQ_SCORE_SIGMOID ? 1 : 0;
     rp.select_bias = l->d.router_select_bias;
     rp.eps = l->d.route_eps;
-    route_kernel_for(l->d.experts, refine_x != nullptr)<<<(tokens + 3) / 4, 128, 0, st>>>(rp);
+    const bool wide = refine_x != nullptr && tokens <= kRouteWideMaxTokens;
+    route_kernel_for(l->d.experts, refine_x != nullptr, wide)<<<wide ? tokens : (tokens + 3) / 4, 128, 0, st>>>(rp);
     return check_cuda(l->ctx, cudaGetLastError(), "route_topk launch");
 }
 

@@ -350,11 +350,16 @@ __device__ __forceinline__ float exact_dot_bf16(const uint16_t* __restrict__ xro
     return (float)acc;
 }
 
-template <int VPL, bool REFINE = false>
+// WPT: warps per token. 1: a block takes four tokens. 4 (refinement only): a block takes one token and its warps share
+// the exact dot products (candidate c goes to warp c % 4, results meet in shared memory); everything else runs in all
+// four warps alike. With few tokens per GPU the refinement is one dependent chain per warp, so four warps per token
+// cut it to a quarter; with thousands of tokens the GPU is full either way.
+template <int VPL, bool REFINE = false, int WPT = 1>
 __global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
-    const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (t >= p.T) return;
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int t = WPT == 1 ? blockIdx.x * 4 + wib : blockIdx.x;
+    if (t >= p.T) return;  // WPT = 4: the whole block leaves
+    __shared__ float sx[WPT > 1 ? VPL * 32 : 1];  // WPT = 4: exact logits of the candidates
     const float* lr = p.logits + (size_t)t * p.ld;
     float v[VPL];   // what the selection compares
     float pv[VPL];  // sigmoid: the unbiased score the weight is made of
@@ -415,6 +420,7 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
         // anything not finite (an infinity or NaN among the inputs): every expert is recomputed
         float thr = kth - 2.f * eps;
         if (!(fabsf(kth) <= 3.0e38f) || !(eps <= 3.0e38f)) thr = -INFINITY;
+        int cidx = 0;  // candidates so far, the same count in every warp of the token
 #pragma unroll
         for (int j = 0; j < VPL; j++) {
             const bool mine = !((taken >> j) & 1u) && v[j] >= thr;
@@ -423,16 +429,34 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
                 const int src = __ffs(bal) - 1;
                 bal &= bal - 1u;
                 const int e = j * 32 + src;
-                const float exact = exact_dot_bf16(xrow, p.wr + (size_t)e * p.D, p.D, lane);
-                if (lane == src) {
-                    p.logits_rw[(size_t)t * p.ld + e] = exact;
-                    float f = exact;
-                    if (p.logit_bias != nullptr) f += p.logit_bias[e];
-                    if (f != f) f = -INFINITY;
-                    v[j] = f;
+                if (WPT == 1 || (cidx & (WPT - 1)) == wib) {
+                    const float exact = exact_dot_bf16(xrow, p.wr + (size_t)e * p.D, p.D, lane);
+                    if (lane == src) {
+                        p.logits_rw[(size_t)t * p.ld + e] = exact;
+                        if (WPT > 1) {
+                            sx[e] = exact;
+                        } else {
+                            float f = exact;
+                            if (p.logit_bias != nullptr) f += p.logit_bias[e];
+                            if (f != f) f = -INFINITY;
+                            v[j] = f;
+                        }
+                    }
                 }
+                cidx++;
             }
             if (!mine) taken |= 1u << j;  // out of the running
+        }
+        if (WPT > 1) {
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < VPL; j++) {
+                if ((taken >> j) & 1u) continue;
+                float f = sx[j * 32 + lane];
+                if (p.logit_bias != nullptr) f += p.logit_bias[j * 32 + lane];
+                if (f != f) f = -INFINITY;
+                v[j] = f;
+            }
         }
     }
     float myv = -INFINITY, myp = 0.f;
@@ -474,7 +498,7 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
         float sum = 0.f;
         for (int k = 0; k < p.topk; k++) sum += __shfl_sync(0xffffffffu, myp, k);
         sum += p.eps;
-        if (lane < p.topk) {
+        if (lane < p.topk && (WPT == 1 || wib == 0)) {
             float w = myp / sum * p.scale;
             if (p.pes != nullptr) w *= p.pes[myi];
             p.inds[(size_t)t * p.topk + lane] = myi;
@@ -486,7 +510,7 @@ __global__ void __launch_bounds__(128) route_topk_kernel(const RouteParams p) {
     const float ex = lane < p.topk ? expf(myv - top1) : 0.f;
     float sum = 0.f;
     for (int k = 0; k < p.topk; k++) sum += __shfl_sync(0xffffffffu, ex, k);
-    if (lane < p.topk) {
+    if (lane < p.topk && (WPT == 1 || wib == 0)) {
         float w = ex / sum * p.scale;
         if (p.pes != nullptr) w *= p.pes[myi];
         p.inds[(size_t)t * p.topk + lane] = myi;
