@@ -300,10 +300,6 @@ QgKernel qg_pick(int mode, int ms, bool tm, bool gw4) {
     if (mode == kModeGateUp) return tm ? qg_pick_mt<kModeGateUp, true>(ms, gw4) : qg_pick_mt<kModeGateUp, false>(ms, gw4);
     return tm ? qg_pick_mt<kModeDown, true>(ms, gw4) : qg_pick_mt<kModeDown, false>(ms, gw4);
 }
-// The down projection (K = d_ff, rows of 384 bytes) stays off this path: with tensor copies it measured 9.73 ms against
-// 8.57 ms per 48-layer step of 64 tokens on the fp16 tile kernels.
-constexpr bool kQgDown = false;
-
 // Returns kOk after a launch, 1 when the shape does not fit this path (the caller falls back), or an error.
 int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c) {
     if ((c.mode != kModeGateUp && c.mode != kModeDown) || c.tiles == nullptr || c.fmt != kFmtAffine4) return 1;
@@ -318,10 +314,12 @@ int32_t launch_qmv_imma_grouped(iq_ctx* ctx, cudaStream_t st, const GqmvCall& c)
     memset(&p, 0, sizeof(p));
     p.row_bytes = c.K / 2;
     // Tensor-copy staging: the stacked tensors must be known (which experts they hold) and dense, rows whole 128-byte
-    // columns. Short weight rows (the down projection's K = d_ff) stay on the fp16 tile kernels either way: with one
-    // bulk copy per 384-byte row this path measured 61.9 against 49.6 us at 64 tokens, with tensor copies no better.
+    // columns. Short weight rows (the down projection's K = d_ff, 384 bytes) take this path only with tensor copies: one
+    // bulk copy per row measured 61.9 against 49.6 us on the fp16 tile kernels at 64 tokens; with tensor copies, 128-row
+    // blocks and no K split (12 groups of 64 inputs do not divide into runs of four over more than one slice) it
+    // measures 37.3 us (16 tokens: 23.9 against 30.6; 256 tokens: 79.8 against 121).
     const bool tm = ctx->encode_tiled != nullptr && c.expert_count > 0 && p.row_bytes % 128 == 0 && p.row_bytes / 128 <= 256 &&
-                    c.w_estride * 4 == (int64_t)c.N * p.row_bytes && (c.K >= 2048 || kQgDown);
+                    c.w_estride * 4 == (int64_t)c.N * p.row_bytes;
     if (c.K < 2048 && !tm) return 1;
     const int ms = c.max_rows > 8 ? 4 : 2;
     p.row_pitch = tm ? p.row_bytes : p.row_bytes + 32;

@@ -12,7 +12,8 @@
 // named barriers: buffer full, buffer free), so that no item waits for a barrier of the whole CTA.
 //
 // Replaces the reference's vnax_moe_gateup* / vnax_moe_down_split* decode kernels (Shaders/verify_nax.metal:258-509)
-// where the fp16 tile kernels of qmv_stream.cuh ran before; those still serve MXFP4 experts and odd shapes.
+// where the fp16 tile kernels of qmv_stream.cuh ran before; those still serve MXFP4 experts and odd shapes. The down
+// projection of a narrow expert (K = 768) runs here as 128-row blocks without a K split.
 #pragma once
 
 #include <type_traits>
@@ -423,14 +424,35 @@ __global__ void __launch_bounds__(kQgThreads, 1)
             // the loop goes on without computing, so that every barrier keeps its count and nobody is left waiting.
             const int buf = it & 1;
             if (it >= 2) qg_bar_sync(4 + buf, NCT + NET);  // the epilogue of two items ago has read this buffer
-            float* mine = red + (buf * kQgWarps + warp) * (NW * MS * 64);
+            if (MODE == kModeDown && p.wk == 1) {
+                // one K slice: the warp's sums are the outputs, stored from here (the epilogue warps only keep step)
+                if (ok && rows_ok) {
 #pragma unroll
-            for (int i = 0; i < NW; i++)
+                    for (int c = 0; c < MS; c++) {
+                        const int m = 4 * c + t;
+                        if (m >= M) continue;
 #pragma unroll
-                for (int c = 0; c < MS; c++) {
-                    mine[(i * MS + c) * 64 + t * 8 + g] = acc[i][c][0];
-                    mine[(i * MS + c) * 64 + 32 + t * 8 + g] = acc[i][c][1];
+                        for (int h = 0; h < 2; h++) {
+                            const int n = r0 + rb * 16 + g + 8 * h;
+                            float v = acc[0][c][h];
+                            if (p.ebias[0] != nullptr) v += p.ebias[0][(size_t)tile.expert * p.N + n];
+                            const size_t oy = (size_t)(tile.start + m) * p.ldy + n;
+                            if (p.y_dtype == kF32) reinterpret_cast<float*>(p.y)[oy] = v;
+                            else if (p.y_dtype == kF16) reinterpret_cast<__half*>(p.y)[oy] = __float2half_rn(v);
+                            else reinterpret_cast<uint16_t*>(p.y)[oy] = (uint16_t)f32_to_bf16_bits(v);
+                        }
+                    }
                 }
+            } else {
+                float* mine = red + (buf * kQgWarps + warp) * (NW * MS * 64);
+#pragma unroll
+                for (int i = 0; i < NW; i++)
+#pragma unroll
+                    for (int c = 0; c < MS; c++) {
+                        mine[(i * MS + c) * 64 + t * 8 + g] = acc[i][c][0];
+                        mine[(i * MS + c) * 64 + 32 + t * 8 + g] = acc[i][c][1];
+                    }
+            }
             qg_bar_arrive(2 + buf, NCT + NET);
             if (++s == p.nstages) { s = 0; ph ^= 1; }
             if (++blk == p.NB) { blk = 0; ti++; }
@@ -456,7 +478,9 @@ __global__ void __launch_bounds__(kQgThreads, 1)
             // Outputs (weight row n, activation row m), n fastest; with two matrices a pair of neighbouring lanes takes one
             // output, one matrix each, and the even lane gets the other's sum by shuffle. Slices are added in slice order.
             // Two outputs per thread and pass, all their loads first.
-            const int total = NW * (R * 4 * ((M + 3) >> 2));  // live row sets only; a multiple of 32: whole warps stay together
+            // live row sets only; a multiple of 32: whole warps stay together. Nothing to add up with one K slice of a down
+            // projection: the consumers stored the outputs themselves.
+            const int total = (MODE == kModeDown && p.wk == 1) ? 0 : NW * (R * 4 * ((M + 3) >> 2));
             for (int u0 = et; u0 < total; u0 += 2 * NET) {
                 float part[2][kQgWarps];
                 int nl[2], m[2];
