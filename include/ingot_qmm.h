@@ -149,10 +149,15 @@ int32_t iq_qmm_noalloc(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype
  * quant_rows_rot_i8g / qmm_i8 (Shaders/xa_dense_i8.metal): per call the 4-bit weights and the activations are rotated
  * along K (unnormalised Hadamard of 256 inputs per block when k / 32 is a multiple of 32, else of 32), quantised to int8
  * per row, and Y = (Xq Wq^T) sx sw / n runs on the int8 tensor cores. The workspace (the reference's DenseI8Scratch)
- * holds the int8 weights [n, k], the int8 activations [rows, k] and both scale vectors. 4-bit affine weights only
+ * holds the int8 weights [n, k], the int8 activations [rows, k] and both scale vectors. 4-bit affine weights
  * (group 64 or 32), rows and n multiples of 64, k a multiple of 128. Bound of the reference's int8-serve case
  * (Tests/IngotTests/KernelCaseTests.swift:623-661): relative RMS error 2e-3 against the CPU emulation of the same
- * arithmetic, 5e-2 against the exact product. */
+ * arithmetic, 5e-2 against the exact product.
+ * A ternary matrix (bits 2, group 128) takes DenseQ.encodeQmmI8T instead (Dense.swift:174-212; quant_rows_i8 and
+ * tern_i8row, Shaders/xc_tern.metal:189-237): x is the input already rotated by iq_had_rows and goes to int8 per row
+ * with no further rotation, a weight row goes to int8 with one scale, s_row = max_g |s_g| / 127, as t * rint(s_g / s_row),
+ * and Y = (Xq Wq^T) sx sw. Bounds of the reference's bonsai-int8 case (Tests/IngotTests/KernelCaseFlashNextI8.swift
+ * :155-213): relative RMS error 2e-3 against the emulation, 3e-2 against the exact product. */
 int32_t iq_qmm_w8a8_workspace_bytes(iq_ctx* ctx, const iq_qlinear* m, int32_t rows, size_t* bytes);
 int32_t iq_qmm_w8a8(iq_ctx* ctx, void* stream, const void* x, int32_t x_dtype, int64_t ldx, const iq_qlinear* m, void* y,
                     int32_t y_dtype, int64_t ldy, int32_t rows, uint32_t flags, void* workspace, size_t workspace_bytes);

@@ -71,6 +71,42 @@ __global__ void __launch_bounds__(256) rot_quant_rows_kernel(const void* __restr
     }
 }
 
+// Ternary weights (2-bit codes t + 1, one fp16 scale per group of 128) to int8 with ONE scale per row:
+// s_row = max_g |s_g| / 127, code = t * rint(s_g / s_row) (tern_i8row, Shaders/xc_tern.metal:213-237). One warp per
+// row, four rows per block.
+__global__ void __launch_bounds__(128) tern_i8row_kernel(const uint32_t* __restrict__ w, const __half* __restrict__ s, int N, int K,
+                                                        int8_t* __restrict__ q, float* __restrict__ scale_out) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (n >= N) return;
+    const int G = K / 128;
+    const __half* sr = s + (size_t)n * G;
+    float m = 0.f;
+    for (int g = lane; g < G; g += 32) m = fmaxf(m, fabsf(__half2float(sr[g])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float srow = m > 0.f ? __fdiv_rn(m, 127.0f) : 1.0f;
+    if (lane == 0) scale_out[n] = srow;
+    const uint32_t* wr = w + (size_t)n * (K / 16);
+    uint4* o = reinterpret_cast<uint4*>(q + (size_t)n * K);  // sixteen codes per word of w
+    for (int u = lane; u < K / 16; u += 32) {
+        const int qg = __float2int_rn(__fdiv_rn(__half2float(sr[u / 8]), srow));
+        const uint32_t x = wr[u];
+        uint32_t out[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int t = (int)((x >> (8 * c + 2 * e)) & 3u) - 1;
+                word |= (uint32_t)((t * qg) & 0xFF) << (8 * e);
+            }
+            out[c] = word;
+        }
+        o[u] = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+}
+
 // Hadamard of 256 along K when K / 32 is a multiple of 32, else of 32 (DenseI8Scratch.lb, Layers/Dense.swift:107-109).
 int rot_block(int K) { return (K / 32) % 32 == 0 ? 256 : 32; }
 
@@ -98,12 +134,14 @@ W8a8Ws carve_w8a8(void* base, int N, int K, int rows) {
 }
 
 int32_t check_w8a8(iq_ctx* ctx, const iq_qlinear* m, int rows) {
-    if (m == nullptr || m->w == nullptr || m->scales == nullptr || m->biases == nullptr)
+    if (m == nullptr || m->w == nullptr || m->scales == nullptr || (m->biases == nullptr && m->bits != 2))
         return fail(ctx, kErrInvalidArg, "qmm_w8a8: null pointer");
-    // the reference converts from 4 bits only (DenseQ.int8OK): 8-bit layers already have int8 precision
-    if (m->mode != IQ_MODE_AFFINE || m->bits != 4 || (m->group != 64 && m->group != 32) || m->experts > 1)
-        return fail(ctx, kErrUnsupported, "qmm_w8a8: %d-bit group %d mode %d (4-bit affine, group 64 or 32)", m->bits, m->group,
-                    m->mode);
+    // the reference converts from 4 bits (DenseQ.int8OK: 8-bit layers already have int8 precision) and from the ternary
+    // format (DenseQ.encodeQmmI8T)
+    const bool tern = m->bits == 2 && m->group == 128;
+    if (m->mode != IQ_MODE_AFFINE || m->experts > 1 || !(tern || (m->bits == 4 && (m->group == 64 || m->group == 32))))
+        return fail(ctx, kErrUnsupported, "qmm_w8a8: %d-bit group %d mode %d (4-bit affine with group 64 or 32, or ternary)", m->bits,
+                    m->group, m->mode);
     if (m->k % 128 != 0 || m->n % 64 != 0 || m->k > 49152)
         return fail(ctx, kErrInvalidArg, "qmm_w8a8: k = %d (a multiple of 128, at most 49152), n = %d (a multiple of 64)", m->k, m->n);
     if (rows < 64 || rows % 64 != 0) return fail(ctx, kErrInvalidArg, "qmm_w8a8: rows = %d must be a multiple of 64", rows);
@@ -146,10 +184,17 @@ extern "C" int32_t iq_qmm_w8a8(iq_ctx* ctx, void* stream, const void* x, int32_t
     if (workspace == nullptr || workspace_bytes < w.bytes || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
         return fail(ctx, kErrWorkspace, "qmm_w8a8: workspace %zu < %zu (256-byte aligned)", workspace_bytes, w.bytes);
     cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
-    const int n = rot_block(m->k);
+    const bool tern = m->bits == 2;
+    // ternary: x arrives rotated by the format's own transform (iq_had_rows), so neither side is rotated here (n = 1)
+    const int n = tern ? 1 : rot_block(m->k);
     const size_t smem = (size_t)m->k * sizeof(float);
-    rot_quant_rows_kernel<0><<<m->n, 256, smem, cs>>>(m->w, static_cast<const uint16_t*>(m->scales),
-                                                      static_cast<const uint16_t*>(m->biases), m->group, 0, 0, m->k, n, w.wq, w.sw);
+    if (tern)
+        tern_i8row_kernel<<<(m->n + 3) / 4, 128, 0, cs>>>(static_cast<const uint32_t*>(m->w), static_cast<const __half*>(m->scales),
+                                                          m->n, m->k, w.wq, w.sw);
+    else
+        rot_quant_rows_kernel<0><<<m->n, 256, smem, cs>>>(m->w, static_cast<const uint16_t*>(m->scales),
+                                                          static_cast<const uint16_t*>(m->biases), m->group, 0, 0, m->k, n, w.wq,
+                                                          w.sw);
     rot_quant_rows_kernel<1><<<rows, 256, smem, cs>>>(x, nullptr, nullptr, 0, x_dtype, ldx, m->k, n, w.xq, w.sx);
     st = check_cuda(ctx, cudaGetLastError(), "rot_quant_rows launch");
     if (st != kOk) return st;

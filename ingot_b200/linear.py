@@ -168,10 +168,14 @@ class DenseQ:
                       scratch: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None):
         """Y[rows, N] (+)= X · Wᵀ in rotated W8A8 (lossy; DenseQ.encodeQmmI8, Dense.swift:131-172): 4-bit weights and
         activations rotated along K, int8 per row, the product on the int8 tensor cores. `scratch` plays the reference's
-        DenseI8Scratch (sized by `qmm_i8_scratch_bytes`; allocated here when absent)."""
+        DenseI8Scratch (sized by `qmm_i8_scratch_bytes`; allocated here when absent). A ternary matrix takes the
+        reference's encodeQmmI8T (Dense.swift:174-212): the format's own input rotation first, then int8 rows and the
+        weights as int8 with one scale per row."""
         _need_cuda(x, y)
         ctx = capi.context(self.device_index)
         ql = self.qlinear()
+        if self.bits == 2 and self.had is not None:
+            x = self.encode_rotate(x, rows, stream)
         if scratch is None:
             scratch = torch.empty(self.qmm_i8_scratch_bytes(rows), dtype=torch.uint8, device=self.w.device)
         ctx.check(capi.lib().iq_qmm_w8a8(ctx.handle, _stream_ptr(stream), x.data_ptr(), _dtype_id(x), x.stride(0), C.byref(ql),

@@ -415,3 +415,20 @@ def w8a8_emulated(x: np.ndarray, wf: np.ndarray, lb: int) -> np.ndarray:
     wq, sw = quant_i8_rows(rot(wf))
     y = (xq.astype(np.float64) @ wq.astype(np.float64).T).astype(np.float32)
     return y * sx[:, None] * sw[None, :] / np.float32(n)
+
+
+def w8a8_ternary_emulated(xr: np.ndarray, w: np.ndarray, scales_f16: np.ndarray) -> np.ndarray:
+    """The ternary layers' W8A8 prefill GEMM, emulated (the bonsai-int8 kernel case,
+    Tests/IngotTests/KernelCaseFlashNextI8.swift:155-213): `xr` is the already rotated input (rotate_input); it goes to
+    int8 per row; a weight row goes to int8 with ONE scale, s_row = max_g |s_g| / 127, as t * round(|s_g| / s_row) with
+    t the ternary digit; Y = (Xq Wq^T) sx sw. w uint32 [N, K/16], scales float16 [N, K/128]."""
+    xq, sx = quant_i8_rows(np.asarray(xr, dtype=np.float32))
+    t = unpack_q(w, 2).astype(np.float32) - np.float32(1)
+    sg = np.abs(np.asarray(scales_f16, dtype=np.float16).astype(np.float32))
+    gmax = sg.max(axis=1)
+    srow = np.where(gmax > 0, gmax / np.float32(127), np.float32(1)).astype(np.float32)
+    qg = np.rint(sg / srow[:, None]).astype(np.float32)
+    sign = np.sign(np.asarray(scales_f16, dtype=np.float16).astype(np.float32))
+    wq = t * np.repeat(qg * sign, 128, axis=1)
+    y = (xq.astype(np.float64) @ wq.astype(np.float64).T).astype(np.float32)
+    return y * sx[:, None] * srow[None, :]

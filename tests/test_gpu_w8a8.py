@@ -62,3 +62,39 @@ def test_w8a8_outputs_accumulate_and_guards(cuda_device):
     assert e.value.status == -2
     with pytest.raises(capi.IngotError):
         m.encode_qmm_i8(xt[:96], y, 96)  # rows % 64
+
+
+@pytest.mark.parametrize("N,K", [(128, 2048), (128, 9216)])
+def test_w8a8_ternary_against_emulation_and_exact(cuda_device, N, K):
+    """The reference's bonsai-int8 kernel case (Tests/IngotTests/KernelCaseFlashNextI8.swift:155-213): its shapes (K = 9216
+    is nine Hadamard blocks), its bounds (relative RMS 2e-3 against the emulation, 3e-2 against the exact product), the
+    half output, the accumulated output, and a 64-row chunk giving the same bits alone as inside 128 rows."""
+    rng = np.random.default_rng(N + K)
+    M = 128
+    w, s, signs = synth.ternary_np(rng, N, K)
+    m = synth.dense_q_ternary(w, s, signs, cuda_device)
+    x = qref.round_f16(rng.normal(0, 1, size=(M, K)).astype(np.float32))
+    xr = qref.rotate_input(x, signs)
+    emu = qref.w8a8_ternary_emulated(xr, w, s)
+    exact = qref.matmul_t(xr, qref.dequant_ternary(w, s))
+    scratch = torch.empty(m.qmm_i8_scratch_bytes(M), dtype=torch.uint8, device=cuda_device)
+
+    def run(rows, r0, acc=None, half=False):
+        xt = x_tensor(x[r0:r0 + rows], cuda_device, torch.float16)
+        if acc is not None:
+            y = torch.from_numpy(acc.copy()).to(cuda_device)
+        else:
+            y = torch.zeros(rows, N, dtype=torch.float16 if half else torch.float32, device=cuda_device)
+        m.encode_qmm_i8(xt, y, rows, accumulate=acc is not None, scratch=scratch)
+        torch.cuda.synchronize()
+        return y.float().cpu().numpy()
+
+    y = run(M, 0)
+    assert rel_rms(y, emu) <= 2e-3
+    assert rel_rms(y, exact) <= 3e-2
+    yh = run(M, 0, half=True)
+    assert qref.max_rel(yh, qref.round_f16(y)) <= 2e-3
+    base = rng.normal(0, 1, size=(M, N)).astype(np.float32)
+    assert qref.max_rel(run(M, 0, acc=base), base + y) <= 1e-4
+    both = np.concatenate([run(64, 0), run(64, 64)], axis=0)
+    assert np.array_equal(both.view(np.uint32), y.view(np.uint32))

@@ -53,3 +53,28 @@ def test_w8a8_emulation_is_close_to_the_exact_product_and_exact_on_integers():
         assert rms <= 0.05, (lb, rms)  # the reference's bound against the exact product (KernelCaseTests.swift:655)
     q, sc = qref.quant_i8_rows(np.array([[0.5, -1.5, 2.5, 127.0], [0, 0, 0, 0]], dtype=np.float32))
     assert q.tolist() == [[0.0, -2.0, 2.0, 127.0], [0, 0, 0, 0]] and sc.tolist() == [1.0, 1.0]  # ties to even
+
+
+def test_w8a8_ternary_emulation_follows_its_definition():
+    """One scale per weight row (max group scale / 127), codes t * rint(s_g / s_row), int8 rows of the rotated input:
+    a hand case, and the lossy product stays within the reference's 3e-2 of the exact one
+    (Tests/IngotTests/KernelCaseFlashNextI8.swift:180-200)."""
+    rng = np.random.default_rng(5)
+    N, K = 4, 256
+    codes = rng.integers(0, 3, size=(N, K)).astype(np.uint32)
+    w = np.zeros((N, K // 16), dtype=np.uint32)
+    for j in range(16):
+        w |= codes[:, j::16] << np.uint32(2 * j)
+    s = np.array([[0.5, 0.25], [1.0, 1.0], [0.125, 0.5], [0.75, 0.375]], dtype=np.float16)
+    xr = qref.round_f16(rng.normal(0, 1, size=(3, K)).astype(np.float32))
+    y = qref.w8a8_ternary_emulated(xr, w, s)
+    xq, sx = qref.quant_i8_rows(xr)
+    t = codes.astype(np.float32) - 1
+    for n in range(N):
+        srow = np.float32(s[n].astype(np.float32).max() / np.float32(127))
+        qg = np.rint(s[n].astype(np.float32) / srow)
+        wq = t[n] * np.repeat(qg, 128)
+        ref = (xq @ wq) * sx * srow
+        assert np.allclose(y[:, n], ref, rtol=1e-6, atol=1e-6)
+    exact = qref.matmul_t(xr, qref.dequant_ternary(w, s))
+    assert np.sqrt(((y - exact) ** 2).sum() / (exact ** 2).sum()) <= 3e-2
