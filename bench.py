@@ -154,10 +154,13 @@ def build_stack(torch, dev, rank: int, world: int, max_local_tokens: int, layers
     return ep.MoEStack(out, max_local_tokens)
 
 
-def time_steps(torch, dist, world, fn, steps, warmup):
-    """W untimed + K timed calls of fn between barriers, CUDA events on the current stream, max over ranks (ms/step)."""
+def time_steps(torch, dist, world, fn, steps, warmup, drain=None):
+    """W untimed + K timed calls of fn between barriers, CUDA events on the current stream, max over ranks (ms/step).
+    drain: called after the last timed step and before the closing timestamp (work that fn left on other streams)."""
     for _ in range(warmup):
         fn()
+    if drain is not None:
+        drain()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -166,6 +169,8 @@ def time_steps(torch, dist, world, fn, steps, warmup):
     e0.record()
     for _ in range(steps):
         fn()
+    if drain is not None:
+        drain()
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -538,18 +543,58 @@ def run_ours(args):
     def step():
         step_graph.replay()
 
-    def step_e2e():  # host buffers in, host buffer out: the public API a caller drives
-        r.copy_(r0_pinned, non_blocking=True)
+    # End to end: host buffers in, host buffer out, through the public API a caller drives. Every step copies its input
+    # from pinned host memory and reads its result back; as a serving loop would, the copies run on streams of their own,
+    # so step i + 1's input arrives while step i computes and step i's result leaves while step i + 1 computes. The host
+    # waits for a step's result one step later.
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    stage = [torch.empty_like(r0_dev) for _ in range(2)]   # inputs as they arrive
+    result = [torch.empty_like(r0_dev) for _ in range(2)]  # results waiting for their copy out
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_taken = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    e2e_state = {"i": 0}
+
+    def fetch(b):  # host -> device copy of one step's input into staging buffer b
+        with torch.cuda.stream(copy_in):
+            copy_in.wait_event(ev_taken[b])
+            stage[b].copy_(r0_pinned, non_blocking=True)
+            ev_in[b].record(copy_in)
+
+    def step_e2e():
+        i = e2e_state["i"]
+        b = i % 2
+        cur = torch.cuda.current_stream()
+        if i == 0:
+            fetch(b)
+        fetch(1 - b)  # the next step's input, while this step computes
+        cur.wait_event(ev_in[b])
+        r.copy_(stage[b])
+        ev_taken[b].record(cur)
         fwd_graph.replay()
-        out_pinned.copy_(r, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        cur.wait_event(ev_out[b])  # the copy out of two steps ago has left this buffer
+        result[b].copy_(r)
+        ev_done[b].record(cur)
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(ev_done[b])
+            out_pinned.copy_(result[b], non_blocking=True)
+            ev_out[b].record(copy_out)
+        if i > 0:
+            ev_out[1 - b].synchronize()  # the previous step's result is on the host
+        e2e_state["i"] = i + 1
+
+    def drain_e2e():  # before the closing timestamp: every copy of the timed steps has finished
+        cur = torch.cuda.current_stream()
+        cur.wait_stream(copy_out)
+        cur.wait_stream(copy_in)
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     ms = time_steps(torch, dist, world, step, args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
-    ms_e2e = time_steps(torch, dist, world, step_e2e, args.steps, 1)
+    ms_e2e = time_steps(torch, dist, world, step_e2e, args.steps, 1, drain=drain_e2e)
     finite = bool(torch.isfinite(r).all().item())
 
     # decode batch of 64 through the same stack
@@ -628,7 +673,9 @@ def run_ours(args):
                        "l2": "per-step working set (weights of all layers) is far larger than L2",
                        "launch": "one CUDA graph per step", "exchange": "peer stores + flag barrier (own kernels)" if world > 1 else "none"},
             "e2e": {"value": round(T / ms_e2e * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 3),
-                    "h2d_bytes_per_step": int(t_n * D * 4), "d2h_bytes_per_step": int(t_n * D * 4)},
+                    "h2d_bytes_per_step": int(t_n * D * 4), "d2h_bytes_per_step": int(t_n * D * 4),
+                    "copies": "pinned host memory, every step, on streams of their own: step i + 1's input arrives and "
+                              "step i's result leaves while a step computes; all of them inside the timed region"},
             **launches,
             "clocks": clocks, "finite": finite, "device_status": status, "parity": parity,
             "roofline": roof if roof is not None else {"bound": "tensor", "achieved": None, "peak": peaks["bf16_tflops_sustained"],
