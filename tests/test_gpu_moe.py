@@ -101,9 +101,11 @@ def test_moe_small_mxfp4_gptoss_style(cuda_device, T):
     check_layer(layer, host, synth.activations_np(rng, T, 576), T, "swiglu_oai")
 
 
-@pytest.mark.parametrize("T", [1, 64, 512])
+@pytest.mark.parametrize("T", [1, 8, 16, 64, 100, 256, 512])
 def test_moe_c2_configuration(cuda_device, T):
-    """128 experts, top-8, d_model 2048, d_ff 768, 4-bit g64, bf16 router ~ N(0, 0.02), x ~ N(0, 1), seed 0."""
+    """128 experts, top-8, d_model 2048, d_ff 768, 4-bit g64, bf16 router ~ N(0, 0.02), x ~ N(0, 1), seed 0. The token
+    counts walk the decode tile kernels (8-row tiles with one and two live row sets, 16-row tiles) and the first size of
+    the grouped GEMM."""
     rng = np.random.default_rng(0)
     layer, host = build_layer(rng, cuda_device, 128, 8, 2048, 768, max_tokens=T)
     check_layer(layer, host, synth.activations_np(rng, T, 2048), T, "silu")
