@@ -423,12 +423,14 @@ def piece_times(torch, dist, world, stack, r, t_n):
         return out
     dx, b, k = l0.dx, l0.buf, L.router.top_k
     v = L.views(t_n)
-    out["pack_push"] = tm(lambda: dx.pack_push(xn, t_n, k, v["inds"], v["pos"], v["offsets"]))
+    by_token = dx.fused_return is True  # every token row once per destination rank
+    out["pack_push"] = tm(lambda: (dx.pack_push_tokens if by_token else dx.pack_push)(xn, t_n, k, v["inds"], v["pos"],
+                                                                                       v["offsets"]))
     out["barrier_plan"] = tm(lambda: dx.barrier(then_plan=True))
     merged = [None]
 
     def index():
-        merged[0] = dx.index(b["index_dx"], b["rows_dx"])
+        merged[0] = (dx.index_tokens if by_token else dx.index)(b["index_dx"], b["rows_dx"])
 
     out["index"] = tm(index)
     out["experts_gateup_down_return"] = tm(lambda: L.experts_indexed(dx.recv, b["index_dx"], min(t_n * k, dx.max_rows), merged[0],
@@ -671,7 +673,7 @@ def run_ours(args):
                                    "d_ff 768 4-bit g64, r += MoE(RMSNorm(r))",
                        "parallelism": f"ep{world}" if world > 1 else "single", "tokens": T, "layers": args.layers,
                        "l2": "per-step working set (weights of all layers) is far larger than L2",
-                       "launch": "one CUDA graph per step", "exchange": "peer stores + flag barrier (own kernels)" if world > 1 else "none"},
+                       "launch": "one CUDA graph per step", "exchange": "peer stores (every token row once per destination rank) + flag barrier (own kernels)" if world > 1 else "none"},
             "e2e": {"value": round(T / ms_e2e * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 3),
                     "h2d_bytes_per_step": int(t_n * D * 4), "d2h_bytes_per_step": int(t_n * D * 4),
                     "copies": "pinned host memory, every step, on streams of their own: step i + 1's input arrives and "

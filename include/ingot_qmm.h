@@ -343,6 +343,17 @@ int32_t iq_ep_compact(iq_ep* ep, void* stream, const void* recv_rows, int32_t d_
  * iq_moe_experts_indexed(recv, row_index, ...). Faster: the rows are read once, by the experts' kernels. */
 int32_t iq_ep_index(iq_ep* ep, void* stream, int32_t d_model, int32_t yd_dtype, uint32_t* row_index, void** table,
                     const uint32_t** merged_counts);
+/* The dispatch with every token row sent once per destination rank, however many of its experts live there (top-8
+ * routing over 2 / 4 / 8 ranks: 4 / 2.2 / 1.5 pairs per token and rank reached, so that many times fewer bytes cross
+ * NVLink). The receive buffer then holds fp16 rows [world * tok_rows, d_model] (row s * tok_rows + t = token t of
+ * source s; tok_rows >= the largest token count of any rank, the same value on every rank) followed by the token of
+ * every received pair; iq_ep_index_tokens turns that into the row index iq_moe_experts_indexed takes. Sequence as
+ * above with iq_ep_pack_push_tokens for iq_ep_pack_push and iq_ep_index_tokens for iq_ep_index. */
+int32_t iq_ep_pack_push_tokens(iq_ep* ep, void* stream, const void* x, int32_t x_dtype, int64_t ldx, int32_t tokens,
+                               int32_t top_k, int32_t d_model, const uint32_t* inds, const uint32_t* pos,
+                               const uint32_t* offsets, int32_t tok_rows);
+int32_t iq_ep_index_tokens(iq_ep* ep, void* stream, int32_t d_model, int32_t yd_dtype, int32_t tok_rows, uint32_t* row_index,
+                           void** table, const uint32_t** merged_counts);
 
 /* ---- column-split dense linear ---------------------------------------------------------------------------------------
  * One dense quantized linear over the GPUs of one box: rank r holds output features [r*n/G, (r+1)*n/G) (rows of w /

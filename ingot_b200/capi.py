@@ -30,7 +30,7 @@ SYMBOLS = [
     "iq_scales_div16_bf16", "iq_argmax_rows", "iq_topk64_scratch_bytes", "iq_topk64", "iq_embed_rows",
     "iq_ctx_set_wait_cycles", "iq_colsplit_create", "iq_colsplit_destroy", "iq_linear_colsplit_workspace_bytes",
     "iq_linear_colsplit", "iq_had_rows", "iq_embed_rows_ternary", "iq_qmm_w8a8_workspace_bytes", "iq_qmm_w8a8",
-    "iq_ep_index", "iq_moe_experts_indexed",
+    "iq_ep_index", "iq_moe_experts_indexed", "iq_ep_pack_push_tokens", "iq_ep_index_tokens",
 ]
 
 
@@ -158,6 +158,10 @@ def lib() -> C.CDLL:
         l.iq_ep_index.argtypes = [vp, vp, i32, i32, vp, vp, C.POINTER(vp)]
         l.iq_moe_experts_indexed.argtypes = [vp, vp, vp, vp, i32, i32, vp, vp, i32, vp, vp, sz]
         l.iq_ep_index.restype = i32
+        l.iq_ep_pack_push_tokens.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, vp, vp, vp, i32]
+        l.iq_ep_index_tokens.argtypes = [vp, vp, i32, i32, i32, vp, vp, C.POINTER(vp)]
+        l.iq_ep_pack_push_tokens.restype = i32
+        l.iq_ep_index_tokens.restype = i32
         l.iq_moe_experts_indexed.restype = i32
         l.iq_had_rows.restype = i32
         l.iq_embed_rows_ternary.restype = i32

@@ -104,6 +104,53 @@ __global__ void __launch_bounds__(256) ep_pack_push_kernel(const void* __restric
     }
 }
 
+// The same dispatch with every token row sent ONCE per destination rank, however many of its experts live there (with
+// top-8 routing over 2 / 4 / 8 ranks a token has on average 4 / 2.2 / 1.5 pairs per rank it reaches). Layout of a
+// receive buffer in this mode: fp16 rows [world * tok_rows, D], row s * tok_rows + t = token t of source s (rows of
+// tokens that do not come here are simply not written), followed at byte ep_tokmap_offset() by uint32
+// [world * region_rows]: entry s * region_rows + q = the token of the q-th pair source s routes here, in its
+// local-expert order. One block per (token, destination); the first `world` blocks also push the counts.
+__host__ __device__ inline size_t ep_tokmap_offset(int world, int tok_rows, int D) {
+    return ((size_t)world * tok_rows * D * 2 + 255) / 256 * 256;
+}
+__global__ void __launch_bounds__(256) ep_pack_push_tokens_kernel(const void* __restrict__ x, int32_t x_dtype, int64_t ldx,
+                                                                 const uint32_t* __restrict__ inds, const uint32_t* __restrict__ pos,
+                                                                 const uint32_t* __restrict__ offsets, PeerPtrs recv, PeerPtrs counts,
+                                                                 int rank, int world, int E, uint32_t region_rows, int T, int D,
+                                                                 int topk, int tok_rows) {
+    const int El = E / world;
+    const int lin = blockIdx.y * gridDim.x + blockIdx.x;
+    if (lin < world) {
+        uint32_t* c = static_cast<uint32_t*>(counts.p[lin]) + rank * E;
+        for (int e = threadIdx.x; e < E; e += 256) c[e] = offsets[e + 1] - offsets[e];
+    }
+    const int t = blockIdx.x, d = blockIdx.y;
+    __shared__ int here;
+    if (threadIdx.x == 0) here = 0;
+    __syncthreads();
+    char* base = static_cast<char*>(recv.p[d]);
+    if ((int)threadIdx.x < topk) {
+        const int pair = t * topk + threadIdx.x;
+        const uint32_t e = inds[pair];
+        if ((int)(e / El) == d) {
+            uint32_t* tokmap = reinterpret_cast<uint32_t*>(base + ep_tokmap_offset(world, tok_rows, D));
+            tokmap[(size_t)rank * region_rows + (pos[pair] - offsets[d * El])] = (uint32_t)t;
+            here = 1;
+        }
+    }
+    __syncthreads();
+    if (!here) return;
+    __half* dst = reinterpret_cast<__half*>(base) + ((size_t)rank * tok_rows + t) * D;
+    const size_t src = (size_t)t * ldx;
+    for (int u = threadIdx.x; u < D / 8; u += 256) {
+        float v[8];
+        load_x8(x, x_dtype, src + u * 8, v);
+        uint4 o;
+        o.x = pack_half2(v[0], v[1]); o.y = pack_half2(v[2], v[3]); o.z = pack_half2(v[4], v[5]); o.w = pack_half2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(dst + u * 8) = o;
+    }
+}
+
 // Expert outputs of the rows this rank computed, written back into each source's return buffer at the source's own
 // expert-sorted positions. Four rows per block, 64 threads per row, four 16-byte loads in flight per thread.
 __global__ void __launch_bounds__(256) ep_return_push_kernel(const void* __restrict__ yd, int elem_bytes,
@@ -173,9 +220,12 @@ __global__ void __launch_bounds__(256) ep_compact_kernel(const __half* __restric
 // The expert-major order without moving a row: index[i] = the receive-buffer row that position i of the expert-major
 // order holds, table[i] = where its output goes in its source rank's return buffer (0 past the rows received). The
 // experts' kernels then fetch their rows through `index` (the grouped GEMM's producer gathers by row index).
+// tokmap: null, or (token mode, see ep_pack_push_tokens_kernel) the token of every received pair: the row of pair j of
+// source s is then s * tok_rows + tokmap[j].
 __global__ void __launch_bounds__(256) ep_index_kernel(const EpPlan* __restrict__ plan, PeerPtrs back, int row_bytes_back, int world,
                                                       int El, uint32_t region_rows, uint32_t* __restrict__ index,
-                                                      uint64_t* __restrict__ table) {
+                                                      uint64_t* __restrict__ table, const uint32_t* __restrict__ tokmap = nullptr,
+                                                      uint32_t tok_rows = 0) {
     uint32_t total = 0;
     for (int q = 0; q < world; q++) total += plan->from[q];
     for (uint32_t j = blockIdx.x * 256 + threadIdx.x; j < (uint32_t)world * region_rows; j += gridDim.x * 256) {
@@ -192,7 +242,7 @@ __global__ void __launch_bounds__(256) ep_index_kernel(const EpPlan* __restrict_
         }
         const uint32_t idx = j - plan->seg_recv[lo];
         const uint32_t dst = plan->seg_dst[lo] + idx;
-        index[dst] = j;
+        index[dst] = tokmap != nullptr ? s * tok_rows + tokmap[j] : j;
         table[dst] = reinterpret_cast<uint64_t>(static_cast<char*>(back.p[s]) + (size_t)(plan->seg_src[lo] + idx) * row_bytes_back);
     }
 }
@@ -382,4 +432,41 @@ extern "C" int32_t iq_ep_index(iq_ep* ep, void* stream, int32_t d_model, int32_t
         row_index, reinterpret_cast<uint64_t*>(table));
     if (merged_counts != nullptr) *merged_counts = ep->plan->merged;
     return check_cuda(ep->ctx, cudaGetLastError(), "ep_index launch");
+}
+
+extern "C" int32_t iq_ep_pack_push_tokens(iq_ep* ep, void* stream, const void* x, int32_t x_dtype, int64_t ldx, int32_t tokens,
+                                          int32_t top_k, int32_t d_model, const uint32_t* inds, const uint32_t* pos,
+                                          const uint32_t* offsets, int32_t tok_rows) {
+    if (ep == nullptr) return kErrInvalidArg;
+    if (x == nullptr || inds == nullptr || pos == nullptr || offsets == nullptr || tokens < 1 || top_k < 1 || top_k > 256 ||
+        d_model % 8 != 0 || ldx < d_model || ldx % 8 != 0 || x_dtype < 0 || x_dtype > 2 || tok_rows < tokens)
+        return fail(ep->ctx, kErrInvalidArg, "ep_pack_push_tokens: arguments");
+    if (tokens * top_k > ep->region_rows)
+        return fail(ep->ctx, kErrInvalidArg, "ep_pack_push_tokens: %d pairs exceed the region of %d rows", tokens * top_k,
+                    ep->region_rows);
+    // the token rows and the pair -> token map share the receive buffer (fp16 [world * region_rows, d_model] as created)
+    if (ep_tokmap_offset(ep->world, tok_rows, d_model) + (size_t)ep->world * ep->region_rows * 4 >
+        (size_t)ep->world * ep->region_rows * d_model * 2)
+        return fail(ep->ctx, kErrInvalidArg, "ep_pack_push_tokens: %d token rows per source do not fit the receive buffer", tok_rows);
+    if ((int64_t)tokens * ep->world < ep->world) return kErrInvalidArg;
+    ep_pack_push_tokens_kernel<<<dim3(tokens, ep->world), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        x, x_dtype, ldx, inds, pos, offsets, ep->recv, ep->counts, ep->rank, ep->world, ep->experts, (uint32_t)ep->region_rows, tokens,
+        d_model, top_k, tok_rows);
+    return check_cuda(ep->ctx, cudaGetLastError(), "ep_pack_push_tokens launch");
+}
+
+extern "C" int32_t iq_ep_index_tokens(iq_ep* ep, void* stream, int32_t d_model, int32_t yd_dtype, int32_t tok_rows,
+                                      uint32_t* row_index, void** table, const uint32_t** merged_counts) {
+    if (ep == nullptr) return kErrInvalidArg;
+    if (row_index == nullptr || table == nullptr || (yd_dtype != kF32 && yd_dtype != kF16) || d_model % 8 != 0 || tok_rows < 1)
+        return fail(ep->ctx, kErrInvalidArg, "ep_index_tokens: arguments");
+    const int64_t rows = (int64_t)ep->world * ep->region_rows;
+    const int64_t want = (rows + 255) / 256, cap = (int64_t)ep->ctx->sms * 4;
+    const uint32_t* tokmap = reinterpret_cast<const uint32_t*>(static_cast<const char*>(ep->recv.p[ep->rank]) +
+                                                               ep_tokmap_offset(ep->world, tok_rows, d_model));
+    ep_index_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        ep->plan, ep->back, d_model * (yd_dtype == kF32 ? 4 : 2), ep->world, ep->experts / ep->world, (uint32_t)ep->region_rows,
+        row_index, reinterpret_cast<uint64_t*>(table), tokmap, (uint32_t)tok_rows);
+    if (merged_counts != nullptr) *merged_counts = ep->plan->merged;
+    return check_cuda(ep->ctx, cudaGetLastError(), "ep_index_tokens launch");
 }

@@ -97,7 +97,9 @@ class ExpertParallelMoE:
         k = L.router.top_k
         L.encode(x, out, rows, only=("router", "route", "group"))
         v = L.views(rows)
-        dx.pack_push(x, rows, k, v["inds"], v["pos"], v["offsets"])  # rows and counts go out; no peer input needed
+        by_token = dx.fused_return is True
+        # rows and counts go out; no peer input needed
+        (dx.pack_push_tokens if by_token else dx.pack_push)(x, rows, k, v["inds"], v["pos"], v["offsets"])
         dx.barrier(then_plan=True)
         # the kernels are picked for the rows this rank expects to receive (about as many as it sends)
         if dx.fused_return == "compact":
@@ -107,7 +109,7 @@ class ExpertParallelMoE:
             L.experts(b["xc_dx"], min(rows * k, dx.max_rows), merged, 1, b["yd_dx"], b["ws_dx"], yd_rows=b["rows_dx"])
         elif dx.fused_return:
             # the same order as an index into the receive buffer: the experts' kernels fetch the rows themselves
-            merged = dx.index(b["index_dx"], b["rows_dx"])
+            merged = (dx.index_tokens if by_token else dx.index)(b["index_dx"], b["rows_dx"])
             L.experts_indexed(dx.recv, b["index_dx"], min(rows * k, dx.max_rows), merged, b["yd_dx"], b["ws_dx"],
                               yd_rows=b["rows_dx"])
         else:
@@ -152,9 +154,10 @@ class DeviceExchange:
     def __init__(self, experts: int, top_k: int, d_model: int, max_local_tokens: int, yd_dtype: torch.dtype,
                  device: torch.device, group=None, fused_return=True):
         """max_local_tokens: the largest token count any rank handles per call (the same value on every rank).
-        fused_return: True (the experts fetch the received rows through an index and store their outputs straight into the
-        sources' return buffers), "compact" (the rows are gathered expert-major first) or False (a copy kernel returns
-        the outputs)."""
+        fused_return: True (every token row is sent once per destination rank, the experts fetch the received rows
+        through an index and store their outputs straight into the sources' return buffers), "pairs" (the same with a
+        row per routed pair on the way out), "compact" (pair rows gathered expert-major first) or False (a copy kernel
+        returns the outputs)."""
         import os
 
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -165,6 +168,7 @@ class DeviceExchange:
         P = max_local_tokens * top_k
         # region s of a receive buffer takes whatever source s sends, at most all of its P rows
         self.fused_return = fused_return
+        self.tok_rows = max_local_tokens  # rows per source in the token layout of the receive buffer
         self.region_rows, max_rows = P, self.world * P
         self.max_rows, self.yd_dtype, self.d_model = max_rows, yd_dtype, d_model
         esz = torch.empty((), dtype=yd_dtype).element_size()
@@ -202,6 +206,22 @@ class DeviceExchange:
         dt = {torch.float32: capi.IQ_F32, torch.float16: capi.IQ_F16, torch.bfloat16: capi.IQ_BF16}[x.dtype]
         self.ctx.check(capi.lib().iq_ep_pack_push(self._h, _stream_ptr(stream), x.data_ptr(), dt, x.stride(0), tokens, top_k,
                                                   self.d_model, inds.data_ptr(), pos.data_ptr(), offsets.data_ptr()))
+
+    def pack_push_tokens(self, x: torch.Tensor, tokens: int, top_k: int, inds: torch.Tensor, pos: torch.Tensor,
+                         offsets: torch.Tensor, stream=None):
+        """The dispatch with each token row sent once per destination rank (and the token of every pair beside it)."""
+        dt = {torch.float32: capi.IQ_F32, torch.float16: capi.IQ_F16, torch.bfloat16: capi.IQ_BF16}[x.dtype]
+        self.ctx.check(capi.lib().iq_ep_pack_push_tokens(self._h, _stream_ptr(stream), x.data_ptr(), dt, x.stride(0), tokens,
+                                                         top_k, self.d_model, inds.data_ptr(), pos.data_ptr(),
+                                                         offsets.data_ptr(), self.tok_rows))
+
+    def index_tokens(self, row_index: torch.Tensor, table: torch.Tensor, stream=None) -> int:
+        """`index` for rows that arrived by `pack_push_tokens`."""
+        dt = capi.IQ_F32 if self.yd_dtype == torch.float32 else capi.IQ_F16
+        merged = C.c_void_p()
+        self.ctx.check(capi.lib().iq_ep_index_tokens(self._h, _stream_ptr(stream), self.d_model, dt, self.tok_rows,
+                                                     row_index.data_ptr(), table.data_ptr(), C.byref(merged)))
+        return merged.value
 
     def return_push(self, yd: torch.Tensor, stream=None):
         dt = capi.IQ_F32 if yd.dtype == torch.float32 else capi.IQ_F16

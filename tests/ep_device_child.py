@@ -33,7 +33,7 @@ def main():
     tmax = -(-T // world)  # the region size must be the same on every rank
     yd_dtype = torch.float16 if "f16" in sys.argv[1:] else torch.float32
     epl = ep.ExpertParallelMoE(layer, None, tn, T * K)
-    dx = ep.DeviceExchange(E, K, D, tmax, yd_dtype, dev, fused_return=False if "copy" in sys.argv[1:] else ("compact" if "compact" in sys.argv[1:] else True))
+    dx = ep.DeviceExchange(E, K, D, tmax, yd_dtype, dev, fused_return=False if "copy" in sys.argv[1:] else ("compact" if "compact" in sys.argv[1:] else ("pairs" if "pairs" in sys.argv[1:] else True)))
     epl.use_device_exchange(dx)
     xt = torch.from_numpy(x[tl:tl + tn]).to(dev).to(torch.bfloat16)
     out = torch.zeros(tn, D, dtype=torch.float32, device=dev)

@@ -158,6 +158,71 @@ def test_ep_device_pieces_emulated_on_one_gpu(cuda_device, world, T, yd_dtype, f
             capi.lib().iq_ep_destroy(h)
 
 
+@pytest.mark.parametrize("world,T,yd_dtype", [(2, 6, torch.float32), (4, 37, torch.float16), (8, 64, torch.float32),
+                                              (2, 200, torch.float16), (4, 150, torch.float32)])
+def test_ep_token_dispatch_emulated_on_one_gpu(cuda_device, world, T, yd_dtype):
+    """The dispatch that sends every token row once per destination rank (iq_ep_pack_push_tokens: the rows in a token
+    layout, the token of every routed pair beside them) and the index built from it (iq_ep_index_tokens), with every
+    rank's buffers on one GPU and the ranks run one after the other; two passes over the same buffers."""
+    import ctypes as C
+
+    from ingot_b200 import capi
+    rng = np.random.default_rng(world * 977 + T)
+    E, K, D, I = 32, 4, 256, 128
+    layers, wr, weights = make_layers(rng, cuda_device, E, K, D, I, world, T)
+    x = synth.activations_np(rng, T, D)
+    slices = [ep.token_slice(r, world, T) for r in range(world)]
+    tok_rows = max(n for _, n in slices)
+    region = tok_rows * K
+    cap = world * region
+    mk = lambda shape, dt: [torch.zeros(shape, dtype=dt, device=cuda_device) for _ in range(world)]
+    recv, back = mk((cap, D), torch.float16), mk((region, D), yd_dtype)
+    flags, counts = mk((64,), torch.int32), mk((world, E), torch.int32)
+    ctx = capi.context(cuda_device.index or 0)
+    arr = lambda ts: (C.c_void_p * world)(*[t.data_ptr() for t in ts])
+    eps = []
+    for r in range(world):
+        h = C.c_void_p()
+        ctx.check(capi.lib().iq_ep_create(ctx.handle, r, world, E, region, arr(recv), arr(back), arr(flags), arr(counts),
+                                          C.byref(h)))
+        eps.append(h)
+    xs = [x_tensor(x[lo:lo + n], cuda_device) for lo, n in slices]
+    outs = [torch.zeros(n, D, dtype=torch.float32, device=cuda_device) for _, n in slices]
+    dt = {torch.float32: capi.IQ_F32, torch.float16: capi.IQ_F16, torch.bfloat16: capi.IQ_BF16}
+    try:
+        for rep in range(2):
+            for r, (lo, n) in enumerate(slices):
+                layers[r].encode(xs[r], outs[r], n, only=("router", "route", "group"))
+                v = layers[r].views(n)
+                ctx.check(capi.lib().iq_ep_pack_push_tokens(eps[r], 0, xs[r].data_ptr(), dt[xs[r].dtype], xs[r].stride(0), n, K,
+                                                            D, v["inds"].data_ptr(), v["pos"].data_ptr(),
+                                                            v["offsets"].data_ptr(), tok_rows))
+            for r in range(world):
+                ctx.check(capi.lib().iq_ep_plan(eps[r], 0))
+                yd = torch.zeros(cap, D, dtype=yd_dtype, device=cuda_device)
+                ws = torch.empty(layers[r].experts_workspace_bytes(cap, world), dtype=torch.uint8, device=cuda_device)
+                table = torch.full((cap,), -1, dtype=torch.int64, device=cuda_device)
+                index = torch.full((cap,), -1, dtype=torch.int32, device=cuda_device)
+                merged = C.c_void_p()
+                ctx.check(capi.lib().iq_ep_index_tokens(eps[r], 0, D, dt[yd_dtype], tok_rows, index.data_ptr(), table.data_ptr(),
+                                                        C.byref(merged)))
+                layers[r].experts_indexed(recv[r], index, min(cap, T * K), merged.value, yd, ws, yd_rows=table)
+                torch.cuda.synchronize()
+                total = int(counts[r].to(torch.int64)[:, r * (E // world):(r + 1) * (E // world)].sum().item())
+                idx = index[:total].cpu().numpy()
+                assert idx.min() >= 0 and idx.max() < world * tok_rows, "a row index outside the token layout"
+            for r, (lo, n) in enumerate(slices):
+                layers[r].combine_rows(back[r], outs[r], n)
+            torch.cuda.synchronize()
+            got = torch.cat(outs).cpu().numpy()
+            inds, wts = qref.route(qref.router_logits(x, wr), K)
+            ref = qref.moe_ffn(x, inds, wts, weights)
+            assert qref.max_rel(got, ref) <= TOL
+    finally:
+        for h in eps:
+            capi.lib().iq_ep_destroy(h)
+
+
 def free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -178,7 +243,7 @@ def test_ep_nccl_two_ranks():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("ret", ["f32", "f16", "f16,copy", "f16,compact"])
+@pytest.mark.parametrize("ret", ["f32", "f16", "f16,copy", "f16,compact", "f16,pairs"])
 def test_ep_device_exchange(ret):
     """The exchange done by the library's own kernels over peer memory (no host synchronisation), eager and from a CUDA
     graph, on as many GPUs as the box has (2, 4 or 8)."""
